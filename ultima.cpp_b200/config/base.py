@@ -1,0 +1,92 @@
+"""Registry of architectures and the reading of ``config.json``.
+
+One table maps the name in ``config.json`` (``architectures[0]``, or ``model_type``)
+to the typed configuration class and to the function that turns a configuration
+into a model description.  An unknown name and a known name that cannot run give two
+different errors, as in the reference (src/model/qwen_model.cpp:259-272, registry
+table src/model/arch_registry.cpp:13-95).
+"""
+from __future__ import annotations
+
+import json
+import os
+from dataclasses import dataclass
+from typing import Callable, Optional
+
+
+class ConfigError(ValueError):
+    """A configuration that is missing a key, holds a bad value or names no known model."""
+
+
+@dataclass(frozen=True)
+class ArchitectureEntry:
+    name: str                      # "Qwen3ForCausalLM"
+    model_type: str                # "qwen3"
+    supported: bool
+    notes: str
+    config_cls: Optional[type] = None
+    build_spec: Optional[Callable] = None   # config -> ModelSpec
+
+
+_REGISTRY: dict[str, ArchitectureEntry] = {}
+
+
+def register_architecture(entry: ArchitectureEntry, replace: bool = False) -> ArchitectureEntry:
+    for key in (entry.name, entry.model_type):
+        if key in _REGISTRY and _REGISTRY[key].name != entry.name and not replace:
+            raise ConfigError(f"architecture key '{key}' is already registered")
+    _REGISTRY[entry.name] = entry
+    _REGISTRY[entry.model_type] = entry
+    return entry
+
+
+def known_architectures() -> list[ArchitectureEntry]:
+    seen, out = set(), []
+    for e in _REGISTRY.values():
+        if e.name not in seen:
+            seen.add(e.name)
+            out.append(e)
+    return out
+
+
+def find_architecture(name: str) -> ArchitectureEntry:
+    entry = _REGISTRY.get(name)
+    if entry is None:
+        known = ", ".join(sorted(e.name for e in known_architectures()))
+        raise ConfigError(f"unknown architecture '{name}'; known architectures: {known}")
+    if not entry.supported:
+        raise ConfigError(f"architecture '{name}' is recognized but not runnable: {entry.notes}")
+    return entry
+
+
+def read_config_json(model_dir: str) -> dict:
+    path = os.path.join(model_dir, "config.json")
+    if not os.path.isfile(path):
+        raise ConfigError(f"no config.json in '{model_dir}'")
+    with open(path, "r", encoding="utf-8") as f:
+        try:
+            data = json.load(f)
+        except json.JSONDecodeError as e:
+            raise ConfigError(f"{path} is not valid JSON: {e}") from e
+    if not isinstance(data, dict):
+        raise ConfigError(f"{path} must hold a JSON object")
+    return data
+
+
+def architecture_name(data: dict) -> str:
+    archs = data.get("architectures")
+    if isinstance(archs, list) and archs:
+        return str(archs[0])
+    if "model_type" in data:
+        return str(data["model_type"])
+    raise ConfigError("config.json names no architecture (neither 'architectures' nor 'model_type')")
+
+
+def config_from_dict(data: dict):
+    """Typed configuration of whatever architecture ``data`` names."""
+    entry = find_architecture(architecture_name(data))
+    return entry.config_cls.from_dict(data)
+
+
+def config_from_dir(model_dir: str):
+    return config_from_dict(read_config_json(model_dir))

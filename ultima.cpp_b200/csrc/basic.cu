@@ -1,0 +1,237 @@
+// Row-wise and element-wise kernels: embedding, RMSNorm, per-head norm + rotation + cache
+// write, SiLU-gate product, type conversion, random fill.
+//
+// Each restates one step of the reference's CPU forward pass for a whole ragged batch:
+//   embedding row read        src/model/qwen_model.cpp:145-157
+//   RMSNorm                   src/kernels/rmsnorm.cpp:10-17
+//   per-head norm of q and k  src/model/qwen_block.cpp:76-82, :713-718
+//   half-split rotation       src/kernels/rope.cpp:17-52
+//   cache write before read   src/model/qwen_block.cpp:725-727
+//   silu(gate) * up           src/kernels/elementwise.cpp:62-68
+// Sums of squares, the rotation and the gate are computed in 32-bit whatever the storage.
+#include "common.cuh"
+
+// ---------------------------------------------------------------------------------------
+// embedding: x[t, :] = float(table[ids[t], :]); a bad id sets *status and writes zeros
+// ---------------------------------------------------------------------------------------
+template <typename TT>
+__global__ void embed_kernel(const TT* __restrict__ table, const int* __restrict__ ids,
+                             float* __restrict__ x, int width, int vocab, int* status) {
+    const int t = blockIdx.x;
+    const int id = ids[t];
+    const bool ok = id >= 0 && id < vocab;
+    if (!ok && threadIdx.x == 0) atomicExch(status, 1);
+    const TT* row = table + (long long)(ok ? id : 0) * width;
+    for (int i = threadIdx.x; i < width; i += blockDim.x)
+        x[(long long)t * width + i] = ok ? to_f32<TT>(row[i]) : 0.f;
+}
+
+UB_API int ub_embed(const void* table, int table_dtype, const int* ids, float* x, int n_tokens,
+                    int width, int vocab, int* status, cudaStream_t st) {
+    if (n_tokens <= 0) return 0;
+    const int threads = width >= 1024 ? 256 : 128;
+    if (table_dtype == UB_F32)
+        embed_kernel<float><<<n_tokens, threads, 0, st>>>((const float*)table, ids, x, width, vocab, status);
+    else if (table_dtype == UB_BF16)
+        embed_kernel<__nv_bfloat16><<<n_tokens, threads, 0, st>>>((const __nv_bfloat16*)table, ids, x, width, vocab, status);
+    else return UB_ERR_UNSUPPORTED;
+    UB_LAUNCH_CHECK();
+    return 0;
+}
+
+// ---------------------------------------------------------------------------------------
+// RMSNorm of rows of a float32 matrix; ``rows`` (optional) picks the input rows
+// ---------------------------------------------------------------------------------------
+template <typename TO>
+__global__ void rmsnorm_kernel(const float* __restrict__ x, const int* __restrict__ rows,
+                               const float* __restrict__ w, TO* __restrict__ out, int width, float eps) {
+    __shared__ float red[33];
+    const int r = blockIdx.x;
+    const float* xr = x + (long long)(rows ? rows[r] : r) * width;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) { const float v = xr[i]; ss += v * v; }
+    ss = block_sum(ss, red);
+    const float inv = 1.0f / sqrtf(ss / (float)width + eps);
+    for (int i = threadIdx.x; i < width; i += blockDim.x)
+        out[(long long)r * width + i] = from_f32<TO>(xr[i] * w[i] * inv);
+}
+
+UB_API int ub_rmsnorm(const float* x, const int* rows, const float* w, void* out, int out_dtype,
+                      int n_rows, int width, float eps, cudaStream_t st) {
+    if (n_rows <= 0) return 0;
+    const int threads = width >= 2048 ? 512 : (width >= 512 ? 256 : 128);
+    if (out_dtype == UB_F32)
+        rmsnorm_kernel<float><<<n_rows, threads, 0, st>>>(x, rows, w, (float*)out, width, eps);
+    else if (out_dtype == UB_BF16)
+        rmsnorm_kernel<__nv_bfloat16><<<n_rows, threads, 0, st>>>(x, rows, w, (__nv_bfloat16*)out, width, eps);
+    else return UB_ERR_UNSUPPORTED;
+    UB_LAUNCH_CHECK();
+    return 0;
+}
+
+// ---------------------------------------------------------------------------------------
+// per-head norm (optional) + rotation (optional) of q and k, and the write of k and v into
+// the paged cache.  One warp for each (token, head) of the fused [q | k | v] row.
+//   qkv   [T, (nh + 2 nkv) * hd]   q heads are normed and rotated in place
+//   cos, sin  [max_pos, hd/2] float32 (null: no rotation)
+//   qw, kw    [hd] float32 (null: no norm)
+// ---------------------------------------------------------------------------------------
+template <typename TA, typename TC>
+__global__ void qk_prepare_kernel(TA* __restrict__ qkv, const float* __restrict__ qw,
+                                  const float* __restrict__ kw, const float* __restrict__ cs,
+                                  const float* __restrict__ sn, const int* __restrict__ tok_pos,
+                                  const int* __restrict__ tok_seq, TC* __restrict__ kcache,
+                                  TC* __restrict__ vcache, PagedKV c, int n_tokens, int nh, float eps,
+                                  int write_kv) {
+    const int lane = threadIdx.x & 31;
+    const long long wid = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    const int heads_all = nh + 2 * c.n_kv_heads;
+    if (wid >= (long long)n_tokens * heads_all) return;
+    const int t = (int)(wid / heads_all), h = (int)(wid % heads_all);
+    const int hd = c.head_dim, half = hd >> 1;
+    TA* row = qkv + ((long long)t * heads_all + h) * hd;
+    const int pos = tok_pos[t];
+    const int seq = tok_seq[t];
+    if (h >= nh + c.n_kv_heads) {                       // a value head: copy into the cache
+        if (!write_kv) return;
+        TC* dst = vcache + paged_offset(c, seq, pos, h - nh - c.n_kv_heads);
+        for (int i = lane; i < hd; i += 32) dst[i] = from_f32<TC>(to_f32<TA>(row[i]));
+        return;
+    }
+    const bool is_k = h >= nh;
+    if (is_k && !write_kv) return;
+    const float* w = is_k ? kw : qw;
+    float ss = 0.f;
+    for (int j = lane; j < half; j += 32) {
+        const float a = to_f32<TA>(row[j]), b = to_f32<TA>(row[j + half]);
+        ss += a * a + b * b;
+    }
+    ss = warp_sum(ss);
+    const float inv = w ? 1.0f / sqrtf(ss / (float)hd + eps) : 1.0f;
+    TC* dst = is_k ? kcache + paged_offset(c, seq, pos, h - nh) : nullptr;
+    for (int j = lane; j < half; j += 32) {
+        float a = to_f32<TA>(row[j]), b = to_f32<TA>(row[j + half]);
+        if (w) { a = a * w[j] * inv; b = b * w[j + half] * inv; }
+        float ra = a, rb = b;
+        if (cs) {
+            const float co = cs[(long long)pos * half + j], si = sn[(long long)pos * half + j];
+            ra = a * co - b * si;
+            rb = a * si + b * co;
+        }
+        if (is_k) { dst[j] = from_f32<TC>(ra); dst[j + half] = from_f32<TC>(rb); }
+        else { row[j] = from_f32<TA>(ra); row[j + half] = from_f32<TA>(rb); }
+    }
+}
+
+UB_API int ub_qk_prepare(void* qkv, int act_dtype, const float* qw, const float* kw, const float* cs,
+                         const float* sn, const int* tok_pos, const int* tok_seq, void* kcache,
+                         void* vcache, int cache_dtype, const int* table, int pages_per_seq, int ring,
+                         int page, int n_tokens, int nh, int nkv, int hd, float eps, int write_kv,
+                         cudaStream_t st) {
+    if (n_tokens <= 0) return 0;
+    if (hd % 2 != 0 || ring % page != 0) return UB_ERR_ARG;
+    PagedKV c{table, pages_per_seq, ring, page, nkv, hd};
+    const long long warps = (long long)n_tokens * (nh + 2 * nkv);
+    const int wpb = 8;
+    const unsigned grid = (unsigned)((warps + wpb - 1) / wpb);
+#define LAUNCH(TA, TC) qk_prepare_kernel<TA, TC><<<grid, wpb * 32, 0, st>>>((TA*)qkv, qw, kw, cs, sn, \
+        tok_pos, tok_seq, (TC*)kcache, (TC*)vcache, c, n_tokens, nh, eps, write_kv)
+    if (act_dtype == UB_F32 && cache_dtype == UB_F32) LAUNCH(float, float);
+    else if (act_dtype == UB_BF16 && cache_dtype == UB_BF16) LAUNCH(__nv_bfloat16, __nv_bfloat16);
+    else if (act_dtype == UB_F32 && cache_dtype == UB_BF16) LAUNCH(float, __nv_bfloat16);
+    else return UB_ERR_UNSUPPORTED;
+#undef LAUNCH
+    UB_LAUNCH_CHECK();
+    return 0;
+}
+
+// ---------------------------------------------------------------------------------------
+// out[t, f] = silu(gu[t, f]) * gu[t, F + f]   (gate and up side by side in one row)
+// ---------------------------------------------------------------------------------------
+template <typename TI, typename TO>
+__global__ void silu_mul_kernel(const TI* __restrict__ gu, TO* __restrict__ out, long long n, int F) {
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const long long t = i / F;
+    const int f = (int)(i % F);
+    const float g = to_f32<TI>(gu[t * 2 * F + f]), u = to_f32<TI>(gu[t * 2 * F + F + f]);
+    out[i] = from_f32<TO>(g / (1.0f + expf(-g)) * u);
+}
+
+UB_API int ub_silu_mul(const void* gu, int in_dtype, void* out, int out_dtype, int n_tokens, int F,
+                       cudaStream_t st) {
+    const long long n = (long long)n_tokens * F;
+    if (n <= 0) return 0;
+    const unsigned grid = (unsigned)((n + 255) / 256);
+    if (in_dtype == UB_F32 && out_dtype == UB_F32) silu_mul_kernel<float, float><<<grid, 256, 0, st>>>((const float*)gu, (float*)out, n, F);
+    else if (in_dtype == UB_F32 && out_dtype == UB_BF16) silu_mul_kernel<float, __nv_bfloat16><<<grid, 256, 0, st>>>((const float*)gu, (__nv_bfloat16*)out, n, F);
+    else if (in_dtype == UB_BF16 && out_dtype == UB_BF16) silu_mul_kernel<__nv_bfloat16, __nv_bfloat16><<<grid, 256, 0, st>>>((const __nv_bfloat16*)gu, (__nv_bfloat16*)out, n, F);
+    else return UB_ERR_UNSUPPORTED;
+    UB_LAUNCH_CHECK();
+    return 0;
+}
+
+// ---------------------------------------------------------------------------------------
+// conversion and accumulation: out = convert(in);  acc += in
+// ---------------------------------------------------------------------------------------
+template <typename TI, typename TO>
+__global__ void convert_kernel(const TI* __restrict__ in, TO* __restrict__ out, long long n) {
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) out[i] = from_f32<TO>(to_f32<TI>(in[i]));
+}
+UB_API int ub_convert(const void* in, int in_dtype, void* out, int out_dtype, long long n, cudaStream_t st) {
+    if (n <= 0) return 0;
+    const unsigned grid = (unsigned)((n + 255) / 256);
+    if (in_dtype == UB_F32 && out_dtype == UB_BF16) convert_kernel<float, __nv_bfloat16><<<grid, 256, 0, st>>>((const float*)in, (__nv_bfloat16*)out, n);
+    else if (in_dtype == UB_BF16 && out_dtype == UB_F32) convert_kernel<__nv_bfloat16, float><<<grid, 256, 0, st>>>((const __nv_bfloat16*)in, (float*)out, n);
+    else if (in_dtype == UB_F32 && out_dtype == UB_F32) convert_kernel<float, float><<<grid, 256, 0, st>>>((const float*)in, (float*)out, n);
+    else if (in_dtype == UB_BF16 && out_dtype == UB_BF16) convert_kernel<__nv_bfloat16, __nv_bfloat16><<<grid, 256, 0, st>>>((const __nv_bfloat16*)in, (__nv_bfloat16*)out, n);
+    else return UB_ERR_UNSUPPORTED;
+    UB_LAUNCH_CHECK();
+    return 0;
+}
+
+template <typename TI>
+__global__ void add_into_kernel(float* __restrict__ acc, const TI* __restrict__ in, long long n) {
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) acc[i] += to_f32<TI>(in[i]);
+}
+UB_API int ub_add_into(float* acc, const void* in, int in_dtype, long long n, cudaStream_t st) {
+    if (n <= 0) return 0;
+    const unsigned grid = (unsigned)((n + 255) / 256);
+    if (in_dtype == UB_F32) add_into_kernel<float><<<grid, 256, 0, st>>>(acc, (const float*)in, n);
+    else if (in_dtype == UB_BF16) add_into_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(acc, (const __nv_bfloat16*)in, n);
+    else return UB_ERR_UNSUPPORTED;
+    UB_LAUNCH_CHECK();
+    return 0;
+}
+
+// ---------------------------------------------------------------------------------------
+// random fill: out[i] = shift + std * N(0,1), from a counter hash of (seed, i)
+// ---------------------------------------------------------------------------------------
+__device__ __forceinline__ unsigned long long mix64(unsigned long long z) {
+    z += 0x9E3779B97F4A7C15ull;
+    z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
+    z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
+    return z ^ (z >> 31);
+}
+template <typename TO>
+__global__ void fill_normal_kernel(TO* __restrict__ out, long long n, unsigned long long seed, float shift, float stdv) {
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const unsigned long long r = mix64(seed ^ mix64((unsigned long long)i));
+    const float u1 = ((float)(unsigned)(r >> 40) + 0.5f) * (1.0f / 16777216.0f);
+    const float u2 = ((float)(unsigned)((r >> 8) & 0xFFFFFFu) + 0.5f) * (1.0f / 16777216.0f);
+    const float z = sqrtf(-2.0f * logf(u1)) * cospif(2.0f * u2);
+    out[i] = from_f32<TO>(shift + stdv * z);
+}
+UB_API int ub_fill_normal(void* out, int dtype, long long n, unsigned long long seed, float shift, float stdv,
+                          cudaStream_t st) {
+    if (n <= 0) return 0;
+    const unsigned grid = (unsigned)((n + 255) / 256);
+    if (dtype == UB_F32) fill_normal_kernel<float><<<grid, 256, 0, st>>>((float*)out, n, seed, shift, stdv);
+    else if (dtype == UB_BF16) fill_normal_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>((__nv_bfloat16*)out, n, seed, shift, stdv);
+    else return UB_ERR_UNSUPPORTED;
+    UB_LAUNCH_CHECK();
+    return 0;
+}

@@ -1,0 +1,83 @@
+// Shared helpers of the kernels: element types, conversions, reductions, launch checks.
+#pragma once
+#include <cuda_runtime.h>
+#include <cuda_bf16.h>
+#include <stdint.h>
+
+#define UB_API extern "C" __attribute__((visibility("default")))
+
+// element type codes of the C interface
+enum : int { UB_F32 = 0, UB_BF16 = 1 };
+
+// Every exported function returns 0 or a negative code for a refused argument, or the
+// positive cudaError_t of a failed launch.
+#define UB_ERR_ARG (-1)
+#define UB_ERR_UNSUPPORTED (-2)
+#define UB_LAUNCH_CHECK() do { cudaError_t e__ = cudaGetLastError(); if (e__ != cudaSuccess) return (int)e__; } while (0)
+
+template <typename T> __device__ __forceinline__ float to_f32(T v);
+template <> __device__ __forceinline__ float to_f32<float>(float v) { return v; }
+template <> __device__ __forceinline__ float to_f32<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+
+template <typename T> __device__ __forceinline__ T from_f32(float v);
+template <> __device__ __forceinline__ float from_f32<float>(float v) { return v; }
+template <> __device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+// Sum over a block of up to 1024 threads; every thread gets the result.  ``red`` holds 33 floats.
+__device__ __forceinline__ float block_sum(float v, float* red) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+    v = warp_sum(v);
+    __syncthreads();
+    if (lane == 0) red[warp] = v;
+    __syncthreads();
+    if (warp == 0) {
+        float t = lane < nw ? red[lane] : 0.f;
+        t = warp_sum(t);
+        if (lane == 0) red[32] = t;
+    }
+    __syncthreads();
+    return red[32];
+}
+__device__ __forceinline__ float block_max(float v, float* red) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+    v = warp_max(v);
+    __syncthreads();
+    if (lane == 0) red[warp] = v;
+    __syncthreads();
+    if (warp == 0) {
+        float t = lane < nw ? red[lane] : -INFINITY;
+        t = warp_max(t);
+        if (lane == 0) red[32] = t;
+    }
+    __syncthreads();
+    return red[32];
+}
+
+// Where a sequence's position lies in a paged cache.  A sequence's pages are listed in
+// ``table`` (``pages_per_seq`` entries for each sequence of the step); ``ring`` is the
+// number of positions the sequence's storage holds (a multiple of the page size): a full
+// cache holds all positions, a window cache wraps around.
+struct PagedKV {
+    const int* table;       // [n_seqs, pages_per_seq]
+    int pages_per_seq;
+    int ring;               // positions held for each sequence
+    int page;               // positions in a page
+    int n_kv_heads;
+    int head_dim;
+};
+__device__ __forceinline__ long long paged_offset(const PagedKV& c, int seq, int pos, int kv_head) {
+    const int li = pos % c.ring;
+    const int pg = c.table[(long long)seq * c.pages_per_seq + li / c.page];
+    return (((long long)pg * c.n_kv_heads + kv_head) * c.page + (li % c.page)) * c.head_dim;
+}

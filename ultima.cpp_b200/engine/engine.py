@@ -1,0 +1,220 @@
+"""The step function: a batch of sequences that started together, with unequal lengths;
+their prompts in one step, then one token each.
+
+``Engine.step`` runs only the tokens it is given, as one batch, from what earlier steps left
+in the cache, and returns float32 logits at the wanted places.  The reference has two calls
+on one sequence, prefill and decode, both one function underneath "because two code paths
+would be two chances for them to disagree" (include/ultima/model/qwen_block.hpp:104-107,
+src/model/qwen_model.cpp:80-141); here the same holds for a whole ragged batch: prompts and
+single tokens go through the same kernels.  Long prompts are cut into several passes inside
+a step (the reference cuts them into chunks of 32, src/model/qwen_model.cpp:104-117); the
+cut changes no result beyond rounding.
+"""
+from __future__ import annotations
+
+import numpy as np
+import torch
+
+from ..arch import model_spec_for
+from ..cache import Cache, CacheError, PAGE
+from ..config.base import config_from_dir, find_architecture
+from ..parts.base import KVNeed, ModelSpec
+from ..weights import load_weights
+from .batch import build_step_batch
+from .model import Model
+from .runtime import Runtime
+
+
+class StepError(ValueError):
+    """A step that cannot run: bad token ids, slots, positions; nothing was launched."""
+
+
+def _dtype_of(name) -> torch.dtype:
+    if isinstance(name, torch.dtype):
+        return name
+    try:
+        return {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16,
+                "float32": torch.float32, "fp32": torch.float32, "f32": torch.float32}[str(name)]
+    except KeyError:
+        raise ValueError(f"dtype must be bfloat16 or float32, got {name!r}") from None
+
+
+class Engine:
+    """A model on one GPU with its cache.
+
+    max_tokens       positions that live sequences may hold together, each sequence rounded up
+                     to a page of 64; sizes the cache
+    max_seqs         slots (sequences alive at once)
+    max_step_tokens  tokens of one pass through the layers; longer steps are cut into passes
+    """
+
+    def __init__(self, spec: ModelSpec, tensors: dict, dtype="bfloat16", max_tokens: int = 4096,
+                 max_seqs: int | None = None, max_step_tokens: int = 4096, device="cuda:0",
+                 max_context: int | None = None, poison_cache: bool = False, runtime=None):
+        self.spec = spec
+        self.dtype = _dtype_of(dtype)
+        self.device = torch.device(device)
+        if self.device.type != "cuda":
+            raise RuntimeError("the engine runs on a CUDA device only; there is no CPU path")
+        if not torch.cuda.is_available():
+            raise RuntimeError("no CUDA device is available; the engine has no CPU path")
+        torch.cuda.set_device(self.device)
+        self.rt = runtime or Runtime(self.device, self.dtype)
+        self.model = Model(spec, tensors, self.rt)
+        self.max_tokens = int(max_tokens)
+        self.max_context = int(min(max_context or spec.max_positions, spec.max_positions))
+        self.max_step_tokens = int(max_step_tokens)
+        n_slots = int(max_seqs) if max_seqs else max(1, min(1024, -(-self.max_tokens // PAGE)))
+        needs = self.model.cache_needs()
+        windows = [n.window for need in needs for n in (need if isinstance(need, tuple) else (need,))
+                   if isinstance(n, KVNeed) and n.window is not None]
+        # a sequence brings at most this many tokens in one pass; with windows it also
+        # bounds the span a windowed group must hold
+        self.seq_chunk = self.max_step_tokens if not windows else min(self.max_step_tokens, 1024)
+        self.cache = Cache(needs, self.model.cache_sources(), self.max_tokens, self.max_context,
+                           n_slots, self.seq_chunk, dtype=self.rt.cache_dtype, device=self.device,
+                           poison=poison_cache)
+
+    # ---- construction ------------------------------------------------------------------
+    @classmethod
+    def from_dir(cls, model_dir: str, dtype="bfloat16", **kw) -> "Engine":
+        """Model class by config.json, weights by name from model.safetensors."""
+        cfg = config_from_dir(model_dir)
+        entry = find_architecture(cfg.architecture)
+        max_ctx = kw.get("max_context")
+        # positions beyond what the cache can hold are never reached: size tables to that
+        reach = min(cfg.max_position_embeddings, max_ctx or cfg.max_position_embeddings,
+                    -(-int(kw.get("max_tokens", 4096)) // PAGE) * PAGE)
+        spec = entry.build_spec(cfg, max_positions=reach)
+        device = kw.get("device", "cuda:0")
+        optional = ("lm_head.weight",) if spec.head.get("tied") else ()
+        tensors = load_weights(model_dir, spec.weight_specs(), _dtype_of(dtype), device, optional)
+        eng = cls(spec, tensors, dtype=dtype, **kw)
+        eng.config = cfg
+        return eng
+
+    def warm_up(self) -> None:
+        """Compile and load every kernel this model uses by running one short sequence."""
+        s = self.open(1)
+        try:
+            self.step(s, [[0, 0, 0]], [[2]])
+            self.step(s, [[0]], [[0]])
+            torch.cuda.synchronize(self.device)
+        finally:
+            self.close(s)
+
+    # ---- slots -------------------------------------------------------------------------
+    def open(self, n: int = 1) -> list[int]:
+        """Acquire ``n`` slots for sequences that start together."""
+        got = []
+        try:
+            for _ in range(n):
+                got.append(self.cache.acquire())
+        except CacheError:
+            for s in got:
+                self.cache.release(s)
+            raise
+        return got
+
+    def close(self, slots) -> None:
+        """Give slots (and what they hold) back."""
+        for s in slots:
+            self.cache.release(s)
+
+    def length(self, slot: int) -> int:
+        return self.cache.length(slot)
+
+    # ---- the step ----------------------------------------------------------------------
+    def step(self, slots, tokens, want=None) -> torch.Tensor:
+        """slots[i] continues with tokens[i]; want[i] lists the places among tokens[i] whose
+        logits are asked for (None: the last of each).  Returns float32 [sum(len(want[i])),
+        vocabulary] on the device, in the order of the entries and of ``want``."""
+        B = len(slots)
+        if len(tokens) != B:
+            raise StepError("step: one token list for each slot is needed")
+        if want is None:
+            want = [[len(t) - 1] if len(t) else [] for t in tokens]
+        if len(want) != B:
+            raise StepError("step: one list of wanted places for each slot is needed")
+        if len(set(slots)) != B:
+            raise StepError("step: a slot is named twice")
+        V = self.spec.vocab_size
+        lens_after = {}
+        for s, t, w in zip(slots, tokens, want):
+            self.cache.slots.check(s)
+            if len(t) == 0:
+                if len(w):
+                    raise StepError("step: logits wanted of a sequence that brings no token")
+                continue
+            a = np.asarray(t)
+            if a.ndim != 1 or not np.issubdtype(a.dtype, np.integer):
+                raise StepError("step: tokens must be flat lists of integers")
+            if a.min() < 0 or a.max() >= V:
+                bad = int(a[(a < 0) | (a >= V)][0])
+                raise StepError(f"step: token id {bad} is outside the vocabulary [0, {V})")
+            for p in w:
+                if not (0 <= p < len(t)):
+                    raise StepError(f"step: wanted place {p} is outside the {len(t)} tokens given")
+            n_after = self.cache.length(s) + len(t)
+            if n_after > self.max_context:
+                raise StepError(f"step: slot {s} would reach {n_after} positions; the limit is "
+                                f"{self.max_context}")
+            lens_after[s] = n_after
+        try:
+            self.cache.can_hold(lens_after)
+        except CacheError as e:
+            raise StepError(str(e)) from e
+
+        # rows of the result: entry by entry, in the order of ``want``
+        n_want = sum(len(w) for w in want)
+        row_of = {}
+        r = 0
+        for i, w in enumerate(want):
+            for p in w:
+                row_of.setdefault((i, p), []).append(r)
+                r += 1
+        done = [0] * B
+        pieces, piece_rows = [], []
+        while True:
+            budget = self.max_step_tokens
+            sel, new, before, wrows, wdst = [], [], [], [], []
+            base = 0
+            for i in range(B):
+                left = len(tokens[i]) - done[i]
+                if left <= 0 or budget <= 0:
+                    continue
+                n = min(left, self.seq_chunk, budget)
+                budget -= n
+                sel.append(i)
+                new.append(tokens[i][done[i]:done[i] + n])
+                before.append(self.cache.length(slots[i]))
+                for j in range(n):
+                    for dst in row_of.get((i, done[i] + j), ()):
+                        wrows.append(base + j)
+                        wdst.append(dst)
+                base += n
+            if not sel:
+                break
+            pieces.append(self._pass([slots[i] for i in sel], new, before, wrows))
+            piece_rows.append(wdst)
+            for i, t in zip(sel, new):
+                done[i] += len(t)
+        if not pieces:
+            return torch.empty((0, V), dtype=torch.float32, device=self.device)
+        order = [d for rows in piece_rows for d in rows]
+        if order == list(range(n_want)):
+            return pieces[0] if len(pieces) == 1 else torch.cat(pieces, dim=0)
+        out = torch.empty((n_want, V), dtype=torch.float32, device=self.device)
+        out[torch.tensor(order, dtype=torch.long, device=self.device)] = torch.cat(pieces, dim=0)
+        return out
+
+    def _pass(self, slots, new_tokens, before, want_rows) -> torch.Tensor:
+        """One pass through the layers: reserve pages, lay the batch out, run, commit."""
+        for s, t, b in zip(slots, new_tokens, before):
+            self.cache.reserve(s, b + len(t))
+        batch = build_step_batch(slots, new_tokens, before, want_rows, self.cache.tables(slots),
+                                 self.device)
+        logits = self.model.forward(batch, self.cache)
+        for s, t in zip(slots, new_tokens):
+            self.cache.commit(s, len(t))
+        return logits

@@ -1,0 +1,94 @@
+"""What parts run on: the device, the element type of activations, scratch memory and the
+choice of kernel for a matrix product or an attention call.
+
+Parts never pick a kernel by model; they ask the runtime for "a product of these two
+matrices with this epilogue" and the runtime picks by element type and shape.
+"""
+from __future__ import annotations
+
+import torch
+
+from ..kernels import ops
+
+
+class Arena:
+    """Scratch memory for one step: a bump allocator over one buffer, reset layer by layer.
+    A request that does not fit gets a fresh, larger buffer (earlier tensors stay valid
+    because they hold their buffer); that happens during warm-up only."""
+
+    ALIGN = 256
+
+    def __init__(self, device, nbytes: int = 1 << 20):
+        self.device = device
+        self._buf = torch.empty(max(nbytes, 1 << 16), dtype=torch.uint8, device=device)
+        self._off = 0
+        self.high_water = 0
+
+    def reserve(self, nbytes: int) -> None:
+        if nbytes > self._buf.numel():
+            if self._off != 0:
+                raise RuntimeError("arena can grow only when empty")
+            self._buf = torch.empty(nbytes, dtype=torch.uint8, device=self.device)
+
+    def mark(self) -> int:
+        return self._off
+
+    def reset(self, mark: int = 0) -> None:
+        self._off = mark
+
+    def alloc(self, shape, dtype) -> torch.Tensor:
+        n = 1
+        for s in shape:
+            n *= int(s)
+        nbytes = n * torch.empty((), dtype=dtype).element_size()
+        start = -(-self._off // self.ALIGN) * self.ALIGN
+        if start + nbytes > self._buf.numel():
+            size = max(2 * self._buf.numel(), start + nbytes + (1 << 20))
+            self._buf = torch.empty(size, dtype=torch.uint8, device=self.device)
+            start = 0
+        self._off = start + nbytes
+        self.high_water = max(self.high_water, self._off)
+        return self._buf[start:start + nbytes].view(dtype).view(*shape)
+
+
+class Runtime:
+    """dtype: torch.float32 (everything in true 32-bit: CUDA-core products, 32-bit cache) or
+    torch.bfloat16 (16-bit activations, weights and cache; 32-bit residual stream, sums,
+    softmax, norms and rotation)."""
+
+    def __init__(self, device="cuda:0", dtype=torch.bfloat16, head_dims=()):
+        self.device = torch.device(device)
+        if dtype not in (torch.float32, torch.bfloat16):
+            raise ValueError(f"run dtype must be float32 or bfloat16, got {dtype}")
+        self.dtype = dtype
+        self.cache_dtype = dtype
+        self.arena = Arena(self.device)
+        self._shared: dict = {}
+        self.use_tensor_cores = dtype == torch.bfloat16
+        self.launches = 0              # kernels of this library launched through the runtime
+
+    def shared(self, key, make):
+        """One object for all parts that ask with the same key (rotation tables and the like)."""
+        if key not in self._shared:
+            self._shared[key] = make()
+        return self._shared[key]
+
+    # ---- products ----------------------------------------------------------------------
+    def matmul(self, a, w, out, epilogue=ops.EPI_STORE, w2=None):
+        """out (=, +=) a @ w.T with float32 accumulation; see kernels.ops for the epilogues."""
+        self.launches += 1
+        if self.use_tensor_cores and a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16:
+            from ..kernels import gemm_tc
+            if gemm_tc.accepts(a, w, out, epilogue, w2):
+                return gemm_tc.gemm(a, w, out, epilogue, w2, self)
+        return ops.gemm_simt(a, w, out, epilogue, w2)
+
+    # ---- attention ----------------------------------------------------------------------
+    def attention(self, q, kv, out, batch, n_heads, n_kv_heads, head_dim, scale):
+        self.launches += 1
+        if self.use_tensor_cores and q.dtype == torch.bfloat16:
+            from ..kernels import attn_tc
+            if attn_tc.accepts(q, kv, head_dim, n_heads, n_kv_heads):
+                return attn_tc.attention(q, kv, out, batch, n_heads, n_kv_heads, head_dim, scale, self)
+        return ops.attn_simple(q, kv.k, kv.v, out, batch.tok_pos, batch.tok_seq, kv.table, kv.ring,
+                               kv.page, n_heads, n_kv_heads, head_dim, kv.window, scale)

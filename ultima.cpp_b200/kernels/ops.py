@@ -1,0 +1,211 @@
+"""Python entry points of the CUDA kernels.  Each takes torch tensors on the GPU, checks
+what the kernel assumes, and launches on torch's current stream.  There is no other
+implementation behind them: on a machine without the GPU or the compiler they raise.
+"""
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_float, c_int, c_longlong, c_ulonglong, c_void_p
+
+import numpy as np
+import torch
+
+from . import build
+
+F32, BF16 = 0, 1
+EPI_STORE, EPI_ADD, EPI_SWIGLU = 0, 1, 2
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def _code(t: torch.Tensor) -> int:
+    if t.dtype == torch.float32:
+        return F32
+    if t.dtype == torch.bfloat16:
+        return BF16
+    raise KernelError(f"kernels take float32 or bfloat16 tensors, got {t.dtype}")
+
+
+def _ptr(t):
+    return 0 if t is None else t.data_ptr()
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _check(rc: int, what: str) -> None:
+    if rc == 0:
+        return
+    if rc == -1:
+        raise KernelError(f"{what}: an argument is outside what the kernel takes")
+    if rc == -2:
+        raise KernelError(f"{what}: this combination of element types is not built")
+    raise KernelError(f"{what}: CUDA error {rc} at launch")
+
+
+def _need_cuda(*ts):
+    for t in ts:
+        if t is not None and not t.is_cuda:
+            raise KernelError("kernels run on CUDA tensors only; there is no CPU path")
+
+
+_sigs_done = set()
+
+
+def _lib(source: str, defines=()):
+    lib = build.load(source, tuple(defines))
+    key = (source, tuple(defines))
+    if key not in _sigs_done:
+        _declare(lib, source)
+        _sigs_done.add(key)
+    return lib
+
+
+def _declare(lib, source: str) -> None:
+    P, I, L, F, U = c_void_p, c_int, c_longlong, c_float, c_ulonglong
+    sigs = {
+        "basic.cu": {
+            "ub_embed": [P, I, P, P, I, I, I, P, P],
+            "ub_rmsnorm": [P, P, P, P, I, I, I, F, P],
+            "ub_qk_prepare": [P, I, P, P, P, P, P, P, P, P, I, P, I, I, I, I, I, I, I, F, I, P],
+            "ub_silu_mul": [P, I, P, I, I, I, P],
+            "ub_convert": [P, I, P, I, L, P],
+            "ub_add_into": [P, P, I, L, P],
+            "ub_fill_normal": [P, I, L, U, F, F, P],
+        },
+        "gemm_simt.cu": {"ub_gemm_simt": [P, I, P, P, I, P, I, I, I, I, L, L, L, I, P]},
+        "attn_simple.cu": {"ub_attn_simple": [P, L, I, P, P, I, P, L, P, P, P, I, I, I, I, I, I, I, I, F, P]},
+        "sampling.cu": {"ub_sample": [P, L, P, I, I, P, P, P, P, P, P], "ub_sample_params_size": []},
+    }.get(source, {})
+    for name, args in sigs.items():
+        fn = getattr(lib, name)
+        fn.argtypes = args
+        fn.restype = c_int
+
+
+# ---------------------------------------------------------------------------------------
+def embed(table, ids, out, status):
+    """out[t, :] = table[ids[t], :] as float32; a bad id raises ``status`` (int32[1])."""
+    _need_cuda(table, ids, out, status)
+    T, width = out.shape
+    assert out.dtype == torch.float32 and ids.dtype == torch.int32 and out.is_contiguous()
+    assert table.is_contiguous() and table.shape[1] == width
+    _check(_lib("basic.cu").ub_embed(_ptr(table), _code(table), _ptr(ids), _ptr(out), T, width,
+                                     table.shape[0], _ptr(status), _stream()), "embed")
+
+
+def rmsnorm(x, weight, out, eps, rows=None):
+    """out[r, :] = x[rows[r] or r, :] * weight / sqrt(mean(x^2) + eps); x float32."""
+    _need_cuda(x, weight, out, rows)
+    assert x.dtype == torch.float32 and weight.dtype == torch.float32
+    assert x.is_contiguous() and out.is_contiguous() and weight.is_contiguous()
+    n, width = out.shape
+    assert x.shape[1] == width and weight.numel() == width
+    if rows is not None:
+        assert rows.dtype == torch.int32 and rows.numel() == n
+    _check(_lib("basic.cu").ub_rmsnorm(_ptr(x), _ptr(rows), _ptr(weight), _ptr(out), _code(out), n,
+                                       width, float(eps), _stream()), "rmsnorm")
+
+
+def qk_prepare(qkv, q_weight, k_weight, cos, sin, tok_pos, tok_seq, k_cache, v_cache, table,
+               ring, page, n_heads, n_kv_heads, head_dim, eps, write_kv=True):
+    """Per-head norm and rotation of q (in place) and k, and the write of k, v into the cache."""
+    _need_cuda(qkv, k_cache, v_cache, table)
+    T = qkv.shape[0]
+    assert qkv.is_contiguous() and qkv.shape[1] == (n_heads + 2 * n_kv_heads) * head_dim
+    assert table.dtype == torch.int32 and table.dim() == 2 and table.is_contiguous()
+    for v in (q_weight, k_weight, cos, sin):
+        assert v is None or (v.dtype == torch.float32 and v.is_contiguous())
+    if cos is not None:
+        assert cos.shape[1] == head_dim // 2
+    _check(_lib("basic.cu").ub_qk_prepare(
+        _ptr(qkv), _code(qkv), _ptr(q_weight), _ptr(k_weight), _ptr(cos), _ptr(sin), _ptr(tok_pos),
+        _ptr(tok_seq), _ptr(k_cache), _ptr(v_cache), _code(k_cache), _ptr(table), table.shape[1],
+        ring, page, T, n_heads, n_kv_heads, head_dim, float(eps), 1 if write_kv else 0, _stream()),
+        "qk_prepare")
+
+
+def silu_mul(gate_up, out):
+    """out[t, f] = silu(gate_up[t, f]) * gate_up[t, F + f]."""
+    _need_cuda(gate_up, out)
+    T, F = out.shape
+    assert gate_up.shape == (T, 2 * F) and gate_up.is_contiguous() and out.is_contiguous()
+    _check(_lib("basic.cu").ub_silu_mul(_ptr(gate_up), _code(gate_up), _ptr(out), _code(out), T, F,
+                                        _stream()), "silu_mul")
+
+
+def convert(src, dst):
+    _need_cuda(src, dst)
+    assert src.numel() == dst.numel() and src.is_contiguous() and dst.is_contiguous()
+    _check(_lib("basic.cu").ub_convert(_ptr(src), _code(src), _ptr(dst), _code(dst), src.numel(),
+                                       _stream()), "convert")
+
+
+def add_into(acc, src):
+    _need_cuda(acc, src)
+    assert acc.dtype == torch.float32 and acc.numel() == src.numel()
+    assert acc.is_contiguous() and src.is_contiguous()
+    _check(_lib("basic.cu").ub_add_into(_ptr(acc), _ptr(src), _code(src), acc.numel(), _stream()),
+           "add_into")
+
+
+def fill_normal(out, seed: int, shift: float, std: float):
+    _need_cuda(out)
+    assert out.is_contiguous()
+    _check(_lib("basic.cu").ub_fill_normal(_ptr(out), _code(out), out.numel(), seed & (2**64 - 1),
+                                           float(shift), float(std), _stream()), "fill_normal")
+
+
+def gemm_simt(a, w, out, epilogue=EPI_STORE, w2=None):
+    """out[t, n] (=, +=) sum_k a[t, k] w[n, k] on the CUDA cores with float32 FMA;
+    EPI_SWIGLU: out = silu(a w^T) * (a w2^T)."""
+    _need_cuda(a, w, out, w2)
+    M, K = a.shape
+    N = w.shape[0]
+    assert w.shape[1] == K and out.shape == (M, N)
+    assert a.stride(1) == 1 and w.stride(1) == 1 and out.stride(1) == 1
+    if w2 is not None:
+        assert w2.shape == w.shape and w2.dtype == w.dtype and w2.stride() == w.stride()
+    _check(_lib("gemm_simt.cu").ub_gemm_simt(
+        _ptr(a), _code(a), _ptr(w), _ptr(w2), _code(w), _ptr(out), _code(out), M, N, K,
+        a.stride(0), w.stride(0), out.stride(0), epilogue, _stream()), "gemm_simt")
+
+
+def attn_simple(q, k_cache, v_cache, out, tok_pos, tok_seq, table, ring, page, n_heads,
+                n_kv_heads, head_dim, window, scale):
+    """Attention of every token of the step over its sequence's cached keys and values."""
+    _need_cuda(q, k_cache, v_cache, out, table)
+    T = q.shape[0]
+    assert q.stride(1) == 1 and out.stride(1) == 1 and q.dtype == out.dtype
+    assert table.dtype == torch.int32 and table.dim() == 2 and table.is_contiguous()
+    _check(_lib("attn_simple.cu").ub_attn_simple(
+        _ptr(q), q.stride(0), _code(q), _ptr(k_cache), _ptr(v_cache), _code(k_cache), _ptr(out),
+        out.stride(0), _ptr(tok_pos), _ptr(tok_seq), _ptr(table), table.shape[1], ring, page, T,
+        n_heads, n_kv_heads, head_dim, int(window or 0), float(scale), _stream()), "attn_simple")
+
+
+# ---------------------------------------------------------------------------------------
+SAMPLE_DTYPE = np.dtype([
+    ("temperature", "<f4"), ("top_p", "<f4"), ("min_p", "<f4"), ("rep_penalty", "<f4"),
+    ("freq_penalty", "<f4"), ("presence_penalty", "<f4"), ("dry_multiplier", "<f4"),
+    ("dry_base", "<f4"), ("top_k", "<i4"), ("repeat_last_n", "<i4"), ("dry_last_n", "<i4"),
+    ("dry_allowed_len", "<i4"), ("n_recent", "<i4"), ("recent_offset", "<i4"), ("n_bias", "<i4"),
+    ("bias_offset", "<i4"), ("seed", "<u8"), ("counter", "<u8")])
+
+
+def sample(logits, work, params_dev, recent, bias_ids, bias_vals, out_ids):
+    """One token id for each row of float32 ``logits``; ``params_dev`` holds one record of
+    SAMPLE_DTYPE a row (as bytes on the device)."""
+    _need_cuda(logits, work, params_dev, out_ids)
+    lib = _lib("sampling.cu")
+    assert lib.ub_sample_params_size() == SAMPLE_DTYPE.itemsize
+    n, V = logits.shape
+    assert logits.dtype == torch.float32 and logits.stride(1) == 1
+    assert work is None or (work.dtype == torch.float32 and work.is_contiguous() and work.numel() >= n * V)
+    assert out_ids.dtype == torch.int32 and out_ids.numel() >= n
+    _check(lib.ub_sample(_ptr(logits), logits.stride(0), _ptr(work), n, V, _ptr(params_dev),
+                         _ptr(recent), _ptr(bias_ids), _ptr(bias_vals), _ptr(out_ids), _stream()),
+           "sample")
