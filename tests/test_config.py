@@ -1,0 +1,114 @@
+"""Configuration and registry (no GPU)."""
+import copy
+import json
+import os
+
+import pytest
+
+from conftest import TINY_A, TINY_B, TINY_C
+import ultima_b200 as u
+from ultima_b200.config import (ConfigError, Qwen3Config, config_from_dict, find_architecture,
+                                known_architectures, register_architecture, ArchitectureEntry)
+
+
+def test_reads_every_size_from_its_keys():
+    c = config_from_dict(TINY_B)
+    assert isinstance(c, Qwen3Config)
+    assert (c.vocab_size, c.hidden_size, c.intermediate_size, c.num_hidden_layers) == (1000, 96, 320, 3)
+    assert (c.num_attention_heads, c.num_key_value_heads, c.head_dim) == (8, 1, 32)
+    assert c.q_width == 256 and c.kv_width == 32 and c.q_width != c.hidden_size
+    assert c.rms_norm_eps == 1e-5 and c.rope_theta == 1e6 and not c.tie_word_embeddings
+    assert c.sliding_window is None and set(c.layer_types) == {"full_attention"}
+
+
+def test_head_dim_falls_back_to_width_over_heads():
+    d = dict(TINY_A)
+    del d["head_dim"]
+    assert config_from_dict(d).head_dim == 64 // 4
+    d["hidden_size"] = 66
+    with pytest.raises(ConfigError, match="not divisible"):
+        config_from_dict(d)
+
+
+def test_kv_heads_default_to_heads_and_must_divide():
+    d = dict(TINY_A)
+    del d["num_key_value_heads"]
+    assert config_from_dict(d).num_key_value_heads == 4
+    d["num_key_value_heads"] = 3
+    with pytest.raises(ConfigError, match="multiple"):
+        config_from_dict(d)
+
+
+@pytest.mark.parametrize("key", ["vocab_size", "hidden_size", "intermediate_size", "num_hidden_layers",
+                                 "num_attention_heads", "rope_theta", "max_position_embeddings"])
+def test_missing_required_key(key):
+    d = dict(TINY_A)
+    del d[key]
+    with pytest.raises(ConfigError, match=key):
+        config_from_dict(d)
+
+
+def test_window_needs_window_and_pattern():
+    c = config_from_dict(TINY_C)
+    assert c.sliding_window == 20
+    assert [c.window_of_layer(i) for i in range(4)] == [20, None, 20, None]
+    d = dict(TINY_C)
+    d["layer_types"] = d["layer_types"][:3]
+    with pytest.raises(ConfigError, match="layer_types"):
+        config_from_dict(d)
+    d = dict(TINY_C)
+    del d["layer_types"]
+    with pytest.raises(ConfigError, match="layer_types"):
+        config_from_dict(d)
+    d = dict(TINY_C)
+    d["sliding_window"] = None
+    with pytest.raises(ConfigError, match="sliding_window"):
+        config_from_dict(d)
+    # a window that is switched off is no window
+    d = dict(TINY_C)
+    d["use_sliding_window"] = False
+    assert config_from_dict(d).sliding_window is None
+
+
+def test_rejects_what_the_model_does_not_apply():
+    for key, val, pat in (("rope_scaling", {"rope_type": "yarn", "factor": 4.0}, "rope_scaling"),
+                          ("hidden_act", "gelu", "hidden_act"), ("attention_bias", True, "attention_bias"),
+                          ("head_dim", 15, "even")):
+        d = dict(TINY_A)
+        d[key] = val
+        with pytest.raises(ConfigError, match=pat):
+            config_from_dict(d)
+
+
+def test_round_trip_through_config_json(tmp_path):
+    for d in (TINY_A, TINY_B, TINY_C):
+        c = config_from_dict(d)
+        (tmp_path / "config.json").write_text(json.dumps(c.to_dict()))
+        assert u.config_from_dir(str(tmp_path)) == c
+
+
+def test_registry_unknown_and_unsupported_are_two_errors():
+    with pytest.raises(ConfigError, match="unknown architecture"):
+        find_architecture("NoSuchModel")
+    register_architecture(ArchitectureEntry("ToyUnsupportedLM", "toy_unsupported", False, "a reason"))
+    with pytest.raises(ConfigError, match="recognized but not runnable: a reason"):
+        find_architecture("ToyUnsupportedLM")
+    assert "Qwen3ForCausalLM" in [e.name for e in known_architectures()]
+    assert find_architecture("qwen3") is find_architecture("Qwen3ForCausalLM")
+    d = dict(TINY_A)
+    d["architectures"] = ["LlamaForCausalLM"]
+    with pytest.raises(ConfigError, match="unknown architecture"):
+        config_from_dict(d)
+
+
+def test_model_description_is_data():
+    spec = u.model_spec_for(config_from_dict(TINY_C))
+    assert len(spec.layers) == 4 and [r.layer for r in spec.runs] == [0, 1, 2, 3]
+    assert [L.mixer.get("window") for L in spec.layers] == [20, None, 20, None]
+    assert spec.layers[0].mixer.get("head_dim") == 48 and spec.layers[0].feed_forward.get("inner") == 176
+    names = {s.name: s.shape for s in spec.weight_specs()}
+    assert names["model.layers.3.self_attn.q_proj.weight"] == (6 * 48, 80)
+    assert names["model.layers.0.self_attn.k_norm.weight"] == (48,)
+    assert names["lm_head.weight"] == (777, 80)
+    tied = u.model_spec_for(config_from_dict(TINY_A))
+    assert "lm_head.weight" not in {s.name for s in tied.weight_specs()}
