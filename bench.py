@@ -1,0 +1,303 @@
+#!/usr/bin/env python3
+"""Decode and prefill throughput of the engine at Qwen3-8B layer sizes on one B200.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
+
+One JSON line on standard output.  A step is one decode step of a batch of 8 sequences whose
+prompts (2,048 random token ids each) are already in the cache; ``value`` is decoded tokens
+a second, timed on the device with CUDA events around exactly K steps.  ``e2e`` is the same
+through the Python entry point (``LLM.generate``): token ids from the host in, sampled ids
+back on the host every step.  ``prefill`` times one 2,048-token prompt; ``points`` gives
+decode at batch 1 and 64; ``roofline`` compares the bytes a decode step has to read (every
+weight once, the cache of the live sequences) with the measured copy bandwidth.
+Weights are random from a seed (there is no checkpoint offline); the step reads 15 GB of
+weights, far more than the 126 MB L2, so no flush is needed between timed steps.
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+QWEN3_8B = dict(architectures=["Qwen3ForCausalLM"], model_type="qwen3", vocab_size=151936,
+                hidden_size=4096, intermediate_size=12288, num_hidden_layers=36,
+                num_attention_heads=32, num_key_value_heads=8, head_dim=128, rms_norm_eps=1e-6,
+                rope_theta=1000000.0, max_position_embeddings=8192, tie_word_embeddings=False,
+                hidden_act="silu")
+PROMPT, CONTEXT, BATCH, PREFILL_TOKENS = 2048, 8192, 8, 2048
+
+
+def peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.isfile(p):
+        try:
+            d = json.load(open(p))
+            return {"hbm_gbs": float(d["hbm_gbs"]), "bf16_tflops": float(d["bf16_tflops"]),
+                    "bf16_tflops_sustained": float(d.get("bf16_tflops_sustained", d["bf16_tflops"])),
+                    "source": "measured"}
+        except Exception:
+            pass
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons, sampled while the timed region runs."""
+    Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self):
+        self.rows, self.proc = [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", "0", f"--query-gpu={self.Q}",
+                                          "--format=csv,noheader,nounits", "-lms", "200"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self):
+        if self.proc is not None:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except Exception:
+                pass
+        sm = [int(r[0]) for r in self.rows if r and r[0].isdigit()]
+        mx = [int(r[1]) for r in self.rows if len(r) > 1 and r[1].isdigit()]
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = sorted({n for r in self.rows if len(r) >= 7 for n, v in zip(names, r[3:7]) if v == "Active"})
+        return {"sm_mhz": int(statistics.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": reasons, "samples": len(sm)}
+
+
+def weight_bytes(engine):
+    seen, total = set(), 0
+    def add(t):
+        nonlocal total
+        if t is not None and t.data_ptr() not in seen:
+            seen.add(t.data_ptr())
+            total += t.numel() * t.element_size()
+    for L in engine.model.layers:
+        for part in (L.mixer, L.feed_forward, L.mixer_norm, L.feed_forward_norm):
+            for v in vars(part).values():
+                if hasattr(v, "data_ptr") and v.dim() >= 1 and v.is_cuda and v.numel() > 64 and not str(v.dtype).endswith("int32"):
+                    if getattr(part, "position", None) is None or True:
+                        add(v)
+    add(engine.model.head.weight)
+    add(engine.model.final_norm.weight)
+    return total
+
+
+def kv_bytes_per_token(cfg, dtype_bytes):
+    return 2 * cfg.num_hidden_layers * cfg.num_key_value_heads * cfg.head_dim * dtype_bytes
+
+
+def prefill_flops(cfg, T):
+    H, Q, KV, F, V, L = (cfg.hidden_size, cfg.q_width, cfg.kv_width, cfg.intermediate_size,
+                         cfg.vocab_size, cfg.num_hidden_layers)
+    linear = 2 * T * L * (H * (Q + 2 * KV) + Q * H + 3 * H * F)
+    attn = L * 4 * cfg.num_attention_heads * cfg.head_dim * (T * (T + 1) // 2)
+    return linear + attn + 2 * V * H
+
+
+def fill_cache(engine, slots, n_tokens):
+    """Put ``n_tokens`` positions of random keys and values into each slot without running the
+    model (what they hold does not change a decode step's time)."""
+    from ultima_b200.kernels import ops
+    for s in slots:
+        engine.cache.reserve(s, n_tokens)
+        engine.cache.commit(s, n_tokens)
+
+
+def timed_decode(engine, sampler, batch, steps, warmup, rng, real_prefill):
+    import torch
+    from ultima_b200.sampling import SamplingParams
+    V = engine.spec.vocab_size
+    slots = engine.open(batch)
+    if real_prefill:
+        prompts = [rng.integers(0, V, size=PROMPT).tolist() for _ in range(batch)]
+        for i in range(batch):             # one prompt a step keeps scratch memory small
+            engine.step([slots[i]], [prompts[i]], [[]])
+    else:
+        fill_cache(engine, slots, PROMPT)
+    toks = rng.integers(0, V, size=(warmup + steps, batch))
+    params = [SamplingParams()] * batch
+    out_ids = torch.empty(batch, dtype=torch.int32, device=engine.device)
+    prm = sampler_params(sampler, params, engine.device)
+
+    def one(i):
+        logits = engine.step(slots, [[int(t)] for t in toks[i]], None)
+        sampler_launch(logits, prm, out_ids)
+    for i in range(warmup):
+        one(i)
+    torch.cuda.synchronize()
+    l0 = engine.rt.launches
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(warmup, warmup + steps):
+        one(i)
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1)
+    launches = engine.rt.launches - l0 + steps
+    ctx = engine.length(slots[0])
+    engine.close(slots)
+    return ms, launches, ctx
+
+
+def sampler_params(sampler, params, device):
+    import numpy as np
+    import torch
+    from ultima_b200.kernels import ops
+    rec = np.zeros(len(params), dtype=ops.SAMPLE_DTYPE)
+    rec["temperature"] = 0.0
+    rec["rep_penalty"] = 1.0
+    rec["top_p"] = 1.0
+    return torch.from_numpy(rec.view(np.uint8).reshape(-1)).to(device)
+
+
+def sampler_launch(logits, prm, out_ids):
+    from ultima_b200.kernels import ops
+    ops.sample(logits, None, prm, None, None, None, out_ids)
+
+
+def run_ours(args):
+    import numpy as np
+    import torch
+    import ultima_b200 as u
+    from ultima_b200.engine import Engine
+    from ultima_b200.engine.generate import LoopStats, generate
+    from ultima_b200.sampling import Sampler, SamplingParams
+    from ultima_b200.weights import random_tensors_on_device
+
+    pk = peaks()
+    d = dict(QWEN3_8B)
+    layers_full = d["num_hidden_layers"]
+    if args.layers:
+        d["num_hidden_layers"] = args.layers
+    cfg = u.config_from_dict(d)
+    dev = torch.device("cuda:0")
+    torch.cuda.set_device(dev)
+    spec = u.model_spec_for(cfg)
+    t0 = time.time()
+    tensors = random_tensors_on_device(spec.weight_specs(), 0, torch.bfloat16, dev)
+    # the cache holds the largest point: 64 sequences of a 2,048-token prompt plus the steps
+    per_seq = -(-(PROMPT + args.warmup + args.steps + 64) // 64) * 64
+    engine = Engine(spec, tensors, dtype="bfloat16", max_tokens=64 * per_seq, max_seqs=64,
+                    max_step_tokens=PREFILL_TOKENS, max_context=CONTEXT)
+    del tensors
+    sampler = Sampler(dev, cfg.vocab_size)
+    rng = np.random.default_rng(0)
+    engine.warm_up()
+    print(f"[bench] model ready in {time.time() - t0:.1f} s", file=sys.stderr, flush=True)
+
+    # prefill of one 2,048-token prompt
+    prompt = rng.integers(0, cfg.vocab_size, size=PREFILL_TOKENS).tolist()
+    pre_ms = []
+    for i in range(2 + 3):
+        s = engine.open(1)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        e0.record()
+        engine.step(s, [prompt], None)
+        e1.record()
+        torch.cuda.synchronize()
+        engine.close(s)
+        if i >= 2:
+            pre_ms.append(e0.elapsed_time(e1))
+    pms = statistics.median(pre_ms)
+    pf = prefill_flops(cfg, PREFILL_TOKENS)
+    prefill = {"value": round(PREFILL_TOKENS / pms * 1e3, 1), "tokens": PREFILL_TOKENS, "ms": round(pms, 3),
+               "frac": round(pf / (pms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)}
+    print(f"[bench] prefill {prefill}", file=sys.stderr, flush=True)
+
+    clocks = ClockSampler()
+    clocks.start()
+    ms, launches, ctx = timed_decode(engine, sampler, BATCH, args.steps, args.warmup, rng, real_prefill=True)
+    clk = clocks.stop()
+    value = BATCH * args.steps / ms * 1e3
+    wbytes = weight_bytes(engine)
+    step_bytes = wbytes + BATCH * (ctx - args.steps / 2) * kv_bytes_per_token(cfg, 2)
+    achieved = step_bytes / (ms / args.steps * 1e-3) / 1e9
+    print(f"[bench] decode b{BATCH}: {value:.1f} tok/s", file=sys.stderr, flush=True)
+
+    points = {}
+    for b in (1, 64):
+        pm, _, _ = timed_decode(engine, sampler, b, args.steps, args.warmup, rng, real_prefill=False)
+        points[f"decode_b{b}"] = round(b * args.steps / pm * 1e3, 1)
+        print(f"[bench] decode b{b}: {points[f'decode_b{b}']} tok/s", file=sys.stderr, flush=True)
+
+    # end to end through the generation loop: host token ids in, sampled ids out, every step
+    prompts = [rng.integers(0, cfg.vocab_size, size=PROMPT).tolist() for _ in range(BATCH)]
+    stats = LoopStats()
+    n_new = args.warmup + args.steps
+    generate(engine, sampler.sample, prompts, SamplingParams(), n_new, (), max_batch=BATCH, stats=stats)
+    stats = LoopStats()
+    generate(engine, sampler.sample, prompts, SamplingParams(), n_new, (), max_batch=BATCH, stats=stats)
+    e2e_val = BATCH * (n_new - 1) / stats.decode_s
+    h2d = 4 * (4 * (-(-BATCH // 4) * 4) + 4 * (-(-(BATCH + 1) // 4) * 4) // 4 + BATCH * engine.cache.kv_groups[0].pages_per_seq)
+    e2e = {"value": round(e2e_val, 1), "unit": "tokens/s", "h2d_bytes_per_step": int(h2d),
+           "d2h_bytes_per_step": 4 * BATCH}
+
+    out = {
+        "metric": "decode tokens/s, Qwen3-8B sizes, bf16, batch 8, 2048-token prompts",
+        "value": round(value, 1), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": round(ms / args.steps, 4), "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+        "data": "synthetic: random weights from a seed, random token ids",
+        "config": {"model": "Qwen3-8B sizes", "layers": cfg.num_hidden_layers, "layers_full": layers_full,
+                   "hidden": cfg.hidden_size, "heads": cfg.num_attention_heads,
+                   "kv_heads": cfg.num_key_value_heads, "head_dim": cfg.head_dim,
+                   "intermediate": cfg.intermediate_size, "vocab": cfg.vocab_size,
+                   "global_batch": BATCH, "seq_len": CONTEXT, "prompt_len": PROMPT, "decode_context": int(ctx),
+                   "parallelism": "single GPU", "l2": "inputs larger than L2 (15 GB of weights a step)",
+                   "peaks": pk["source"]},
+        "e2e": e2e, "gpu_launches": int(launches), "clocks": clk, "prefill": prefill,
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
+                     "frac": round(achieved / pk["hbm_gbs"], 4)},
+        "points": points, "impl": "ours",
+    }
+    print(json.dumps(out), flush=True)
+    return 0
+
+
+def run_reference(args):
+    why = ("the reference is a CPU-only C++/CMake program with no Python package, no CUDA code and a "
+           "Windows-only model loader; the offline pip install of it fails (no setup.py or pyproject.toml)")
+    print(json.dumps({"impl": "reference", "unavailable": why}), flush=True)
+    return 0
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--warmup", type=int, default=4)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--layers", type=int, default=0, help="fewer layers than the configuration (named in config)")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        return run_reference(args)
+    if args.gpus != 1:
+        print(f"bench.py: this library runs on one GPU; --gpus {args.gpus} is not supported")
+        return 2
+    if args.warmup < 3:
+        args.warmup = 3
+    return run_ours(args)
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -1,0 +1,246 @@
+"""Each kernel alone against a plain PyTorch float64 restatement of the same operation, at
+sizes other than the tiny models' (odd widths, head sizes in steps of 16, groups of 1, 3, 8)."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda:0"
+
+
+def _ops():
+    from ultima_b200.kernels import ops
+    return ops
+
+
+def rel_err(got, ref):
+    """Per-element error relative to max(1, |ref|), as the reference's tests measure
+    (tests/unit/test_kernels_correctness.cpp:40-48)."""
+    got, ref = got.double().cpu(), ref.double().cpu()
+    return float(((got - ref).abs() / ref.abs().clamp(min=1.0)).max())
+
+
+@pytest.mark.parametrize("table_dtype", [torch.float32, torch.bfloat16])
+def test_embed(table_dtype):
+    ops = _ops()
+    g = torch.Generator().manual_seed(0)
+    table = torch.randn(1003, 131, generator=g).to(table_dtype).to(DEV)
+    ids = torch.tensor([0, 1002, 5, 5, 77], dtype=torch.int32, device=DEV)
+    out = torch.empty(5, 131, dtype=torch.float32, device=DEV)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    ops.embed(table, ids, out, status)
+    assert torch.equal(out, table[ids.long()].float()) and int(status) == 0
+    bad = torch.tensor([3, 1003], dtype=torch.int32, device=DEV)
+    ops.embed(table, bad, out[:2], status)
+    assert int(status) == 1 and float(out[1].abs().sum()) == 0.0
+
+
+@pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("width", [131, 896, 4100])
+def test_rmsnorm(width, out_dtype):
+    ops = _ops()
+    g = torch.Generator().manual_seed(width)
+    x = (torch.randn(7, width, generator=g) * 3).to(DEV)
+    w = (1 + 0.1 * torch.randn(width, generator=g)).to(DEV)
+    out = torch.empty(7, width, dtype=out_dtype, device=DEV)
+    ops.rmsnorm(x, w, out, 1e-5)
+    xd = x.double()
+    ref = xd * w.double() / torch.sqrt((xd * xd).mean(-1, keepdim=True) + 1e-5)
+    assert rel_err(out, ref) <= (2e-6 if out_dtype == torch.float32 else 2 ** -8)
+    rows = torch.tensor([6, 0, 3], dtype=torch.int32, device=DEV)
+    out2 = torch.empty(3, width, dtype=out_dtype, device=DEV)
+    ops.rmsnorm(x, w, out2, 1e-5, rows)
+    assert torch.equal(out2, out[rows.long()])
+
+
+@pytest.mark.parametrize("dt", [(torch.float32, torch.float32, torch.float32),
+                                (torch.bfloat16, torch.bfloat16, torch.bfloat16),
+                                (torch.bfloat16, torch.float32, torch.float32),
+                                (torch.bfloat16, torch.bfloat16, torch.float32)])
+@pytest.mark.parametrize("shape", [(1, 517, 131), (5, 64, 200), (70, 333, 129), (130, 96, 1000)])
+def test_gemm_simt(shape, dt):
+    ops = _ops()
+    M, K, N = shape
+    ta, tw, to = dt
+    g = torch.Generator().manual_seed(M * 7 + N)
+    a = torch.randn(M, K, generator=g).to(ta).to(DEV)
+    w = (torch.randn(N, K, generator=g) * 0.05).to(tw).to(DEV)
+    w2 = (torch.randn(N, K, generator=g) * 0.05).to(tw).to(DEV)
+    ref = a.double() @ w.double().T
+    out = torch.empty(M, N, dtype=to, device=DEV)
+    ops.gemm_simt(a, w, out)
+    tol = 1e-5 if to == torch.float32 else 2 ** -8
+    assert rel_err(out, ref) <= tol
+    if to == torch.float32:
+        acc = torch.randn(M, N, generator=g).to(DEV)
+        before = acc.clone()
+        ops.gemm_simt(a, w, acc, ops.EPI_ADD)
+        assert rel_err(acc, before.double() + ref) <= 1e-5
+    ref2 = a.double() @ w2.double().T
+    ops.gemm_simt(a, w, out, ops.EPI_SWIGLU, w2=w2)
+    assert rel_err(out, ref / (1 + torch.exp(-ref)) * ref2) <= tol
+    # a view with a row stride (columns of a wider matrix), as the q part of [q | k | v]
+    wide = torch.randn(M, K + 24, generator=g).to(ta).to(DEV)
+    ops.gemm_simt(wide[:, 8:8 + K], w, out)
+    assert rel_err(out, wide[:, 8:8 + K].double() @ w.double().T) <= tol
+
+
+def _paged(n_seqs, lens, nkv, hd, dtype, ring_pages, seed, page=64):
+    """Random K, V for sequences of the given lengths, stored in shuffled pages (ring_pages
+    pages a sequence, wrapped).  Returns caches, table and the dense tensors."""
+    g = torch.Generator().manual_seed(seed)
+    n_pages = n_seqs * ring_pages + 3
+    perm = torch.randperm(n_pages, generator=g)[:n_seqs * ring_pages].reshape(n_seqs, ring_pages)
+    kc = torch.full((n_pages, nkv, page, hd), float("nan"), dtype=dtype)
+    vc = torch.full((n_pages, nkv, page, hd), float("nan"), dtype=dtype)
+    dense = []
+    for s, n in enumerate(lens):
+        k = torch.randn(n, nkv, hd, generator=g).to(dtype)
+        v = torch.randn(n, nkv, hd, generator=g).to(dtype)
+        dense.append((k, v))
+        for p in range(n):
+            li = p % (ring_pages * page)
+            kc[perm[s, li // page], :, li % page] = k[p]
+            vc[perm[s, li // page], :, li % page] = v[p]
+    return kc.to(DEV), vc.to(DEV), perm.to(torch.int32).to(DEV), dense
+
+
+def _attn_ref(q, k, v, pos, window, scale):
+    """q [nh, hd] at position pos over k, v [n, nkv, hd] (float64)."""
+    nh, nkv = q.shape[0], k.shape[1]
+    lo = max(0, pos + 1 - window) if window else 0
+    out = torch.zeros_like(q)
+    for h in range(nh):
+        g = h // (nh // nkv)
+        s = (k[lo:pos + 1, g] @ q[h]) * scale
+        out[h] = torch.softmax(s, 0) @ v[lo:pos + 1, g]
+    return out
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("cfg", [dict(nh=6, nkv=2, hd=48, window=0), dict(nh=8, nkv=1, hd=16, window=0),
+                                 dict(nh=4, nkv=4, hd=80, window=37), dict(nh=3, nkv=3, hd=256, window=0)])
+def test_attn_simple(cfg, dtype):
+    ops = _ops()
+    nh, nkv, hd, window = cfg["nh"], cfg["nkv"], cfg["hd"], cfg["window"]
+    lens = [1, 70, 129, 600]
+    ring_pages = 10
+    kc, vc, table, dense = _paged(len(lens), lens, nkv, hd, dtype, ring_pages, seed=hd)
+    # queries: for each sequence its last token and, for longer ones, two earlier tokens
+    toks = [(s, p) for s, n in enumerate(lens) for p in sorted({n - 1, n // 2, 0})]
+    g = torch.Generator().manual_seed(1)
+    q = torch.randn(len(toks), nh * hd + 8, generator=g).to(dtype).to(DEV)[:, :nh * hd]   # strided rows
+    out = torch.empty(len(toks), nh * hd, dtype=dtype, device=DEV)
+    pos = torch.tensor([p for _, p in toks], dtype=torch.int32, device=DEV)
+    seq = torch.tensor([s for s, _ in toks], dtype=torch.int32, device=DEV)
+    scale = 1 / math.sqrt(hd)
+    ops.attn_simple(q, kc, vc, out, pos, seq, table, ring_pages * 64, 64, nh, nkv, hd, window, scale)
+    for i, (s, p) in enumerate(toks):
+        k, v = dense[s]
+        ref = _attn_ref(q[i].double().cpu().view(nh, hd), k.double(), v.double(), p, window, scale)
+        err = rel_err(out[i].view(nh, hd), ref)
+        assert err <= (2e-5 if dtype == torch.float32 else 2 ** -7), (i, s, p, err)
+
+
+def test_attention_finds_a_far_key_and_respects_the_window_edge():
+    """One key among hundreds is made to stand out; with a window that just excludes it the
+    output must not see it, with one position more it must."""
+    ops = _ops()
+    nh, nkv, hd, n = 2, 1, 32, 700
+    g = torch.Generator().manual_seed(3)
+    k = torch.randn(n, nkv, hd, generator=g) * 0.1
+    v = torch.randn(n, nkv, hd, generator=g) * 0.1
+    q = torch.randn(1, nh * hd, generator=g) * 0.1
+    far = 213
+    k[far, 0] = q[0, :hd] * 400.0            # a huge score for head 0 at position 213
+    v[far, 0] = 5.0
+    ring_pages = 11
+    kc = torch.full((ring_pages, nkv, 64, hd), float("nan"))
+    vc = torch.full((ring_pages, nkv, 64, hd), float("nan"))
+    for p in range(n):
+        kc[p // 64, :, p % 64], vc[p // 64, :, p % 64] = k[p], v[p]
+    table = torch.arange(ring_pages, dtype=torch.int32).view(1, -1).to(DEV)
+    pos = torch.tensor([n - 1], dtype=torch.int32, device=DEV)
+    seq = torch.zeros(1, dtype=torch.int32, device=DEV)
+    out = torch.empty(1, nh * hd, device=DEV)
+    args = (q.to(DEV), kc.to(DEV), vc.to(DEV), out, pos, seq, table, ring_pages * 64, 64, nh, nkv, hd)
+    ops.attn_simple(*args, 0, 1 / math.sqrt(hd))
+    assert float(out[0, :hd].min()) > 4.9                      # head 0 is all that one value
+    ops.attn_simple(*args, n - 1 - far, 1 / math.sqrt(hd))     # window ends one short of it
+    assert float(out[0, :hd].abs().max()) < 1.0
+    ops.attn_simple(*args, n - far, 1 / math.sqrt(hd))         # window just reaches it
+    assert float(out[0, :hd].min()) > 4.9
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("cfg", [dict(nh=6, nkv=2, hd=48), dict(nh=8, nkv=1, hd=16), dict(nh=2, nkv=2, hd=112)])
+def test_qk_prepare_norm_rotation_and_cache_write(cfg, dtype):
+    ops = _ops()
+    nh, nkv, hd = cfg["nh"], cfg["nkv"], cfg["hd"]
+    half, eps, theta = hd // 2, 1e-5, 1e4
+    toks = [(0, 0), (0, 1), (1, 63), (1, 64), (2, 150), (2, 151)]          # (sequence, position)
+    T = len(toks)
+    g = torch.Generator().manual_seed(hd)
+    qkv = torch.randn(T, (nh + 2 * nkv) * hd, generator=g).to(dtype)
+    qw, kw = 1 + 0.1 * torch.randn(hd, generator=g), 1 + 0.1 * torch.randn(hd, generator=g)
+    inv = 1.0 / theta ** (2.0 * torch.arange(half, dtype=torch.float64) / hd)
+    ang = torch.arange(200, dtype=torch.float64)[:, None] * inv[None]
+    cos, sin = torch.cos(ang).float(), torch.sin(ang).float()
+    ring_pages, n_pages = 2, 8                                             # ring of 128 positions
+    table = torch.tensor([[5, 1], [0, 7], [3, 2]], dtype=torch.int32)
+    kc = torch.zeros(n_pages, nkv, 64, hd, dtype=dtype, device=DEV)
+    vc = torch.zeros(n_pages, nkv, 64, hd, dtype=dtype, device=DEV)
+    dev_qkv = qkv.clone().to(DEV)
+    ops.qk_prepare(dev_qkv, qw.to(DEV), kw.to(DEV), cos.to(DEV), sin.to(DEV),
+                   torch.tensor([p for _, p in toks], dtype=torch.int32, device=DEV),
+                   torch.tensor([s for s, _ in toks], dtype=torch.int32, device=DEV),
+                   kc, vc, table.to(DEV), ring_pages * 64, 64, nh, nkv, hd, eps)
+
+    def prep(x, w, p):          # x [heads, hd] float64
+        x = x * w.double() / torch.sqrt((x * x).mean(-1, keepdim=True) + eps)
+        a, b = x[:, :half], x[:, half:]
+        c, s = torch.cos(ang[p])[None], torch.sin(ang[p])[None]
+        return torch.cat([a * c - b * s, a * s + b * c], -1)
+    tol = 1e-5 if dtype == torch.float32 else 2 ** -7
+    for t, (s, p) in enumerate(toks):
+        row = qkv[t].double()
+        q_ref = prep(row[:nh * hd].view(nh, hd), qw, p)
+        k_ref = prep(row[nh * hd:(nh + nkv) * hd].view(nkv, hd), kw, p)
+        v_ref = row[(nh + nkv) * hd:].view(nkv, hd)
+        assert rel_err(dev_qkv[t, :nh * hd].view(nh, hd), q_ref) <= tol
+        li = p % (ring_pages * 64)
+        pg = int(table[s, li // 64])
+        assert rel_err(kc[pg, :, li % 64], k_ref) <= tol, (t, s, p)
+        assert rel_err(vc[pg, :, li % 64], v_ref) <= (0 if dtype == torch.float32 else tol)
+    # a run that reads another run's cache writes nothing
+    kc2, vc2 = torch.zeros_like(kc), torch.zeros_like(vc)
+    ops.qk_prepare(qkv.clone().to(DEV), qw.to(DEV), kw.to(DEV), cos.to(DEV), sin.to(DEV),
+                   torch.tensor([p for _, p in toks], dtype=torch.int32, device=DEV),
+                   torch.tensor([s for s, _ in toks], dtype=torch.int32, device=DEV),
+                   kc2, vc2, table.to(DEV), ring_pages * 64, 64, nh, nkv, hd, eps, write_kv=False)
+    assert float(kc2.abs().sum()) == 0 and float(vc2.abs().sum()) == 0
+
+
+def test_silu_mul_convert_add_fill():
+    ops = _ops()
+    g = torch.Generator().manual_seed(9)
+    gu = torch.randn(5, 2 * 177, generator=g).to(DEV)
+    out = torch.empty(5, 177, device=DEV)
+    ops.silu_mul(gu, out)
+    gd = gu.double()
+    assert rel_err(out, gd[:, :177] / (1 + torch.exp(-gd[:, :177])) * gd[:, 177:]) <= 1e-6
+    b = torch.empty(5, 2 * 177, dtype=torch.bfloat16, device=DEV)
+    ops.convert(gu, b)
+    assert torch.equal(b, gu.to(torch.bfloat16))
+    acc = torch.ones(5, 2 * 177, device=DEV)
+    ops.add_into(acc, b)
+    assert torch.equal(acc, 1 + b.float())
+    big = torch.empty(1 << 20, device=DEV)
+    ops.fill_normal(big, 1234, 1.0, 0.05)
+    assert abs(float(big.mean()) - 1.0) < 1e-3 and abs(float(big.std()) - 0.05) < 1e-3
+    again = torch.empty(1 << 20, device=DEV)
+    ops.fill_normal(again, 1234, 1.0, 0.05)
+    assert torch.equal(big, again)

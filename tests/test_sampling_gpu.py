@@ -1,0 +1,148 @@
+"""The sampling kernel against a plain restatement of the same ladder on the host."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def _sampler(V):
+    from ultima_b200.sampling import Sampler
+    return Sampler(DEV, V)
+
+
+def host_ladder(logits, p, recent):
+    """The steps of src/sampler/sampler.cpp:230-277 on a float64 copy; returns the kept
+    probabilities (zeros for masked entries), or the argmax for temperature <= 0."""
+    x = np.array(logits, dtype=np.float64)
+    V = len(x)
+    for k, b in p.logit_bias.items():
+        if 0 <= k < V:
+            x[k] += b
+    def counts(win):
+        seg = recent[-win:] if win > 0 else []
+        c = {}
+        for t in seg:
+            c[t] = c.get(t, 0) + 1
+        return c, len(seg)
+    if p.rep_penalty != 1.0 and p.repeat_last_n > 0:
+        for t in counts(p.repeat_last_n)[0]:
+            if 0 <= t < V:
+                x[t] = x[t] / p.rep_penalty if x[t] > 0 else x[t] * p.rep_penalty
+    if p.dry_multiplier > 0 and p.dry_last_n > 0:
+        c, n = counts(p.dry_last_n)
+        if n >= 2:
+            for t, k in c.items():
+                if k > p.dry_allowed_len and 0 <= t < V:
+                    x[t] -= p.dry_multiplier * p.dry_base ** (k - p.dry_allowed_len)
+    if p.frequency_penalty != 0 or p.presence_penalty != 0:
+        for t, k in counts(max(p.repeat_last_n, p.dry_last_n))[0].items():
+            if 0 <= t < V:
+                x[t] -= k * p.frequency_penalty + p.presence_penalty
+    if p.temperature <= 0:
+        return int(np.argmax(x)), x
+    x = x / p.temperature
+    keep = np.ones(V, dtype=bool)
+    if 0 < p.top_k < V:
+        kth = np.sort(x)[-p.top_k]
+        keep &= x >= kth
+    def probs():
+        e = np.where(keep, np.exp(x - x[keep].max()), 0.0)
+        return e / e.sum()
+    if 0 < p.top_p < 1:
+        pr = probs()
+        order = np.argsort(-pr, kind="stable")
+        cum = np.cumsum(pr[order])
+        cutoff = int(np.searchsorted(cum, p.top_p - 1e-12)) + 1
+        thr = pr[order[cutoff - 1]]
+        keep &= pr >= thr
+    if p.min_p > 0:
+        pr = probs()
+        keep &= pr >= p.min_p * pr.max()
+    return probs(), x
+
+
+def test_greedy_takes_the_first_maximum():
+    V = 1000
+    s = _sampler(V)
+    from ultima_b200.sampling import SamplingParams
+    x = torch.zeros(3, V)
+    x[0, [17, 400, 999]] = 2.0
+    x[1, 999] = 1.0
+    x[2] = -5.0
+    got = s.sample(x.to(DEV), [SamplingParams()] * 3, [1, 2, 3], [0, 0, 0])
+    assert got == [17, 999, 0]
+
+
+def test_temperature_draw_follows_the_inverse_cdf_and_its_stream():
+    from ultima_b200.sampling import SamplingParams, uniform_of
+    from ultima_b200.sampling.sampler import stream_seed
+    V = 777
+    s = _sampler(V)
+    g = torch.Generator().manual_seed(0)
+    logits = torch.randn(4, V, generator=g) * 2
+    p = SamplingParams(temperature=0.8)
+    streams = [stream_seed(11, i) for i in range(4)]
+    for counter in range(6):
+        got = s.sample(logits.to(DEV), [p] * 4, streams, [counter] * 4)
+        for r in range(4):
+            pr, _ = host_ladder(logits[r].numpy(), p, [])
+            cdf = np.cumsum(pr)
+            u = uniform_of(streams[r], counter)
+            lo = cdf[got[r] - 1] if got[r] > 0 else 0.0
+            assert lo - 1e-5 <= u <= cdf[got[r]] + 1e-5, (r, counter, got[r], u, lo, cdf[got[r]])
+    # same stream and counter: same token, whatever the batch around it
+    alone = s.sample(logits[2:3].to(DEV), [p], streams[2:3], [3])
+    batch = s.sample(logits.to(DEV), [p] * 4, streams, [3] * 4)
+    assert alone[0] == batch[2]
+    # the draws follow the distribution: sharp logits, many counters
+    sharp = torch.tensor([[0.0, math.log(3.0), -30.0, math.log(6.0)]]).repeat(2000, 1)
+    ids = _sampler(4).sample(sharp.to(DEV), [SamplingParams(temperature=1.0)] * 2000, [5] * 2000, list(range(2000)))
+    freq = np.bincount(ids, minlength=4) / 2000.0
+    assert np.allclose(freq, [0.1, 0.3, 0.0, 0.6], atol=0.04)
+
+
+@pytest.mark.parametrize("case", ["top_k", "top_p", "min_p", "all"])
+def test_cuts_keep_the_same_set_as_the_host(case):
+    from ultima_b200.sampling import SamplingParams
+    V = 5003
+    s = _sampler(V)
+    g = torch.Generator().manual_seed(5)
+    logits = torch.randn(1, V, generator=g) * 3
+    p = {"top_k": SamplingParams(temperature=0.7, top_k=12),
+         "top_p": SamplingParams(temperature=1.3, top_p=0.6),
+         "min_p": SamplingParams(temperature=1.0, min_p=0.2),
+         "all": SamplingParams(temperature=0.9, top_k=40, top_p=0.9, min_p=0.05)}[case]
+    pr, _ = host_ladder(logits[0].numpy(), p, [])
+    kept = set(np.nonzero(pr)[0].tolist())
+    assert 1 <= len(kept) < 200
+    n = 400
+    ids = s.sample(logits.repeat(n, 1).to(DEV), [p] * n, [9] * n, list(range(n)))
+    assert set(ids) <= kept, sorted(set(ids) - kept)
+    if len(kept) <= 12:
+        assert set(ids) == kept            # with 400 draws every kept token of a small set appears
+
+
+def test_penalties_and_bias_change_the_greedy_choice():
+    from ultima_b200.sampling import SamplingParams
+    V = 300
+    s = _sampler(V)
+    x = torch.zeros(1, V)
+    x[0, 10], x[0, 20], x[0, 30] = 3.0, 2.9, 2.5
+    assert s.sample(x.to(DEV), [SamplingParams()], [1], [0], [[]]) == [10]
+    rep = SamplingParams(rep_penalty=1.2, repeat_last_n=8)
+    assert s.sample(x.to(DEV), [rep], [1], [3], [[10, 10, 5]]) == [20]            # 3.0/1.2 < 2.9
+    assert s.sample(x.to(DEV), [SamplingParams(rep_penalty=1.2, repeat_last_n=1)], [1], [3], [[10, 5]]) == [10]
+    bias = SamplingParams(logit_bias={30: 1.0, 999: 5.0})
+    assert s.sample(x.to(DEV), [bias], [1], [0], [[]]) == [30]
+    fp = SamplingParams(frequency_penalty=0.3, presence_penalty=0.1, repeat_last_n=16)
+    assert s.sample(x.to(DEV), [fp], [1], [2], [[10, 10]]) == [20]               # 3.0 - 0.6 - 0.1 < 2.9
+    dry = SamplingParams(dry_multiplier=0.8, dry_base=1.75, dry_allowed_len=2, dry_last_n=32)
+    assert s.sample(x.to(DEV), [dry], [1], [3], [[10, 10, 7]]) == [10]           # two repeats are allowed
+    assert s.sample(x.to(DEV), [dry], [1], [4], [[10, 10, 10, 7]]) == [20]       # three are not
+    for p, rec in ((rep, [10, 10, 5]), (fp, [10, 10]), (dry, [10, 10, 10, 7])):
+        want, _ = host_ladder(x[0].numpy(), p, rec)
+        assert s.sample(x.to(DEV), [p], [1], [len(rec)], [rec]) == [want]

@@ -15,12 +15,13 @@ __version__ = "0.1.0"
 
 def __getattr__(name):
     # the engine pulls in torch.cuda and the kernels; load it on first use
-    if name in ("Engine", "StepError", "engine"):
-        from . import engine as _e
-        return _e if name == "engine" else getattr(_e, name)
-    if name in ("LLM", "SamplingParams", "generate", "sampling"):
-        from . import sampling as _s
-        from .engine import generate as _g
-        return {"LLM": _g.LLM, "SamplingParams": _s.SamplingParams, "generate": _g,
-                "sampling": _s}[name]
-    raise AttributeError(name)
+    import importlib
+    if name in ("engine", "sampling", "kernels", "cli"):
+        return importlib.import_module(f"{__name__}.{name}")
+    if name in ("Engine", "StepError"):
+        return getattr(importlib.import_module(f"{__name__}.engine"), name)
+    if name in ("LLM", "Generation", "generate"):
+        return getattr(importlib.import_module(f"{__name__}.engine.generate"), name)
+    if name in ("SamplingParams", "Sampler"):
+        return getattr(importlib.import_module(f"{__name__}.sampling"), name)
+    raise AttributeError(f"module '{__name__}' has no attribute '{name}'")

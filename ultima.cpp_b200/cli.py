@@ -1,0 +1,152 @@
+"""The command line, in the manner of the reference's ``ultima`` program
+(apps/ultima-cli/main.cpp:36-63 usage, :554-700 ``run``, :360-370 ``archs``): the same command
+and option names where it has them.  Prompts are token ids, since the library starts at a
+request's tokens: ``--prompt "1,2,3"``; several prompts are separated by ``;`` and run as a batch.
+
+  ultima --version | --help
+  ultima archs                               list known architectures and their status
+  ultima archinfo <model_dir>                configuration and tensors the model asks for
+  ultima random <model_dir> --config C.json [--seed N] [--dtype bfloat16|float32]
+                                             write config.json and model.safetensors
+  ultima run <model_dir> [--prompt IDS] [--n-predict N] [--n-ctx N] [--temp X] [--seed N]
+             [--show-tokens] [--dtype bfloat16|float32] [--top-k K] [--top-p P] [--min-p P]
+             [--repeat-penalty R] [--repeat-last-n N] [--stop-ids a,b] [--n-threads N]
+  ultima replay ...                          same as bin/trace_run
+"""
+from __future__ import annotations
+
+import json
+import sys
+import time
+
+USAGE = __doc__
+
+
+def _ids(text: str) -> list:
+    return [[int(x) for x in part.replace(",", " ").split()] for part in text.split(";") if part.strip()]
+
+
+def cmd_archs() -> int:
+    from .config import known_architectures
+    from . import arch  # noqa: F401
+    for e in known_architectures():
+        print(f"{e.name:24s} {e.model_type:12s} {'supported' if e.supported else 'unsupported':12s} {e.notes}")
+    return 0
+
+
+def cmd_archinfo(argv) -> int:
+    if not argv:
+        print("ultima archinfo: missing model folder", file=sys.stderr)
+        return 2
+    from . import config_from_dir, model_spec_for
+    cfg = config_from_dir(argv[0])
+    print(json.dumps(cfg.to_dict(), indent=1))
+    spec = model_spec_for(cfg)
+    total = 0
+    for s in spec.weight_specs():
+        n = 1
+        for d in s.shape:
+            n *= d
+        total += n
+        print(f"{s.name:56s} {list(s.shape)}")
+    print(f"{total} parameters; runs: {[r.layer for r in spec.runs]}")
+    return 0
+
+
+def cmd_random(argv) -> int:
+    import argparse
+    ap = argparse.ArgumentParser(prog="ultima random")
+    ap.add_argument("model_dir")
+    ap.add_argument("--config", required=True)
+    ap.add_argument("--seed", type=int, default=0)
+    ap.add_argument("--dtype", default=None, choices=["bfloat16", "float32"])
+    a = ap.parse_args(argv)
+    from . import config_from_dict, write_random_model
+    with open(a.config) as f:
+        cfg = config_from_dict(json.load(f))
+    write_random_model(a.model_dir, cfg, a.seed, a.dtype)
+    print(a.model_dir)
+    return 0
+
+
+def cmd_run(argv) -> int:
+    if not argv:
+        print("ultima run: missing model folder", file=sys.stderr)
+        return 2
+    model_dir = argv[0]
+    opt = {"prompt": "1,2,3", "n_predict": 48, "n_ctx": 512, "temp": 0.0, "seed": 0, "show_tokens": False,
+           "dtype": "bfloat16", "top_k": 0, "top_p": 1.0, "min_p": 0.0, "repeat_penalty": 1.0,
+           "repeat_last_n": 0, "stop_ids": None, "n_threads": 0}
+    conv = {"prompt": str, "n_predict": int, "n_ctx": int, "temp": float, "seed": int, "dtype": str,
+            "top_k": int, "top_p": float, "min_p": float, "repeat_penalty": float, "repeat_last_n": int,
+            "stop_ids": str, "n_threads": int}
+    i = 1
+    while i < len(argv):
+        a = argv[i]
+        key = a[2:].replace("-", "_") if a.startswith("--") else None
+        if key == "show_tokens":
+            opt[key] = True
+        elif key in conv:
+            if i + 1 >= len(argv):
+                print(f"ultima run: {a} requires a value", file=sys.stderr)
+                return 2
+            i += 1
+            opt[key] = conv[key](argv[i])
+        else:
+            print(f"ultima run: unknown flag '{a}'", file=sys.stderr)
+            return 2
+        i += 1
+    from .engine.generate import LLM
+    from .sampling import SamplingParams
+    prompts = _ids(opt["prompt"])
+    if opt["show_tokens"]:
+        for p in prompts:
+            print("prompt tokens:", " ".join(map(str, p)))
+    for p in prompts:
+        if len(p) + opt["n_predict"] > opt["n_ctx"]:
+            print(f"ultima run: prompt ({len(p)}) + n-predict ({opt['n_predict']}) exceeds n-ctx "
+                  f"({opt['n_ctx']})", file=sys.stderr)
+            return 1
+    llm = LLM(model_dir, dtype=opt["dtype"], n_ctx=opt["n_ctx"], max_batch=max(1, len(prompts)))
+    sp = SamplingParams(temperature=opt["temp"], top_k=opt["top_k"], top_p=opt["top_p"], min_p=opt["min_p"],
+                        rep_penalty=opt["repeat_penalty"], repeat_last_n=opt["repeat_last_n"])
+    stop = None if opt["stop_ids"] is None else [int(x) for x in opt["stop_ids"].replace(",", " ").split()]
+    outs = llm.generate(prompts, n_predict=opt["n_predict"], seed=opt["seed"], stop_token_ids=stop, sampling=sp)
+    for g in outs:
+        print(" ".join(map(str, g.tokens)))
+    st = llm.last_stats
+    pre = st.prompt_tokens / st.prefill_s if st.prefill_s > 0 else 0.0
+    dec = (st.generated_tokens - len(prompts)) / st.decode_s if st.decode_s > 0 else 0.0
+    print(f"[{st.prompt_tokens} prompt tok in {st.prefill_s * 1e3:.1f} ms ({pre:.1f} tok/s) | "
+          f"{st.generated_tokens} gen tok in {st.decode_s * 1e3:.1f} ms ({dec:.1f} tok/s)]", file=sys.stderr)
+    return 0
+
+
+def main(argv=None) -> int:
+    argv = list(sys.argv[1:] if argv is None else argv)
+    if not argv or argv[0] in ("--help", "-h", "help"):
+        print(USAGE)
+        return 0
+    if argv[0] == "--version":
+        from . import __version__
+        print(f"ultima_b200 {__version__}")
+        return 0
+    cmd, rest = argv[0], argv[1:]
+    try:
+        if cmd == "archs":
+            return cmd_archs()
+        if cmd == "archinfo":
+            return cmd_archinfo(rest)
+        if cmd == "random":
+            return cmd_random(rest)
+        if cmd == "run":
+            return cmd_run(rest)
+        if cmd == "replay":
+            from .engine.trace import main as replay_main
+            return replay_main(rest)
+    except (ValueError, RuntimeError, OSError) as e:
+        print(f"ultima {cmd}: {e}", file=sys.stderr)
+        return 1
+    print(f"ultima: unknown command '{cmd}'\n", file=sys.stderr)
+    print(USAGE, file=sys.stderr)
+    return 2

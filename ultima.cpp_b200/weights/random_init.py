@@ -57,3 +57,25 @@ def write_random_model(model_dir: str, config, seed: int, dtype: str | None = No
     write_safetensors(os.path.join(model_dir, "model.safetensors"), tensors,
                       metadata={"format": "pt", "seed": seed})
     return model_dir
+
+
+def random_tensors_on_device(specs: list[WeightSpec], seed: int, run_dtype: torch.dtype, device) -> dict:
+    """name -> tensor drawn on the GPU by the fill kernel (for models too large to draw on the
+    host in reasonable time).  Same distributions as ``random_tensors``, other values."""
+    from ..kernels import ops
+    from .loader import storage_dtype
+    out = {}
+    file_dtype = "BF16" if run_dtype == torch.bfloat16 else "F32"
+    for s in specs:
+        dt = storage_dtype(file_dtype, run_dtype, s.kind)
+        if s.kind == "table":
+            out[s.name] = torch.zeros(s.shape, dtype=torch.int32, device=device)
+            continue
+        t = torch.empty(s.shape, dtype=dt, device=device)
+        if s.init[0] == "zeros":
+            t.zero_()
+        else:
+            shift = 1.0 if s.init[0] == "one_plus_normal" else 0.0
+            ops.fill_normal(t, _tensor_seed(seed, s.name), shift, float(s.init[1]))
+        out[s.name] = t
+    return out
