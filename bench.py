@@ -83,22 +83,14 @@ class ClockSampler:
                 "reasons": reasons, "samples": len(sm)}
 
 
-def weight_bytes(engine):
-    seen, total = set(), 0
-    def add(t):
-        nonlocal total
-        if t is not None and t.data_ptr() not in seen:
-            seen.add(t.data_ptr())
-            total += t.numel() * t.element_size()
-    for L in engine.model.layers:
-        for part in (L.mixer, L.feed_forward, L.mixer_norm, L.feed_forward_norm):
-            for v in vars(part).values():
-                if hasattr(v, "data_ptr") and v.dim() >= 1 and v.is_cuda and v.numel() > 64 and not str(v.dtype).endswith("int32"):
-                    if getattr(part, "position", None) is None or True:
-                        add(v)
-    add(engine.model.head.weight)
-    add(engine.model.final_norm.weight)
-    return total
+def weight_bytes(cfg, dtype_bytes=2):
+    """Every weight a decode step uses, once: the projections of each layer and the head (the
+    embedding table is read one row a token; norm weights are counted)."""
+    H, Q, KV, F, V, L = (cfg.hidden_size, cfg.q_width, cfg.kv_width, cfg.intermediate_size,
+                         cfg.vocab_size, cfg.num_hidden_layers)
+    mats = L * (H * (Q + 2 * KV) + Q * H + 3 * H * F) + V * H
+    vecs = L * (2 * H + 2 * cfg.head_dim) + H
+    return mats * dtype_bytes + vecs * 4
 
 
 def kv_bytes_per_token(cfg, dtype_bytes):
@@ -229,7 +221,7 @@ def run_ours(args):
     ms, launches, ctx = timed_decode(engine, sampler, BATCH, args.steps, args.warmup, rng, real_prefill=True)
     clk = clocks.stop()
     value = BATCH * args.steps / ms * 1e3
-    wbytes = weight_bytes(engine)
+    wbytes = weight_bytes(cfg)
     step_bytes = wbytes + BATCH * (ctx - args.steps / 2) * kv_bytes_per_token(cfg, 2)
     achieved = step_bytes / (ms / args.steps * 1e-3) / 1e9
     print(f"[bench] decode b{BATCH}: {value:.1f} tok/s", file=sys.stderr, flush=True)
@@ -248,7 +240,7 @@ def run_ours(args):
     stats = LoopStats()
     generate(engine, sampler.sample, prompts, SamplingParams(), n_new, (), max_batch=BATCH, stats=stats)
     e2e_val = BATCH * (n_new - 1) / stats.decode_s
-    h2d = 4 * (4 * (-(-BATCH // 4) * 4) + 4 * (-(-(BATCH + 1) // 4) * 4) // 4 + BATCH * engine.cache.kv_groups[0].pages_per_seq)
+    h2d = engine.last_h2d_bytes + BATCH * 64      # the step's batch record and the sampler's records
     e2e = {"value": round(e2e_val, 1), "unit": "tokens/s", "h2d_bytes_per_step": int(h2d),
            "d2h_bytes_per_step": 4 * BATCH}
 

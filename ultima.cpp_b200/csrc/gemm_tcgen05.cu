@@ -1,0 +1,368 @@
+// Matrix product on the fifth-generation tensor cores: out[t, n] = sum_k A[t, k] * W[n, k],
+// bfloat16 operands, float32 accumulation in tensor memory.
+//
+// The weight matrix is the M operand of the MMA (128 rows of W a tile) and the tokens are the
+// N operand (16 to 256 tokens a tile).  A prompt of thousands of tokens and a decode step of one
+// token are the same kernel with another token tile: with few tokens the kernel streams the
+// weights once at memory speed, with many it is bound by the tensor cores.  Both operands are
+// K-major, which is how activations [tokens, k] and weights [out, k] lie in memory.
+//
+// One CTA computes one tile (optionally one slice of K).  Warp 0 issues the TMA loads (weights
+// and activations, 64 k-columns = 128 bytes a row, 128-byte swizzle) into a ring of stages;
+// warp 1 allocates tensor memory and issues tcgen05.mma from one thread; warps 2-5 read the
+// accumulators back with tcgen05.ld (each warp its quarter of the 128 lanes = weight rows) and
+// apply the epilogue: store (bfloat16 or float32), add into a float32 matrix (the residual
+// stream; with atomics when K is split), or silu(gate) * up from two accumulators fed by two
+// weight tiles.  Every wait on an mbarrier has a time limit; on a timeout the kernel raises a
+// flag in global memory, lets its copies land, frees its tensor memory and returns.
+//
+// The reference computes these products with AVX2 row-dot kernels in float32
+// (src/kernels/dot_batched.cpp:39-96, src/model/weight_dispatch.cpp:374-441); the float32
+// restatement of that is gemm_simt.cu, which this kernel is tested against.
+#include "common.cuh"
+#include <cuda.h>
+
+enum : int { EPI_STORE = 0, EPI_ADD = 1, EPI_SWIGLU = 2 };
+
+constexpr int BM = 128;              // weight rows a tile (MMA M)
+constexpr int BK = 64;               // k columns a stage: 128 bytes of bfloat16
+constexpr int UMMA_K = 16;
+constexpr int NUM_THREADS = 192;
+constexpr long long WAIT_LIMIT_CYCLES = 4000000000ll;      // about two seconds
+
+// ---------------------------------------------------------------------------------------
+// PTX wrappers
+// ---------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+    return ok != 0;
+}
+// Wait with a time limit.  False (and *err_flag raised) if the limit ran out.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* err_smem) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const long long t0 = clock64();
+    while (!mbar_try_wait(bar, parity)) {
+        if (*err_smem) return false;
+        if (clock64() - t0 > WAIT_LIMIT_CYCLES) { *err_smem = 1; return false; }
+    }
+    return true;
+}
+__device__ __forceinline__ void fence_barrier_init() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
+__device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
+__device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* map, uint64_t* bar, int x, int y) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(smem_u32(smem_dst)), "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void prefetch_tmap(const CUtensorMap* map) {
+    asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
+}
+
+__device__ __forceinline__ void tmem_alloc(uint32_t* dst_smem, uint32_t ncols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(dst_smem)), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish() { asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tc_mma_bf16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t* r) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Shared-memory matrix descriptor of a K-major tile with 128-byte swizzle: rows of 128 bytes,
+// groups of 8 rows 1024 bytes apart; descriptor version 1 (sm_100), layout type 2 (128B).
+__device__ __forceinline__ uint64_t make_desc(uint32_t smem_addr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr & 0x3FFFF) >> 4);           // start address
+    d |= (uint64_t)1 << 16;                                // leading byte offset (unused with swizzle)
+    d |= (uint64_t)(1024 >> 4) << 32;                      // stride byte offset: 8 rows
+    d |= (uint64_t)1 << 46;                                // version
+    d |= (uint64_t)2 << 61;                                // SWIZZLE_128B
+    return d;
+}
+// Instruction descriptor: float32 accumulate, bfloat16 A and B, both K-major, M = 128, N = n.
+__host__ __device__ constexpr uint32_t make_idesc(int n) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+}
+
+struct GemmParams {
+    void* out;            // [T, N] (element type by the kernel's template)
+    long long ldo;        // row stride of out, elements
+    long long split_stride;   // elements between the partial results of K slices (EPI_STORE float32), else 0
+    int T, N, K;
+    int kb_per_split;     // 64-column blocks of K a slice
+    int atomic;           // EPI_ADD: add with atomics (K is split)
+    int* error;           // raised on a timeout
+};
+
+template <int BN, int EPI>
+struct Smem {
+    static constexpr int A_BYTES = BM * BK * 2;
+    static constexpr int B_BYTES = BN * BK * 2;
+    static constexpr int STAGE_BYTES = A_BYTES * (EPI == EPI_SWIGLU ? 2 : 1) + B_BYTES;
+    static constexpr int BUDGET = 200 * 1024;
+    static constexpr int STAGES_RAW = BUDGET / STAGE_BYTES;
+    static constexpr int STAGES = STAGES_RAW > 10 ? 10 : STAGES_RAW;
+    static constexpr int TOTAL = STAGES * STAGE_BYTES + 1024 /*alignment*/ + 256 /*barriers*/;
+    static constexpr int ACC_COLS = BN * (EPI == EPI_SWIGLU ? 2 : 1);
+    static constexpr int TMEM_COLS = ACC_COLS <= 32 ? 32 : ACC_COLS <= 64 ? 64 : ACC_COLS <= 128 ? 128 : ACC_COLS <= 256 ? 256 : 512;
+};
+
+template <int BN, int EPI, typename TO>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_w2,
+               const __grid_constant__ CUtensorMap map_a, GemmParams p) {
+    using S = Smem<BN, EPI>;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint64_t* full = (uint64_t*)(smem + S::STAGES * S::STAGE_BYTES);
+    uint64_t* empty = full + S::STAGES;
+    uint64_t* acc_full = empty + S::STAGES;
+    uint32_t* tmem_slot = (uint32_t*)(acc_full + 1);
+    volatile int* err = (volatile int*)(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int n0 = blockIdx.x * BM;                 // first weight row = first output column
+    const int t0 = blockIdx.y * BN;                 // first token
+    const int nkb_all = (p.K + BK - 1) / BK;
+    const int kb0 = blockIdx.z * p.kb_per_split;
+    const int kb1 = min(nkb_all, kb0 + p.kb_per_split);
+    const int nkb = kb1 - kb0;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < S::STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+        mbar_init(acc_full, 1);
+        *err = 0;
+        fence_barrier_init();
+    }
+    if (warp == 1) { tmem_alloc(tmem_slot, S::TMEM_COLS); tmem_relinquish(); }
+    if (warp == 0 && lane == 0) {
+        prefetch_tmap(&map_w); prefetch_tmap(&map_a);
+        if (EPI == EPI_SWIGLU) prefetch_tmap(&map_w2);
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        // ---------------- producer ----------------
+        if (lane == 0) {
+            int armed = 0;
+            for (int i = 0; i < nkb; ++i) {
+                const int s = i % S::STAGES;
+                const uint32_t ph = (i / S::STAGES) & 1;
+                if (!mbar_wait(&empty[s], ph ^ 1, err)) break;
+                uint8_t* st = smem + s * S::STAGE_BYTES;
+                mbar_expect_tx(&full[s], S::STAGE_BYTES);
+                const int kx = (kb0 + i) * BK;
+                tma_load_2d(st, &map_w, &full[s], kx, n0);
+                if (EPI == EPI_SWIGLU) tma_load_2d(st + S::A_BYTES, &map_w2, &full[s], kx, n0);
+                tma_load_2d(st + S::A_BYTES * (EPI == EPI_SWIGLU ? 2 : 1), &map_a, &full[s], kx, t0);
+                armed = i + 1;
+            }
+            if (*err) {
+                // let the copies that are in flight land before the CTA's memory goes away
+                for (int i = max(0, armed - S::STAGES); i < armed; ++i) {
+                    const long long tstart = clock64();
+                    while (!mbar_try_wait(&full[i % S::STAGES], (i / S::STAGES) & 1))
+                        if (clock64() - tstart > WAIT_LIMIT_CYCLES / 8) break;
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issuer ----------------
+        if (lane == 0) {
+            constexpr uint32_t idesc = make_idesc(BN);
+            bool ok = true;
+            for (int i = 0; i < nkb && ok; ++i) {
+                const int s = i % S::STAGES;
+                const uint32_t ph = (i / S::STAGES) & 1;
+                ok = mbar_wait(&full[s], ph, err);
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t a_addr = smem_u32(smem + s * S::STAGE_BYTES);
+                const uint32_t b_addr = a_addr + S::A_BYTES * (EPI == EPI_SWIGLU ? 2 : 1);
+                const uint64_t da = make_desc(a_addr), db = make_desc(b_addr);
+                const uint64_t da2 = make_desc(a_addr + S::A_BYTES);
+#pragma unroll
+                for (int k = 0; k < BK / UMMA_K; ++k) {
+                    const uint64_t koff = (uint64_t)((k * UMMA_K * 2) >> 4);       // 32 bytes a step
+                    const uint32_t accum = (i > 0 || k > 0) ? 1u : 0u;
+                    tc_mma_bf16(tmem_base, da + koff, db + koff, idesc, accum);
+                    if (EPI == EPI_SWIGLU) tc_mma_bf16(tmem_base + BN, da2 + koff, db + koff, idesc, accum);
+                }
+                tc_commit(&empty[s]);            // the stage is free once these MMAs have read it
+            }
+            tc_commit(acc_full);                 // all MMAs done: accumulators complete
+        }
+    } else {
+        // ---------------- epilogue: warps 2..5 ----------------
+        const int q = warp & 3;                          // the lanes this warp may read: 32 q .. 32 q + 31
+        const int n = n0 + q * 32 + lane;                // this thread's weight row = output column
+        bool ok = nkb > 0 ? mbar_wait(acc_full, 0, err) : true;
+        tc_fence_after();
+        if (ok && nkb > 0) {
+            TO* out = (TO*)p.out + (EPI == EPI_STORE ? (long long)blockIdx.z * p.split_stride : 0);
+#pragma unroll 1
+            for (int c0 = 0; c0 < BN; c0 += 16) {
+                if (t0 + c0 >= p.T) break;               // uniform over the warp
+                uint32_t r[16], r2[16];
+                const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)c0;
+                tmem_ld16(taddr, r);
+                if (EPI == EPI_SWIGLU) tmem_ld16(taddr + BN, r2);
+                tmem_ld_wait();
+                if (n < p.N) {
+#pragma unroll
+                    for (int c = 0; c < 16; ++c) {
+                        const int t = t0 + c0 + c;
+                        if (t >= p.T) break;
+                        const float v = __uint_as_float(r[c]);
+                        TO* dst = out + (long long)t * p.ldo + n;
+                        if (EPI == EPI_STORE) *dst = from_f32<TO>(v);
+                        else if (EPI == EPI_ADD) {
+                            if (p.atomic) atomicAdd((float*)dst, v);
+                            else *(float*)dst += v;
+                        } else {
+                            const float u = __uint_as_float(r2[c]);
+                            *dst = from_f32<TO>(v / (1.0f + expf(-v)) * u);
+                        }
+                    }
+                }
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, S::TMEM_COLS);
+    }
+    if (threadIdx.x == 0 && *err) atomicExch(p.error, 1);
+}
+
+// ---------------------------------------------------------------------------------------
+// host side
+// ---------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static EncodeTiledFn g_encode = nullptr;
+
+static int load_encode() {
+    if (g_encode) return 0;
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres);
+    if (e != cudaSuccess || qres != cudaDriverEntryPointSuccess || !fn) return UB_ERR_UNSUPPORTED;
+    g_encode = (EncodeTiledFn)fn;
+    return 0;
+}
+
+// A tensor map of a row-major bfloat16 matrix [rows, cols] with row stride ld (elements): boxes
+// of box_rows x 64 columns, 128-byte swizzle, zeros outside.  ``out_map`` is 128 bytes on the host.
+UB_API int ub_tmap_bf16_2d(void* out_map, const void* base, long long rows, long long cols, long long ld, int box_rows) {
+    if (load_encode()) return UB_ERR_UNSUPPORTED;
+    if (((uintptr_t)base & 15) || (ld * 2) % 16 != 0 || box_rows < 1 || box_rows > 256 || rows < 1 || cols < 1) return UB_ERR_ARG;
+    cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+    cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = g_encode((CUtensorMap*)out_map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (void*)base, dims, strides, box, estr,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? 0 : UB_ERR_ARG;
+}
+
+template <int BN, int EPI, typename TO>
+static int launch_one(const CUtensorMap* mw, const CUtensorMap* mw2, const CUtensorMap* ma, const GemmParams& p,
+                      int splits, cudaStream_t st) {
+    using S = Smem<BN, EPI>;
+    static bool attr_done = false;
+    auto kern = gemm_tc_kernel<BN, EPI, TO>;
+    if (!attr_done) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL);
+        if (e != cudaSuccess) return (int)e;
+        attr_done = true;
+    }
+    dim3 grid((p.N + BM - 1) / BM, (p.T + BN - 1) / BN, splits);
+    if (grid.y > 65535 || grid.z > 65535) return UB_ERR_ARG;
+    kern<<<grid, NUM_THREADS, S::TOTAL, st>>>(*mw, *mw2, *ma, p);
+    UB_LAUNCH_CHECK();
+    return 0;
+}
+
+template <int BN>
+static int launch_bn(const CUtensorMap* mw, const CUtensorMap* mw2, const CUtensorMap* ma, const GemmParams& p,
+                     int epi, int o_dtype, int splits, cudaStream_t st) {
+    if (epi == EPI_STORE && o_dtype == UB_BF16) return launch_one<BN, EPI_STORE, __nv_bfloat16>(mw, mw2, ma, p, splits, st);
+    if (epi == EPI_STORE && o_dtype == UB_F32) return launch_one<BN, EPI_STORE, float>(mw, mw2, ma, p, splits, st);
+    if (epi == EPI_ADD && o_dtype == UB_F32) return launch_one<BN, EPI_ADD, float>(mw, mw2, ma, p, splits, st);
+    if (epi == EPI_SWIGLU && o_dtype == UB_BF16) {
+        if constexpr (BN <= 128) return launch_one<BN, EPI_SWIGLU, __nv_bfloat16>(mw, mw2, ma, p, splits, st);
+        else return UB_ERR_ARG;
+    }
+    return UB_ERR_UNSUPPORTED;
+}
+
+// map_w (and map_w2 for EPI_SWIGLU): weights [N, K], boxes of 128 rows; map_a: activations [T, K],
+// boxes of ``bn`` rows.  splits > 1 cuts K into slices of kb_per_split blocks of 64: EPI_ADD then adds
+// with atomics, EPI_STORE (float32 only) writes slice z at out + z * split_stride.
+UB_API int ub_gemm_tc(const void* map_w, const void* map_w2, const void* map_a, void* out, int o_dtype, long long ldo,
+                      long long split_stride, int T, int N, int K, int bn, int epi, int splits, int* error,
+                      cudaStream_t st) {
+    if (T <= 0 || N <= 0) return 0;
+    if (K <= 0 || splits < 1) return UB_ERR_ARG;
+    if (splits > 1 && epi == EPI_SWIGLU) return UB_ERR_ARG;
+    if (splits > 1 && epi == EPI_STORE && o_dtype != UB_F32) return UB_ERR_ARG;
+    const int nkb = (K + BK - 1) / BK;
+    GemmParams p;
+    p.out = out; p.ldo = ldo; p.split_stride = splits > 1 ? split_stride : 0;
+    p.T = T; p.N = N; p.K = K;
+    p.kb_per_split = (nkb + splits - 1) / splits;
+    p.atomic = (epi == EPI_ADD && splits > 1) ? 1 : 0;
+    p.error = error;
+    if ((long long)(splits - 1) * p.kb_per_split >= nkb) return UB_ERR_ARG;      // an empty slice
+    const CUtensorMap* mw = (const CUtensorMap*)map_w;
+    const CUtensorMap* mw2 = (const CUtensorMap*)(map_w2 ? map_w2 : map_w);
+    const CUtensorMap* ma = (const CUtensorMap*)map_a;
+    switch (bn) {
+        case 16: return launch_bn<16>(mw, mw2, ma, p, epi, o_dtype, splits, st);
+        case 32: return launch_bn<32>(mw, mw2, ma, p, epi, o_dtype, splits, st);
+        case 64: return launch_bn<64>(mw, mw2, ma, p, epi, o_dtype, splits, st);
+        case 128: return launch_bn<128>(mw, mw2, ma, p, epi, o_dtype, splits, st);
+        case 256: return launch_bn<256>(mw, mw2, ma, p, epi, o_dtype, splits, st);
+    }
+    return UB_ERR_ARG;
+}

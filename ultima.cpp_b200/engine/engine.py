@@ -214,6 +214,7 @@ class Engine:
             self.cache.reserve(s, b + len(t))
         batch = build_step_batch(slots, new_tokens, before, want_rows, self.cache.tables(slots),
                                  self.device)
+        self.last_h2d_bytes = batch.host["pinned"].numel() * 4
         logits = self.model.forward(batch, self.cache)
         for s, t in zip(slots, new_tokens):
             self.cache.commit(s, len(t))
