@@ -244,3 +244,85 @@ def test_silu_mul_convert_add_fill():
     again = torch.empty(1 << 20, device=DEV)
     ops.fill_normal(again, 1234, 1.0, 0.05)
     assert torch.equal(big, again)
+
+
+# ---------------------------------------------------------------------------------------
+# the tensor-core product against the CUDA-core product and float64
+# ---------------------------------------------------------------------------------------
+def _tc():
+    from ultima_b200.kernels import gemm_tc
+    from ultima_b200.engine import Runtime
+    return gemm_tc, Runtime(DEV, torch.bfloat16)
+
+
+@pytest.mark.parametrize("shape", [(1, 64, 128), (5, 96, 200), (16, 512, 128), (33, 1024, 384), (64, 4096, 256),
+                                   (130, 320, 96), (300, 200, 1000), (513, 2048, 640)])
+def test_gemm_tc_store(shape):
+    gemm_tc, rt = _tc()
+    ops = _ops()
+    T, K, N = shape
+    g = torch.Generator().manual_seed(T + K)
+    a = torch.randn(T, K, generator=g).to(torch.bfloat16).to(DEV)
+    w = (torch.randn(N, K, generator=g) * 0.05).to(torch.bfloat16).to(DEV)
+    ref = a.double() @ w.double().T
+    for dt in (torch.bfloat16, torch.float32):
+        out = torch.full((T, N), float("nan"), dtype=dt, device=DEV)
+        assert gemm_tc.accepts(a, w, out, ops.EPI_STORE, None)
+        gemm_tc.gemm(a, w, out, ops.EPI_STORE, None, rt)
+        torch.cuda.synchronize()
+        gemm_tc.check_error(rt)
+        # the tensor cores align and truncate the products of one instruction: the error grows with K
+        assert rel_err(out, ref) <= (2 ** -8 if dt == torch.bfloat16 else max(2e-6, K * 2.0 ** -25)), (shape, dt)
+
+
+@pytest.mark.parametrize("shape", [(3, 4096, 512, None), (8, 12288, 256, None), (64, 2048, 128, 4), (200, 1024, 300, 2),
+                                   (7, 960, 130, 3)])
+def test_gemm_tc_add_with_and_without_k_split(shape):
+    gemm_tc, rt = _tc()
+    ops = _ops()
+    T, K, N, splits = shape
+    g = torch.Generator().manual_seed(K)
+    a = torch.randn(T, K, generator=g).to(torch.bfloat16).to(DEV)
+    w = (torch.randn(N, K, generator=g) * 0.05).to(torch.bfloat16).to(DEV)
+    acc = torch.randn(T, N, generator=g).to(DEV)
+    ref = acc.double() + a.double() @ w.double().T
+    gemm_tc.gemm(a, w, acc, ops.EPI_ADD, None, rt, splits=splits)
+    torch.cuda.synchronize()
+    gemm_tc.check_error(rt)
+    assert rel_err(acc, ref) <= max(2e-6, K * 2.0 ** -25), shape
+
+
+@pytest.mark.parametrize("shape", [(2, 64, 192), (40, 96, 320), (128, 4096, 384), (257, 512, 130)])
+def test_gemm_tc_gate_product(shape):
+    gemm_tc, rt = _tc()
+    ops = _ops()
+    T, K, F = shape
+    g = torch.Generator().manual_seed(F)
+    a = torch.randn(T, K, generator=g).to(torch.bfloat16).to(DEV)
+    wgu = (torch.randn(2 * F, K, generator=g) * 0.05).to(torch.bfloat16).to(DEV)
+    out = torch.full((T, F), float("nan"), dtype=torch.bfloat16, device=DEV)
+    gemm_tc.gemm(a, wgu[:F], out, ops.EPI_SWIGLU, wgu[F:], rt)
+    torch.cuda.synchronize()
+    gemm_tc.check_error(rt)
+    gt, up = a.double() @ wgu[:F].double().T, a.double() @ wgu[F:].double().T
+    assert rel_err(out, gt / (1 + torch.exp(-gt)) * up) <= 2 ** -8, shape
+
+
+def test_gemm_tc_views_and_what_it_refuses():
+    gemm_tc, rt = _tc()
+    ops = _ops()
+    g = torch.Generator().manual_seed(0)
+    wide = torch.randn(50, 256 + 64, generator=g).to(torch.bfloat16).to(DEV)
+    a = wide[:, 64:]                                   # rows start on 16-byte boundaries: taken
+    w = (torch.randn(96, 256, generator=g) * 0.05).to(torch.bfloat16).to(DEV)
+    out = torch.empty(50, 96, dtype=torch.float32, device=DEV)
+    assert gemm_tc.accepts(a, w, out, ops.EPI_STORE, None)
+    gemm_tc.gemm(a, w, out, ops.EPI_STORE, None, rt)
+    assert rel_err(out, a.double() @ w.double().T) <= 2e-5
+    assert not gemm_tc.accepts(wide[:, 3:259], w, out, ops.EPI_STORE, None)          # misaligned rows
+    assert not gemm_tc.accepts(a[:, :100], w[:, :100], out, ops.EPI_STORE, None)     # K not a multiple of 8
+    assert not gemm_tc.accepts(a.float(), w, out, ops.EPI_STORE, None)
+    # the runtime sends refused shapes to the CUDA-core kernel and gets the same answer
+    a2, w2 = a[:, :100].contiguous(), w[:, :100].contiguous()
+    rt.matmul(a2, w2, out)
+    assert rel_err(out, a2.double() @ w2.double().T) <= 2e-5

@@ -1,0 +1,418 @@
+// Attention over the paged bfloat16 cache on the tensor cores, for one head size fixed at
+// compile time (-DHEAD_DIM=..., any multiple of 16 up to 256).
+//
+// Two kernels share the inner tile code (flash attention: scores, running maximum and sum in
+// float32, probabilities rounded to bfloat16 for the second product):
+//   prefill  one CTA for 64 rows of one KV head, a row being (token, query head of the group);
+//            the group's heads share every K/V tile that is loaded.  4 warps x 16 rows.
+//   decode   one new token a sequence: one CTA for (slice of the keys, sequence, KV head); its
+//            4 warps take every fourth 16 keys of each 64-key tile and their partial results
+//            are merged in shared memory; with several slices the CTA writes an unnormalised
+//            partial result (maximum, sum, output) that attn_combine merges.
+// K and V tiles are one cache page (64 positions of one KV head, contiguous) and arrive with
+// cp.async, double buffered.  Positions the sequence has not reached are written as zeros into
+// shared memory, so whatever the cache held before cannot reach the result.
+//
+// The arithmetic restated is the reference's per-token loop (src/model/qwen_block.cpp:94-135):
+// scores q.k * scale over the visible positions (p - window, p], max-shifted softmax, weighted
+// sum of values, query head h on KV head h / (heads / kv heads).
+#include "common.cuh"
+
+#ifndef HEAD_DIM
+#define HEAD_DIM 128
+#endif
+static_assert(HEAD_DIM % 16 == 0 && HEAD_DIM >= 16 && HEAD_DIM <= 256, "head size: a multiple of 16 up to 256");
+
+constexpr int HD = HEAD_DIM;
+constexpr int LDS = HD + 8;                 // shared-memory row stride (elements): no bank conflicts for ldmatrix
+constexpr int KT = 64;                      // keys a tile = positions a page
+constexpr int NTHREADS = 128;
+constexpr int KSTEPS = HD / 16;
+constexpr int DTILES = HD / 8;
+
+typedef __nv_bfloat16 bf16;
+
+__device__ __forceinline__ uint32_t smem_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void cp_async16(void* dst, const void* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_addr(dst)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+__device__ __forceinline__ void ldsm_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ void ldsm_x2(uint32_t addr, uint32_t& r0, uint32_t& r1) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x2.shared.b16 {%0, %1}, [%2];" : "=r"(r0), "=r"(r1) : "r"(addr));
+}
+__device__ __forceinline__ void ldsm_x4_trans(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ void mma_bf16(float* d, const uint32_t* a, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+
+// Load one page (64 positions of one KV head) of K and V into shared memory; positions above
+// ``last_pos`` become zeros.  ``base`` is the absolute position of the tile's first key.
+__device__ __forceinline__ void load_kv_tile(bf16* Ks, bf16* Vs, const bf16* __restrict__ kc, const bf16* __restrict__ vc,
+                                             const PagedKV& c, int seq, int kvh, int base, int last_pos, int tid) {
+    const long long off = paged_offset(c, seq, base, kvh);            // first position of the page
+    constexpr int CH = HD / 8;                                         // 16-byte pieces a row
+    for (int i = tid; i < KT * CH; i += NTHREADS) {
+        const int r = i / CH, ch = i % CH;
+        bf16* kd = Ks + r * LDS + ch * 8;
+        bf16* vd = Vs + r * LDS + ch * 8;
+        if (base + r <= last_pos) {
+            cp_async16(kd, kc + off + (long long)r * HD + ch * 8);
+            cp_async16(vd, vc + off + (long long)r * HD + ch * 8);
+        } else {
+            *reinterpret_cast<uint4*>(kd) = make_uint4(0, 0, 0, 0);
+            *reinterpret_cast<uint4*>(vd) = make_uint4(0, 0, 0, 0);
+        }
+    }
+}
+
+// Scores of 16 rows against ``NT`` groups of 8 keys starting at key row ``key0`` of the K tile.
+template <int NT>
+__device__ __forceinline__ void scores(float (*s)[4], const bf16* Qs, int q_row0, const bf16* Ks, int key0, int lane) {
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) { s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.f; }
+#pragma unroll
+    for (int ks = 0; ks < KSTEPS; ++ks) {
+        uint32_t a[4];
+        ldsm_x4(smem_addr(Qs + (q_row0 + (lane & 15)) * LDS + ks * 16 + (lane >> 4) * 8), a[0], a[1], a[2], a[3]);
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) {
+            uint32_t b0, b1;
+            ldsm_x2(smem_addr(Ks + (key0 + nt * 8 + (lane & 7)) * LDS + ks * 16 + ((lane >> 3) & 1) * 8), b0, b1);
+            mma_bf16(s[nt], a, b0, b1);
+        }
+    }
+}
+
+// o += P V for 16 rows, P being the probabilities of ``NT`` groups of 8 keys (NT even) held in
+// the accumulator layout of ``scores``; the V rows start at ``key0`` of the V tile.
+template <int NT>
+__device__ __forceinline__ void weighted_values(float (*o)[4], const float (*s)[4], const bf16* Vs, int key0, int lane) {
+#pragma unroll
+    for (int kk = 0; kk < NT / 2; ++kk) {
+        uint32_t a[4];
+        a[0] = pack_bf16(s[2 * kk][0], s[2 * kk][1]);
+        a[1] = pack_bf16(s[2 * kk][2], s[2 * kk][3]);
+        a[2] = pack_bf16(s[2 * kk + 1][0], s[2 * kk + 1][1]);
+        a[3] = pack_bf16(s[2 * kk + 1][2], s[2 * kk + 1][3]);
+#pragma unroll
+        for (int dt = 0; dt < DTILES; dt += 2) {
+            uint32_t b0, b1, b2, b3;
+            const int row = key0 + kk * 16 + ((lane >> 3) & 1) * 8 + (lane & 7);
+            const int col = dt * 8 + (lane >> 4) * 8;
+            ldsm_x4_trans(smem_addr(Vs + row * LDS + col), b0, b1, b2, b3);
+            mma_bf16(o[dt], a, b0, b1);
+            mma_bf16(o[dt + 1], a, b2, b3);
+        }
+    }
+}
+
+// One step of the running softmax over the masked scores of NT key groups; scores come in raw
+// (q.k) and leave as probabilities relative to the new maximum.  c = scale * log2(e).
+template <int NT>
+__device__ __forceinline__ void softmax_step(float (*s)[4], float (*o)[4], float* m, float* l, float c,
+                                             const int* row_pos, bool const* row_ok, int key_pos0, int window, int lane) {
+    float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const int r = e >> 1;
+            const int kp = key_pos0 + nt * 8 + (lane & 3) * 2 + (e & 1);
+            const bool ok = row_ok[r] && kp <= row_pos[r] && (window <= 0 || kp > row_pos[r] - window);
+            const float v = ok ? s[nt][e] * c : -INFINITY;
+            s[nt][e] = v;
+            mx[r] = fmaxf(mx[r], v);
+        }
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
+        mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
+    }
+    float corr[2], base[2];
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        const float m_new = fmaxf(m[r], mx[r]);
+        base[r] = m_new == -INFINITY ? 0.f : m_new;           // a row with nothing visible yet
+        corr[r] = exp2f(m[r] - base[r]);                      // 0 when m is -inf
+        m[r] = m_new;
+    }
+    float sum[2] = {0.f, 0.f};
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const float p = exp2f(s[nt][e] - base[e >> 1]);
+            s[nt][e] = p;
+            sum[e >> 1] += p;
+        }
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        sum[r] += __shfl_xor_sync(0xffffffffu, sum[r], 1);
+        sum[r] += __shfl_xor_sync(0xffffffffu, sum[r], 2);
+        l[r] = l[r] * corr[r] + sum[r];
+    }
+#pragma unroll
+    for (int dt = 0; dt < DTILES; ++dt) {
+        o[dt][0] *= corr[0]; o[dt][1] *= corr[0];
+        o[dt][2] *= corr[1]; o[dt][3] *= corr[1];
+    }
+}
+
+struct AttnParams {
+    const bf16* q; long long q_stride;
+    bf16* out; long long o_stride;
+    const bf16* kc; const bf16* vc;
+    const int* seq_start; const int* seq_before;
+    int nh, group, window;
+    float c;                                  // scale * log2(e)
+    float* part_o; float* part_ml;            // decode with several slices
+    int n_slices;
+};
+
+// ---------------------------------------------------------------------------------------
+// prefill: grid (row tiles of the longest sequence, sequences, KV heads)
+// ---------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(NTHREADS)
+attn_prefill_kernel(AttnParams p, PagedKV c) {
+    extern __shared__ __align__(16) uint8_t smem_raw[];
+    bf16* Qs = (bf16*)smem_raw;                    // [64][LDS]
+    bf16* Ks = Qs + 64 * LDS;                      // [2][64][LDS]
+    bf16* Vs = Ks + 2 * KT * LDS;                  // [2][64][LDS]
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int seq = blockIdx.y, kvh = blockIdx.z;
+    const int q0 = p.seq_start[seq], q_len = p.seq_start[seq + 1] - q0, before = p.seq_before[seq];
+    const int G = p.group;
+    const int R0 = blockIdx.x * 64;                // first row of this tile; row = token * G + head in group
+    if (R0 >= q_len * G) return;
+    const int last_pos = before + q_len - 1;
+
+    // Q rows of the tile into shared memory (rows past the sequence's end: zeros)
+    constexpr int CH = HD / 8;
+    for (int i = tid; i < 64 * CH; i += NTHREADS) {
+        const int r = i / CH, ch = i % CH;
+        const int R = R0 + r, tok = R / G, g = R % G;
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (tok < q_len) v = *reinterpret_cast<const uint4*>(p.q + (long long)(q0 + tok) * p.q_stride + (long long)(kvh * G + g) * HD + ch * 8);
+        *reinterpret_cast<uint4*>(Qs + r * LDS + ch * 8) = v;
+    }
+    // this thread's two rows
+    int row_pos[2]; bool row_ok[2]; int row_tok[2], row_g[2];
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        const int R = R0 + warp * 16 + (lane >> 2) + r * 8;
+        row_tok[r] = R / G; row_g[r] = R % G;
+        row_ok[r] = row_tok[r] < q_len;
+        row_pos[r] = before + row_tok[r];
+    }
+    const int tok_first = R0 / G, tok_last = min(q_len - 1, (R0 + 63) / G);
+    const int pos_hi = before + tok_last;
+    int pos_lo = 0;
+    if (p.window > 0) pos_lo = max(0, before + tok_first - p.window + 1);
+    const int t_lo = pos_lo / KT, t_hi = pos_hi / KT;
+
+    float o[DTILES][4];
+#pragma unroll
+    for (int dt = 0; dt < DTILES; ++dt) o[dt][0] = o[dt][1] = o[dt][2] = o[dt][3] = 0.f;
+    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+
+    load_kv_tile(Ks, Vs, p.kc, p.vc, c, seq, kvh, t_lo * KT, last_pos, tid);
+    cp_async_commit();
+    for (int t = t_lo; t <= t_hi; ++t) {
+        const int buf = (t - t_lo) & 1;
+        if (t < t_hi) {
+            load_kv_tile(Ks + (buf ^ 1) * KT * LDS, Vs + (buf ^ 1) * KT * LDS, p.kc, p.vc, c, seq, kvh, (t + 1) * KT, last_pos, tid);
+            cp_async_commit();
+            cp_async_wait<1>();
+        } else {
+            cp_async_wait<0>();
+        }
+        __syncthreads();
+        const bf16* K = Ks + buf * KT * LDS;
+        const bf16* V = Vs + buf * KT * LDS;
+        float s[8][4];
+        scores<8>(s, Qs, warp * 16, K, 0, lane);
+        softmax_step<8>(s, o, m, l, p.c, row_pos, row_ok, t * KT, p.window, lane);
+        weighted_values<8>(o, s, V, 0, lane);
+        __syncthreads();                             // the buffer is loaded again two tiles on
+    }
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        if (!row_ok[r]) continue;
+        const float inv = 1.0f / l[r];
+        bf16* dst = p.out + (long long)(q0 + row_tok[r]) * p.o_stride + (long long)(kvh * G + row_g[r]) * HD + (lane & 3) * 2;
+#pragma unroll
+        for (int dt = 0; dt < DTILES; ++dt)
+            *reinterpret_cast<uint32_t*>(dst + dt * 8) = pack_bf16(o[dt][2 * r] * inv, o[dt][2 * r + 1] * inv);
+    }
+}
+
+// ---------------------------------------------------------------------------------------
+// decode: one new token a sequence; grid (slices, sequences, KV heads); group <= 16
+// ---------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(NTHREADS)
+attn_decode_kernel(AttnParams p, PagedKV c) {
+    extern __shared__ __align__(16) uint8_t smem_raw[];
+    bf16* Qs = (bf16*)smem_raw;                    // [16][LDS]
+    bf16* Ks = Qs + 16 * LDS;                      // [2][64][LDS]
+    bf16* Vs = Ks + 2 * KT * LDS;
+    float* red = (float*)(Vs + 2 * KT * LDS);      // [4 warps][16 rows][HD + 2]
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int slice = blockIdx.x, seq = blockIdx.y, kvh = blockIdx.z;
+    const int G = p.group;
+    const int row = p.seq_start[seq];              // the sequence's one token
+    const int pos = p.seq_before[seq];             // its position; keys [lo, pos]
+    int lo = 0;
+    if (p.window > 0) lo = max(0, pos - p.window + 1);
+    const int t_first = lo / KT, t_last = pos / KT;
+    const int n_tiles = t_last - t_first + 1;
+    const int per = (n_tiles + p.n_slices - 1) / p.n_slices;
+    const int t_lo = t_first + slice * per, t_hi = min(t_last, t_lo + per - 1);
+
+    constexpr int CH = HD / 8;
+    for (int i = tid; i < 16 * CH; i += NTHREADS) {
+        const int r = i / CH, ch = i % CH;
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (r < G) v = *reinterpret_cast<const uint4*>(p.q + (long long)row * p.q_stride + (long long)(kvh * G + r) * HD + ch * 8);
+        *reinterpret_cast<uint4*>(Qs + r * LDS + ch * 8) = v;
+    }
+    int row_pos[2] = {pos, pos};
+    bool row_ok[2] = {(lane >> 2) < G, (lane >> 2) + 8 < G};
+    float o[DTILES][4];
+#pragma unroll
+    for (int dt = 0; dt < DTILES; ++dt) o[dt][0] = o[dt][1] = o[dt][2] = o[dt][3] = 0.f;
+    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+
+    if (t_lo <= t_hi) {
+        load_kv_tile(Ks, Vs, p.kc, p.vc, c, seq, kvh, t_lo * KT, pos, tid);
+        cp_async_commit();
+    }
+    for (int t = t_lo; t <= t_hi; ++t) {
+        const int buf = (t - t_lo) & 1;
+        if (t < t_hi) {
+            load_kv_tile(Ks + (buf ^ 1) * KT * LDS, Vs + (buf ^ 1) * KT * LDS, p.kc, p.vc, c, seq, kvh, (t + 1) * KT, pos, tid);
+            cp_async_commit();
+            cp_async_wait<1>();
+        } else {
+            cp_async_wait<0>();
+        }
+        __syncthreads();
+        float s[2][4];
+        scores<2>(s, Qs, 0, Ks + buf * KT * LDS, warp * 16, lane);
+        softmax_step<2>(s, o, m, l, p.c, row_pos, row_ok, t * KT + warp * 16, p.window, lane);
+        weighted_values<2>(o, s, Vs + buf * KT * LDS, warp * 16, lane);
+        __syncthreads();
+    }
+    if (t_lo > t_hi) __syncthreads();               // Qs written above; keep the barrier count equal
+    // merge the four warps: each has (m, l, o) over its keys
+    constexpr int RS = HD + 2;
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        float* dst = red + ((warp * 16) + (lane >> 2) + r * 8) * RS;
+#pragma unroll
+        for (int dt = 0; dt < DTILES; ++dt) {
+            dst[dt * 8 + (lane & 3) * 2] = o[dt][2 * r];
+            dst[dt * 8 + (lane & 3) * 2 + 1] = o[dt][2 * r + 1];
+        }
+        if ((lane & 3) == 0) { dst[HD] = m[r]; dst[HD + 1] = l[r]; }
+    }
+    __syncthreads();
+    for (int i = tid; i < G * HD; i += NTHREADS) {
+        const int g = i / HD, d = i % HD;
+        float mm = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) mm = fmaxf(mm, red[(w * 16 + g) * RS + HD]);
+        float acc = 0.f, ll = 0.f;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+            const float mw = red[(w * 16 + g) * RS + HD];
+            const float f = mw == -INFINITY ? 0.f : exp2f(mw - mm);
+            acc += f * red[(w * 16 + g) * RS + d];
+            ll += f * red[(w * 16 + g) * RS + HD + 1];
+        }
+        const int head = kvh * G + g;
+        if (p.n_slices == 1) {
+            p.out[(long long)row * p.o_stride + (long long)head * HD + d] = __float2bfloat16_rn(acc / ll);
+        } else {
+            const long long pi = ((long long)seq * p.nh + head) * p.n_slices + slice;
+            p.part_o[pi * HD + d] = acc;
+            if (d == 0) { p.part_ml[pi * 2] = mm; p.part_ml[pi * 2 + 1] = ll; }
+        }
+    }
+}
+
+// merge the slices of a decode step: grid (sequences * heads), HD threads (rounded up to a warp)
+__global__ void attn_combine_kernel(AttnParams p) {
+    const int sh = blockIdx.x, d = threadIdx.x;
+    const int seq = sh / p.nh, head = sh % p.nh;
+    const long long base = (long long)sh * p.n_slices;
+    float mm = -INFINITY;
+    for (int s = 0; s < p.n_slices; ++s) mm = fmaxf(mm, p.part_ml[(base + s) * 2]);
+    float acc = 0.f, ll = 0.f;
+    for (int s = 0; s < p.n_slices; ++s) {
+        const float ms = p.part_ml[(base + s) * 2];
+        const float f = ms == -INFINITY ? 0.f : exp2f(ms - mm);
+        ll += f * p.part_ml[(base + s) * 2 + 1];
+        if (d < HD) acc += f * p.part_o[(base + s) * HD + d];
+    }
+    if (d < HD) p.out[(long long)p.seq_start[seq] * p.o_stride + (long long)head * HD + d] = __float2bfloat16_rn(acc / ll);
+}
+
+// ---------------------------------------------------------------------------------------
+UB_API int ub_attn_head_dim() { return HD; }
+
+// mode 0: prefill kernel (any numbers of new tokens), mode 1: decode kernel (one new token for
+// every sequence, group <= 16).  part_o: float32 [n_seqs, nh, n_slices, HD], part_ml: [.., 2].
+UB_API int ub_attn_mma(int mode, const void* q, long long q_stride, void* out, long long o_stride, const void* kcache,
+                       const void* vcache, const int* seq_start, const int* seq_before, const int* table,
+                       int pages_per_seq, int ring, int page, int n_seqs, int max_new, int nh, int nkv, int window,
+                       float scale, int n_slices, float* part_o, float* part_ml, cudaStream_t st) {
+    if (n_seqs <= 0) return 0;
+    if (page != KT || ring % page != 0 || nh % nkv != 0 || (q_stride % 8) != 0 || (o_stride % 2) != 0) return UB_ERR_ARG;
+    if (((uintptr_t)q & 15) || ((uintptr_t)out & 3) || ((uintptr_t)kcache & 15) || ((uintptr_t)vcache & 15)) return UB_ERR_ARG;
+    if (n_seqs > 65535 || nkv > 65535) return UB_ERR_ARG;
+    PagedKV c{table, pages_per_seq, ring, page, nkv, HD};
+    AttnParams p;
+    p.q = (const bf16*)q; p.q_stride = q_stride; p.out = (bf16*)out; p.o_stride = o_stride;
+    p.kc = (const bf16*)kcache; p.vc = (const bf16*)vcache; p.seq_start = seq_start; p.seq_before = seq_before;
+    p.nh = nh; p.group = nh / nkv; p.window = window; p.c = scale * 1.4426950408889634f;
+    p.part_o = part_o; p.part_ml = part_ml; p.n_slices = n_slices < 1 ? 1 : n_slices;
+    static bool attr_done = false;
+    const size_t sm_pre = (size_t)(64 + 4 * KT) * LDS * sizeof(bf16);
+    const size_t sm_dec = (size_t)(16 + 4 * KT) * LDS * sizeof(bf16) + (size_t)64 * (HD + 2) * sizeof(float);
+    if (!attr_done) {
+        cudaError_t e = cudaFuncSetAttribute(attn_prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm_pre);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(attn_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm_dec);
+        if (e != cudaSuccess) return (int)e;
+        attr_done = true;
+    }
+    if (mode == 0) {
+        const int tiles = (max_new * p.group + 63) / 64;
+        if (tiles < 1) return 0;
+        dim3 grid(tiles, n_seqs, nkv);
+        attn_prefill_kernel<<<grid, NTHREADS, sm_pre, st>>>(p, c);
+    } else {
+        if (p.group > 16 || max_new != 1) return UB_ERR_ARG;
+        if (p.n_slices > 1 && (!part_o || !part_ml)) return UB_ERR_ARG;
+        dim3 grid(p.n_slices, n_seqs, nkv);
+        attn_decode_kernel<<<grid, NTHREADS, sm_dec, st>>>(p, c);
+        UB_LAUNCH_CHECK();
+        if (p.n_slices > 1) attn_combine_kernel<<<n_seqs * nh, ((HD + 31) / 32) * 32, 0, st>>>(p);
+    }
+    UB_LAUNCH_CHECK();
+    return 0;
+}

@@ -103,6 +103,10 @@ class Engine:
         finally:
             self.close(s)
 
+    def check_errors(self) -> None:
+        """Raise if a kernel flagged a fault since the last check (waits for the stream)."""
+        self.rt.check_status()
+
     # ---- slots -------------------------------------------------------------------------
     def open(self, n: int = 1) -> list[int]:
         """Acquire ``n`` slots for sequences that start together."""

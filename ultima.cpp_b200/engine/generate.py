@@ -88,6 +88,8 @@ def run_batch(engine, sample, prompts: list, params: list, n_predict: list, stop
         while live:
             ids = sample(logits, [params[i] for i in live], [streams[i] for i in live],
                          [len(out[i].tokens) for i in live], [out[i].tokens for i in live])
+            if hasattr(engine, "check_errors"):
+                engine.check_errors()
             now = time.perf_counter()
             if stats:
                 if first:

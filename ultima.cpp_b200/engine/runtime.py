@@ -66,12 +66,23 @@ class Runtime:
         self._shared: dict = {}
         self.use_tensor_cores = dtype == torch.bfloat16
         self.launches = 0              # kernels of this library launched through the runtime
+        # flags the kernels raise: [0] a token id outside the vocabulary, [1] a wait that ran out
+        self.status = torch.zeros(4, dtype=torch.int32, device=self.device)
 
     def shared(self, key, make):
         """One object for all parts that ask with the same key (rotation tables and the like)."""
         if key not in self._shared:
             self._shared[key] = make()
         return self._shared[key]
+
+    def check_status(self) -> None:
+        """Read the flags the kernels raise (one small copy; waits for the stream)."""
+        st = self.status.tolist()
+        if any(st):
+            self.status.zero_()
+            if st[0]:
+                raise RuntimeError("a token id outside the vocabulary reached the embedding kernel")
+            raise RuntimeError("a wait inside a kernel ran out of time; the step's results are not valid")
 
     # ---- products ----------------------------------------------------------------------
     def matmul(self, a, w, out, epilogue=ops.EPI_STORE, w2=None):

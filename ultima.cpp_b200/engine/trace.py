@@ -43,6 +43,7 @@ def replay(engine, lines, out_dir: str, say=None) -> int:
             want.append([int(p) for p in e.get("want", [])])
         if entries:
             logits = engine.step(slots, tokens, want)
+            engine.check_errors()
             if logits.shape[0] > 0:
                 arr = logits.detach().to("cpu").numpy().astype("<f4", copy=False)
                 tmp = os.path.join(out_dir, f".{step}.f32.tmp")

@@ -1,12 +1,109 @@
-"""Entry point of the tcgen05 matrix product (csrc/gemm_tcgen05.cu)."""
+"""Entry point of the tcgen05 matrix product (csrc/gemm_tcgen05.cu): which calls it takes,
+which token tile and K split it uses, and the tensor maps it needs (made once for each matrix
+and kept)."""
 from __future__ import annotations
 
-ENABLED = False
+import ctypes
+from ctypes import c_int, c_longlong, c_void_p
+
+import torch
+
+from . import build
+from .ops import EPI_ADD, EPI_STORE, EPI_SWIGLU, BF16, F32, KernelError, _check, _ptr, _stream
+
+SOURCE = "gemm_tcgen05.cu"
+N_SMS = 148
+_lib = None
+_maps: dict = {}
+
+
+def lib():
+    global _lib
+    if _lib is None:
+        L = build.load(SOURCE)
+        L.ub_tmap_bf16_2d.argtypes = [c_void_p, c_void_p, c_longlong, c_longlong, c_longlong, c_int]
+        L.ub_tmap_bf16_2d.restype = c_int
+        L.ub_gemm_tc.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_longlong, c_longlong,
+                                 c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p]
+        L.ub_gemm_tc.restype = c_int
+        _lib = L
+    return _lib
+
+
+def _tmap(t: torch.Tensor, box_rows: int) -> int:
+    """Address of a 64-byte aligned CUtensorMap on the host for the 2-D bfloat16 matrix ``t``."""
+    key = (t.data_ptr(), t.shape[0], t.shape[1], t.stride(0), box_rows)
+    hit = _maps.get(key)
+    if hit is not None:
+        return hit[1]
+    raw = ctypes.create_string_buffer(128 + 64)
+    addr = (ctypes.addressof(raw) + 63) & ~63
+    rc = lib().ub_tmap_bf16_2d(addr, t.data_ptr(), t.shape[0], t.shape[1], t.stride(0), box_rows)
+    if rc != 0:
+        raise KernelError(f"tensor map for a [{t.shape[0]}, {t.shape[1]}] matrix with row stride "
+                          f"{t.stride(0)} could not be made (code {rc})")
+    if len(_maps) > 4096:
+        _maps.clear()
+    _maps[key] = (raw, addr)
+    return addr
+
+
+def _ok_operand(t: torch.Tensor) -> bool:
+    return (t.dtype == torch.bfloat16 and t.dim() == 2 and t.stride(1) == 1 and t.stride(0) % 8 == 0
+            and t.data_ptr() % 16 == 0)
 
 
 def accepts(a, w, out, epilogue, w2) -> bool:
-    return False
+    """bfloat16 operands whose rows start on 16-byte boundaries (K and row strides multiples of 8);
+    anything else goes to the CUDA-core kernel."""
+    if not (_ok_operand(a) and _ok_operand(w)) or a.shape[1] % 8 != 0:
+        return False
+    if epilogue == EPI_SWIGLU:
+        return w2 is not None and _ok_operand(w2) and out.dtype == torch.bfloat16
+    if epilogue == EPI_ADD:
+        return out.dtype == torch.float32
+    return out.dtype in (torch.bfloat16, torch.float32)
 
 
-def gemm(a, w, out, epilogue, w2, rt):
-    raise NotImplementedError
+def token_tile(T: int, epilogue: int) -> int:
+    for bn in (16, 32, 64, 128):
+        if T <= bn:
+            return bn
+    if epilogue == EPI_SWIGLU:
+        return 128
+    return 256 if T > 192 else 128
+
+
+def k_splits(T: int, N: int, K: int, bn: int, epilogue: int) -> int:
+    """Slices of K, so that a product with few tiles still fills the GPU.  Only the add-into
+    epilogue is split (its slices meet in the float32 residual stream)."""
+    if epilogue != EPI_ADD:
+        return 1
+    tiles = -(-N // 128) * -(-T // bn)
+    nkb = -(-K // 64)
+    if tiles >= N_SMS or nkb < 16:
+        return 1
+    want = -(-2 * N_SMS // tiles)
+    s = max(1, min(want, nkb // 8, 16))
+    per = -(-nkb // s)
+    return -(-nkb // per)
+
+
+def gemm(a, w, out, epilogue, w2, rt, splits: int | None = None, bn: int | None = None):
+    T, K = a.shape
+    N = w.shape[0]
+    assert w.shape[1] == K and out.shape == (T, N) and out.stride(1) == 1
+    bn = bn or token_tile(T, epilogue)
+    s = splits or k_splits(T, N, K, bn, epilogue)
+    L = lib()
+    mw = _tmap(w, 128)
+    mw2 = _tmap(w2, 128) if w2 is not None else 0
+    ma = _tmap(a, bn)
+    err = rt.status[1:2]
+    rc = L.ub_gemm_tc(mw, mw2, ma, _ptr(out), BF16 if out.dtype == torch.bfloat16 else F32, out.stride(0),
+                      0, T, N, K, bn, epilogue, s, _ptr(err), _stream())
+    _check(rc, "gemm_tc")
+
+
+def check_error(rt) -> None:
+    rt.check_status()

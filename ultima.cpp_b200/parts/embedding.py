@@ -23,7 +23,7 @@ class TokenTable(Part):
 
     def bind(self, tensors, rt):
         self.table = tensors["weight"].contiguous()
-        self.status = torch.zeros(1, dtype=torch.int32, device=rt.device)
+        self.status = rt.status[0:1]
 
     def forward(self, ids, rt):
         x = rt.arena.alloc((ids.numel(), self.width), torch.float32)
