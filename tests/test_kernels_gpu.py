@@ -326,3 +326,72 @@ def test_gemm_tc_views_and_what_it_refuses():
     a2, w2 = a[:, :100].contiguous(), w[:, :100].contiguous()
     rt.matmul(a2, w2, out)
     assert rel_err(out, a2.double() @ w2.double().T) <= 2e-5
+
+
+# ---------------------------------------------------------------------------------------
+# tensor-core attention against the float64 restatement
+# ---------------------------------------------------------------------------------------
+class _KV:
+    def __init__(self, k, v, table, ring, window):
+        self.k, self.v, self.table, self.ring, self.page, self.window = k, v, table, ring, 64, window
+
+
+class _B:
+    pass
+
+
+def _attn_tc_case(nh, nkv, hd, window, befores, news, seed, slices=None, ring_pages=12):
+    """Sequences with ``befores[i]`` cached positions bring ``news[i]`` new tokens."""
+    from ultima_b200.kernels import attn_tc
+    from ultima_b200.engine import Runtime
+    rt = Runtime(DEV, torch.bfloat16)
+    lens = [b + n for b, n in zip(befores, news)]
+    kc, vc, table, dense = _paged(len(lens), lens, nkv, hd, torch.bfloat16, ring_pages, seed)
+    T = sum(news)
+    g = torch.Generator().manual_seed(seed + 1)
+    qkv = torch.randn(T, (nh + 2 * nkv) * hd, generator=g).to(torch.bfloat16).to(DEV)
+    q = qkv[:, :nh * hd]
+    out = torch.full((T, nh * hd), float("nan"), dtype=torch.bfloat16, device=DEV)
+    b = _B()
+    start = [0]
+    for n in news:
+        start.append(start[-1] + n)
+    b.seq_start = torch.tensor(start, dtype=torch.int32, device=DEV)
+    b.seq_before = torch.tensor(befores, dtype=torch.int32, device=DEV)
+    b.n_seqs, b.max_new, b.max_after = len(lens), max(news), max(lens)
+    kv = _KV(kc, vc, table, ring_pages * 64, window or None)
+    assert attn_tc.accepts(q, kv, hd, nh, nkv)
+    attn_tc.attention(q, kv, out, b, nh, nkv, hd, 1 / math.sqrt(hd), rt, slices=slices)
+    torch.cuda.synchronize()
+    worst = 0.0
+    for s, (bf, n) in enumerate(zip(befores, news)):
+        k, v = dense[s]
+        for t in range(n):
+            ref = _attn_ref(q[start[s] + t].double().cpu().view(nh, hd), k.double(), v.double(), bf + t, window, 1 / math.sqrt(hd))
+            got = out[start[s] + t].view(nh, hd)
+            assert torch.isfinite(got).all(), (s, t)
+            worst = max(worst, rel_err(got, ref))
+    return worst
+
+
+@pytest.mark.parametrize("cfg", [dict(nh=8, nkv=2, hd=128, window=0), dict(nh=6, nkv=3, hd=48, window=0),
+                                 dict(nh=8, nkv=1, hd=32, window=0), dict(nh=4, nkv=2, hd=16, window=0),
+                                 dict(nh=6, nkv=2, hd=80, window=50), dict(nh=2, nkv=2, hd=256, window=0),
+                                 dict(nh=5, nkv=5, hd=64, window=130)])
+def test_attn_mma_prefill(cfg):
+    # whole prompts of unequal lengths, and continued prompts (cached positions before the new ones)
+    for befores, news in (([0, 0, 0, 0], [1, 17, 64, 200]), ([5, 64, 130, 0], [70, 1, 33, 129])):
+        err = _attn_tc_case(cfg["nh"], cfg["nkv"], cfg["hd"], cfg["window"], befores, news, seed=cfg["hd"])
+        assert err <= 2 ** -7, (cfg, befores, news, err)
+
+
+@pytest.mark.parametrize("cfg", [dict(nh=8, nkv=2, hd=128, window=0), dict(nh=6, nkv=3, hd=48, window=0),
+                                 dict(nh=8, nkv=1, hd=32, window=0), dict(nh=16, nkv=1, hd=16, window=0),
+                                 dict(nh=6, nkv=2, hd=80, window=50), dict(nh=2, nkv=2, hd=256, window=0),
+                                 dict(nh=32, nkv=1, hd=64, window=0)])
+@pytest.mark.parametrize("slices", [None, 1, 3])
+def test_attn_mma_decode(cfg, slices):
+    # one token a sequence, at unequal lengths: position 0, a page edge, mid page, many pages
+    befores = [0, 63, 64, 300, 700]
+    err = _attn_tc_case(cfg["nh"], cfg["nkv"], cfg["hd"], cfg["window"], befores, [1] * 5, seed=cfg["hd"] + 7, slices=slices)
+    assert err <= 2 ** -7, (cfg, slices, err)

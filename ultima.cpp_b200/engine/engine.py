@@ -60,6 +60,8 @@ class Engine:
             raise RuntimeError("no CUDA device is available; the engine has no CPU path")
         torch.cuda.set_device(self.device)
         self.rt = runtime or Runtime(self.device, self.dtype)
+        from ..kernels import build as _build, catalog as _catalog
+        _build.prebuild(_catalog.targets_for_model(spec, self.dtype))     # nvcc runs side by side
         self.model = Model(spec, tensors, self.rt)
         self.max_tokens = int(max_tokens)
         self.max_context = int(min(max_context or spec.max_positions, spec.max_positions))

@@ -1,12 +1,67 @@
-"""Entry point of the tensor-core attention kernels (csrc/attn_mma.cu)."""
+"""Entry point of the tensor-core attention kernels (csrc/attn_mma.cu), which are compiled
+once for each head size a model uses."""
 from __future__ import annotations
 
-ENABLED = False
+from ctypes import c_float, c_int, c_longlong, c_void_p
+
+import torch
+
+from . import build
+from .ops import KernelError, _check, _ptr, _stream
+
+SOURCE = "attn_mma.cu"
+N_SMS = 148
+_libs: dict = {}
+
+
+def target(head_dim: int):
+    return (SOURCE, (f"HEAD_DIM={int(head_dim)}",))
+
+
+def lib(head_dim: int):
+    L = _libs.get(head_dim)
+    if L is None:
+        L = build.load(*target(head_dim))
+        L.ub_attn_mma.argtypes = [c_int, c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p,
+                                  c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+                                  c_float, c_int, c_void_p, c_void_p, c_void_p]
+        L.ub_attn_mma.restype = c_int
+        L.ub_attn_head_dim.restype = c_int
+        if L.ub_attn_head_dim() != head_dim:
+            raise KernelError(f"attention library was built for head size {L.ub_attn_head_dim()}, not {head_dim}")
+        _libs[head_dim] = L
+    return L
 
 
 def accepts(q, kv, head_dim, n_heads, n_kv_heads) -> bool:
-    return False
+    return (q.dtype == torch.bfloat16 and kv.k.dtype == torch.bfloat16 and head_dim % 16 == 0
+            and 16 <= head_dim <= 256 and kv.page == 64 and q.stride(1) == 1 and q.stride(0) % 8 == 0
+            and q.data_ptr() % 16 == 0)
 
 
-def attention(q, kv, out, batch, n_heads, n_kv_heads, head_dim, scale, rt):
-    raise NotImplementedError
+def decode_slices(n_seqs: int, n_kv_heads: int, longest: int, window) -> int:
+    """Slices of the key range, so that a decode step with few sequences still fills the GPU."""
+    span = longest if not window else min(longest, window + 64)
+    tiles = max(1, -(-span // 64))
+    ctas = n_seqs * n_kv_heads
+    want = -(-2 * N_SMS // ctas)
+    return max(1, min(want, tiles, 64))
+
+
+def attention(q, kv, out, batch, n_heads, n_kv_heads, head_dim, scale, rt, slices: int | None = None):
+    L = lib(head_dim)
+    assert out.dtype == torch.bfloat16 and out.stride(1) == 1
+    group = n_heads // n_kv_heads
+    decode = batch.max_new == 1 and group <= 16
+    part_o = part_ml = None
+    n_slices = 1
+    if decode:
+        n_slices = slices or decode_slices(batch.n_seqs, n_kv_heads, batch.max_after, kv.window)
+        if n_slices > 1:
+            part_o = rt.arena.alloc((batch.n_seqs, n_heads, n_slices, head_dim), torch.float32)
+            part_ml = rt.arena.alloc((batch.n_seqs, n_heads, n_slices, 2), torch.float32)
+    rc = L.ub_attn_mma(1 if decode else 0, _ptr(q), q.stride(0), _ptr(out), out.stride(0), _ptr(kv.k), _ptr(kv.v),
+                       _ptr(batch.seq_start), _ptr(batch.seq_before), _ptr(kv.table), kv.table.shape[1], kv.ring,
+                       kv.page, batch.n_seqs, batch.max_new, n_heads, n_kv_heads, int(kv.window or 0), float(scale),
+                       n_slices, _ptr(part_o), _ptr(part_ml), _stream())
+    _check(rc, "attn_mma")
