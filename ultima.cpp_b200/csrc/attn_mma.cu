@@ -416,3 +416,41 @@ UB_API int ub_attn_mma(int mode, const void* q, long long q_stride, void* out, l
     UB_LAUNCH_CHECK();
     return 0;
 }
+
+// ---------------------------------------------------------------------------------------
+// decode attention without any allocation: see attn_noalloc.h
+// ---------------------------------------------------------------------------------------
+#include "attn_noalloc.h"
+
+// Partial results of the key slices: [o floats | (max, sum) floats].  Part of the library's
+// device image; in host code this name is only a handle, never a device address.
+static __device__ __align__(256) float g_noalloc_scratch[UB_NOALLOC_SCRATCH_O_FLOATS + UB_NOALLOC_SCRATCH_ML_FLOATS];
+
+constexpr int NOALLOC_MAX_DEVICES = 64;
+static float* g_noalloc_ptr[NOALLOC_MAX_DEVICES] = {};
+
+UB_API int ub_attn_decode_noalloc(const void* q, long long q_stride, void* out, long long o_stride, const void* kcache,
+                                  const void* vcache, const int* seq_start, const int* seq_before, const int* table,
+                                  int pages_per_seq, int ring, int page, int n_seqs, int nh, int nkv, int window,
+                                  float scale, int n_slices, cudaStream_t st) {
+    if (n_seqs <= 0) return 0;
+    if (n_slices < 1 || nh < 1) return UB_ERR_ARG;
+    const long long parts = (long long)n_seqs * nh * n_slices;
+    if (parts * HD > UB_NOALLOC_SCRATCH_O_FLOATS || parts * 2 > UB_NOALLOC_SCRATCH_ML_FLOATS) return UB_ERR_NOALLOC_TOO_LARGE;
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return (int)e;
+    if (dev < 0 || dev >= NOALLOC_MAX_DEVICES) return UB_ERR_ARG;
+    if (!g_noalloc_ptr[dev]) {
+        // set-up, once a device, with that device current: the array's address on this device
+        float* ptr = nullptr;
+        e = cudaGetSymbolAddress((void**)&ptr, g_noalloc_scratch);
+        if (e != cudaSuccess) return (int)e;
+        if (!ptr) return UB_ERR_ARG;
+        g_noalloc_ptr[dev] = ptr;
+    }
+    float* part_o = g_noalloc_ptr[dev];
+    float* part_ml = part_o + UB_NOALLOC_SCRATCH_O_FLOATS;
+    return ub_attn_mma(1, q, q_stride, out, o_stride, kcache, vcache, seq_start, seq_before, table, pages_per_seq, ring,
+                       page, n_seqs, 1, nh, nkv, window, scale, n_slices, part_o, part_ml, st);
+}
