@@ -131,7 +131,7 @@ def timed_decode(engine, sampler, batch, steps, warmup, rng, real_prefill):
     prm = sampler_params(sampler, params, engine.device)
 
     def one(i):
-        logits = engine.step(slots, [[int(t)] for t in toks[i]], None)
+        logits = engine.step(slots, [[int(t)] for t in toks[i]], None, borrow=True)
         sampler_launch(logits, prm, out_ids)
     for i in range(warmup):
         one(i)
@@ -196,6 +196,15 @@ def run_ours(args):
     engine.warm_up()
     print(f"[bench] model ready in {time.time() - t0:.1f} s", file=sys.stderr, flush=True)
 
+    if args.only == "decode":
+        ms, launches, ctx = timed_decode(engine, sampler, args.batch, args.steps, args.warmup, rng,
+                                         real_prefill=not args.fast_fill)
+        engine.check_errors()
+        print(json.dumps({"only": "decode", "batch": args.batch, "layers": cfg.num_hidden_layers,
+                          "ms_per_step": round(ms / args.steps, 4), "context": int(ctx),
+                          "value": round(args.batch * args.steps / ms * 1e3, 1), "gpu_launches": int(launches)}))
+        return 0
+
     # prefill of one 2,048-token prompt
     prompt = rng.integers(0, cfg.vocab_size, size=PREFILL_TOKENS).tolist()
     pre_ms = []
@@ -215,6 +224,10 @@ def run_ours(args):
     prefill = {"value": round(PREFILL_TOKENS / pms * 1e3, 1), "tokens": PREFILL_TOKENS, "ms": round(pms, 3),
                "frac": round(pf / (pms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)}
     print(f"[bench] prefill {prefill}", file=sys.stderr, flush=True)
+    if args.only == "prefill":
+        engine.check_errors()
+        print(json.dumps({"only": "prefill", "layers": cfg.num_hidden_layers, **prefill}))
+        return 0
 
     clocks = ClockSampler()
     clocks.start()
@@ -244,6 +257,7 @@ def run_ours(args):
     e2e = {"value": round(e2e_val, 1), "unit": "tokens/s", "h2d_bytes_per_step": int(h2d),
            "d2h_bytes_per_step": 4 * BATCH}
 
+    engine.check_errors()
     out = {
         "metric": "decode tokens/s, Qwen3-8B sizes, bf16, batch 8, 2048-token prompts",
         "value": round(value, 1), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps,
@@ -280,6 +294,10 @@ def main():
     ap.add_argument("--warmup", type=int, default=4)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--layers", type=int, default=0, help="fewer layers than the configuration (named in config)")
+    ap.add_argument("--only", default="all", choices=["all", "prefill", "decode"],
+                    help="a part of the run only (for profiling); the JSON line then holds that part")
+    ap.add_argument("--batch", type=int, default=BATCH, help="sequences of the decode step")
+    ap.add_argument("--fast-fill", action="store_true", help="do not run the prompts; mark the cache as filled")
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference(args)

@@ -3,7 +3,8 @@
 A step brings, for each of its sequences, some new tokens that follow what the sequence's
 slot already holds.  Tokens of all sequences are packed one after another; for every token
 the kernels get its id, its absolute position and the index of its sequence in the step,
-and for every sequence its first row, its length before the step and its slot.
+and for every sequence its first row, its length before the step and its slot.  All of it
+is one int32 record, written into pinned host memory and moved to the device in one copy.
 """
 from __future__ import annotations
 
@@ -30,17 +31,51 @@ class StepBatch:
     host: dict = field(default_factory=dict)
 
 
-def build_step_batch(slots, new_tokens, before, want_rows, tables_np, device, pin=None) -> StepBatch:
+class PinnedRing:
+    """A few pinned host buffers used in turn for the step records.  A buffer is written again
+    only after the copy that last read it has finished (an event recorded behind that copy)."""
+
+    def __init__(self, device, n_buffers: int = 4, n_ints: int = 1 << 14):
+        self.device = device
+        self.n = n_buffers
+        self.size = n_ints
+        self.bufs = [None] * n_buffers
+        self.events = [None] * n_buffers
+        self.next = 0
+
+    def take(self, n_ints: int):
+        i = self.next
+        self.next = (i + 1) % self.n
+        if self.events[i] is not None:
+            self.events[i].synchronize()
+        if self.bufs[i] is None or self.bufs[i].numel() < n_ints:
+            size = max(self.size, 1 << (max(n_ints, 1) - 1).bit_length())
+            self.bufs[i] = torch.empty(size, dtype=torch.int32).pin_memory()
+        return i, self.bufs[i]
+
+    def copied(self, i: int) -> None:
+        if self.events[i] is None:
+            self.events[i] = torch.cuda.Event()
+        self.events[i].record()
+
+
+def build_step_batch(slots, new_tokens, before, want_rows, tables_np, device, ring: PinnedRing | None = None,
+                     static: torch.Tensor | None = None) -> StepBatch:
     """slots: slot of each sequence; new_tokens: list of int sequences; before: positions
     already held; want_rows: rows (in the packed order) whose logits are wanted;
-    tables_np: per KV group an int32 array [B, pages]."""
+    tables_np: per KV group an int32 array [B, pages].  ``static``: a device buffer to fill
+    instead of a fresh one (the same layout step after step, for a captured graph)."""
     B = len(slots)
     lens = np.fromiter((len(t) for t in new_tokens), dtype=np.int64, count=B)
     T = int(lens.sum())
     start = np.zeros(B + 1, dtype=np.int32)
     np.cumsum(lens, out=start[1:])
-    ids = np.concatenate([np.asarray(t, dtype=np.int32) for t in new_tokens]) if T else np.zeros(0, np.int32)
-    seq = np.repeat(np.arange(B, dtype=np.int32), lens)
+    if T == B:                      # one token a sequence
+        ids = np.fromiter((t[0] for t in new_tokens), dtype=np.int32, count=B)
+        seq = np.arange(B, dtype=np.int32)
+    else:
+        ids = np.concatenate([np.asarray(t, dtype=np.int32) for t in new_tokens]) if T else np.zeros(0, np.int32)
+        seq = np.repeat(np.arange(B, dtype=np.int32), lens)
     before = np.asarray(before, dtype=np.int32)
     pos = (np.arange(T, dtype=np.int32) - start[:-1][seq] + before[seq]).astype(np.int32)
     want = np.asarray(want_rows, dtype=np.int32)
@@ -52,19 +87,31 @@ def build_step_batch(slots, new_tokens, before, want_rows, tables_np, device, pi
     for s in sizes:
         offs.append(o)
         o += -(-s // 4) * 4
-    flat = np.zeros(max(o, 4), dtype=np.int32)
-    for p, off in zip(parts, offs):
-        flat[off:off + p.size] = p
-    host = torch.from_numpy(flat)
+    total = max(o, 4)
     if device.type == "cuda":
-        host = host.pin_memory()
-        dev = host.to(device, non_blocking=True)
+        if ring is None:
+            ring = PinnedRing(device, 1, total)
+        idx, host = ring.take(total)
+        flat = host.numpy()
+        for p, off in zip(parts, offs):
+            flat[off:off + p.size] = p
+        if static is not None:
+            if static.numel() < total:
+                raise ValueError("static step record is too small")
+            dev = static
+            dev[:total].copy_(host[:total], non_blocking=True)
+        else:
+            dev = host[:total].to(device, non_blocking=True)
+        ring.copied(idx)
     else:
-        dev = host
+        flat = np.zeros(total, dtype=np.int32)
+        for p, off in zip(parts, offs):
+            flat[off:off + p.size] = p
+        dev = torch.from_numpy(flat)
     views = [dev[off:off + s] for off, s in zip(offs, sizes)]
     tables = [views[7 + i].view(B, tables_np[i].shape[1]) for i in range(len(tables_np))]
     return StepBatch(n_tokens=T, n_seqs=B, tok_ids=views[0], tok_pos=views[1], tok_seq=views[2],
                      seq_start=views[3], seq_before=views[4], seq_slot=views[5], want_rows=views[6],
                      tables=tables, max_new=int(lens.max()) if B else 0,
                      max_after=int((lens + before).max()) if B else 0,
-                     host={"lens": lens, "before": before, "pinned": host})
+                     host={"lens": lens, "before": before, "n_ints": total})

@@ -20,7 +20,7 @@ from ..cache import Cache, CacheError, PAGE
 from ..config.base import config_from_dir, find_architecture
 from ..parts.base import KVNeed, ModelSpec
 from ..weights import load_weights
-from .batch import build_step_batch
+from .batch import PinnedRing, build_step_batch
 from .model import Model
 from .runtime import Runtime
 
@@ -50,7 +50,8 @@ class Engine:
 
     def __init__(self, spec: ModelSpec, tensors: dict, dtype="bfloat16", max_tokens: int = 4096,
                  max_seqs: int | None = None, max_step_tokens: int = 4096, device="cuda:0",
-                 max_context: int | None = None, poison_cache: bool = False, runtime=None):
+                 max_context: int | None = None, poison_cache: bool = False, runtime=None,
+                 use_graphs: bool = True):
         self.spec = spec
         self.dtype = _dtype_of(dtype)
         self.device = torch.device(device)
@@ -76,6 +77,14 @@ class Engine:
         self.cache = Cache(needs, self.model.cache_sources(), self.max_tokens, self.max_context,
                            n_slots, self.seq_chunk, dtype=self.rt.cache_dtype, device=self.device,
                            poison=poison_cache)
+        self._ring = PinnedRing(self.device)
+        self.last_h2d_bytes = 0
+        # decode steps (one token a sequence, every logit wanted) are captured as CUDA graphs,
+        # one for each (number of sequences, slices of the key range); parts must allow it
+        self.use_graphs = bool(use_graphs) and all(
+            getattr(L.mixer, "graph_safe", False) and getattr(L.feed_forward, "graph_safe", False)
+            for L in self.model.layers)
+        self._graphs: dict = {}
 
     # ---- construction ------------------------------------------------------------------
     @classmethod
@@ -131,10 +140,13 @@ class Engine:
         return self.cache.length(slot)
 
     # ---- the step ----------------------------------------------------------------------
-    def step(self, slots, tokens, want=None) -> torch.Tensor:
+    def step(self, slots, tokens, want=None, borrow: bool = False) -> torch.Tensor:
         """slots[i] continues with tokens[i]; want[i] lists the places among tokens[i] whose
         logits are asked for (None: the last of each).  Returns float32 [sum(len(want[i])),
-        vocabulary] on the device, in the order of the entries and of ``want``."""
+        vocabulary] on the device, in the order of the entries and of ``want``.
+        ``borrow``: the caller reads the result before the next step and needs no copy of its own
+        (a captured decode step writes its logits to the same memory every time)."""
+        self._borrow = borrow
         B = len(slots)
         if len(tokens) != B:
             raise StepError("step: one token list for each slot is needed")
@@ -218,10 +230,49 @@ class Engine:
         """One pass through the layers: reserve pages, lay the batch out, run, commit."""
         for s, t, b in zip(slots, new_tokens, before):
             self.cache.reserve(s, b + len(t))
-        batch = build_step_batch(slots, new_tokens, before, want_rows, self.cache.tables(slots),
-                                 self.device)
-        self.last_h2d_bytes = batch.host["pinned"].numel() * 4
-        logits = self.model.forward(batch, self.cache)
+        B = len(slots)
+        tables = self.cache.tables(slots)
+        decode = self.use_graphs and all(len(t) == 1 for t in new_tokens) and list(want_rows) == list(range(B))
+        if decode:
+            logits = self._decode_pass(slots, new_tokens, before, want_rows, tables)
+        else:
+            batch = build_step_batch(slots, new_tokens, before, want_rows, tables, self.device, self._ring)
+            self.last_h2d_bytes = batch.host["n_ints"] * 4
+            logits = self.model.forward(batch, self.cache)
         for s, t in zip(slots, new_tokens):
             self.cache.commit(s, len(t))
         return logits
+
+    def _decode_key(self, B: int, longest: int):
+        """What a captured decode step depends on besides the record it reads: the number of
+        sequences and, through the slices of the key range, the length of the longest one."""
+        from ..kernels import attn_tc
+        key = [B]
+        for g in self.cache.kv_groups:
+            key.append(attn_tc.decode_slices(B, g.need.n_kv_heads, longest, g.need.window))
+        return tuple(key)
+
+    def _decode_pass(self, slots, new_tokens, before, want_rows, tables) -> torch.Tensor:
+        B = len(slots)
+        longest = max(before) + 1
+        key = self._decode_key(B, longest)
+        entry = self._graphs.get(key)
+        if entry is None:
+            n_ints = 8 * (-(-(B + 1) // 4) * 4) + sum(-(-t.size // 4) * 4 for t in tables)
+            static = torch.zeros(n_ints, dtype=torch.int32, device=self.device)
+            batch = build_step_batch(slots, new_tokens, before, want_rows, tables, self.device, self._ring, static)
+            self.model.forward(batch, self.cache)              # warm: libraries, tensor maps, scratch
+            torch.cuda.synchronize(self.device)
+            graph = torch.cuda.CUDAGraph()
+            l0 = self.rt.launches
+            with torch.cuda.graph(graph):
+                logits = self.model.forward(batch, self.cache)
+            entry = (graph, static, logits, batch, self.rt.launches - l0)
+            self.rt.launches = l0
+            self._graphs[key] = entry
+        graph, static, logits, _, n_launch = entry
+        batch = build_step_batch(slots, new_tokens, before, want_rows, tables, self.device, self._ring, static)
+        self.last_h2d_bytes = batch.host["n_ints"] * 4
+        graph.replay()
+        self.rt.launches += n_launch
+        return logits if getattr(self, "_borrow", False) else logits.clone()

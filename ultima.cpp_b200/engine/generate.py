@@ -81,6 +81,7 @@ def run_batch(engine, sample, prompts: list, params: list, n_predict: list, stop
         if not live:
             return out
         t0 = time.perf_counter()
+        borrow = {"borrow": True} if getattr(engine, "use_graphs", False) else {}
         logits = engine.step([slots[i] for i in live], [prompts[i] for i in live], None)
         if stats:
             stats.prompt_tokens += sum(len(prompts[i]) for i in live)
@@ -117,7 +118,7 @@ def run_batch(engine, sample, prompts: list, params: list, n_predict: list, stop
             live = going
             if not live:
                 break
-            logits = engine.step([slots[i] for i in live], feed, None)
+            logits = engine.step([slots[i] for i in live], feed, None, **borrow)
         return out
     finally:
         if stats:

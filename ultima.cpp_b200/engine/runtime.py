@@ -23,11 +23,13 @@ class Arena:
         self._buf = torch.empty(max(nbytes, 1 << 16), dtype=torch.uint8, device=device)
         self._off = 0
         self.high_water = 0
+        self._retired = []          # earlier buffers stay alive: captured graphs may point into them
 
     def reserve(self, nbytes: int) -> None:
         if nbytes > self._buf.numel():
             if self._off != 0:
                 raise RuntimeError("arena can grow only when empty")
+            self._retired.append(self._buf)
             self._buf = torch.empty(nbytes, dtype=torch.uint8, device=self.device)
 
     def mark(self) -> int:
@@ -44,6 +46,7 @@ class Arena:
         start = -(-self._off // self.ALIGN) * self.ALIGN
         if start + nbytes > self._buf.numel():
             size = max(2 * self._buf.numel(), start + nbytes + (1 << 20))
+            self._retired.append(self._buf)
             self._buf = torch.empty(size, dtype=torch.uint8, device=self.device)
             start = 0
         self._off = start + nbytes

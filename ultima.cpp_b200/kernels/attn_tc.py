@@ -45,7 +45,8 @@ def decode_slices(n_seqs: int, n_kv_heads: int, longest: int, window) -> int:
     tiles = max(1, -(-span // 64))
     ctas = n_seqs * n_kv_heads
     want = -(-2 * N_SMS // ctas)
-    return max(1, min(want, tiles, 64))
+    n = max(1, min(want, tiles, 64))
+    return 1 << (n.bit_length() - 1)            # a power of two: few distinct captured graphs
 
 
 def attention(q, kv, out, batch, n_heads, n_kv_heads, head_dim, scale, rt, slices: int | None = None):

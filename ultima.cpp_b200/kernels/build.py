@@ -120,6 +120,7 @@ def ensure_built(targets: list[tuple]) -> dict:
                 errors.append(f"nvcc failed on {source}:\n{log}")
                 continue
             os.replace(tmp, path)
+            _drop_stale(path)
             _say(f"built {os.path.basename(path)} after {time.time() - t0:.0f} s")
         if pending and time.time() - last > 5:
             last = time.time()
@@ -129,6 +130,18 @@ def ensure_built(targets: list[tuple]) -> dict:
     if errors:
         raise BuildError("\n".join(errors))
     return out
+
+
+def _drop_stale(path: str) -> None:
+    """Remove earlier builds of the same source and defines (other hashes)."""
+    d, name = os.path.split(path)
+    stem = name.rsplit("-", 1)[0]
+    for f in os.listdir(d):
+        if f != name and f.endswith(".so") and f.rsplit("-", 1)[0] == stem:
+            try:
+                os.remove(os.path.join(d, f))
+            except OSError:
+                pass
 
 
 def load(source: str, defines: tuple = ()) -> ctypes.CDLL:

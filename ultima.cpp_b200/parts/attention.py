@@ -23,6 +23,9 @@ class Attention(Mixer):
     The three projections are held as one matrix [q | k | v] and run as one product.
     """
 
+    graph_safe = True        # launches kernels only; no host work that depends on the data
+
+
     def __init__(self, width: int, n_heads: int, n_kv_heads: int, head_dim: int, qk_norm: bool,
                  eps: float, position: PartSpec | None, window: int | None = None,
                  scale: float | None = None):

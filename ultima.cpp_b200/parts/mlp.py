@@ -15,6 +15,9 @@ class GatedSiLU(FeedForward):
     Gate and up are held as one matrix [gate ; up]; the gate product is formed in float32
     from the float32 accumulators and rounded once."""
 
+    graph_safe = True        # launches kernels only; no host work that depends on the data
+
+
     def __init__(self, width: int, inner: int):
         self.width, self.inner = int(width), int(inner)
         self.wgu = self.wd = None
