@@ -252,8 +252,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                         TO* dst = out + (long long)t * p.ldo + n;
                         if (EPI == EPI_STORE) *dst = from_f32<TO>(v);
                         else if (EPI == EPI_ADD) {
-                            if (p.atomic) atomicAdd((float*)dst, v);
-                            else *(float*)dst += v;
+                            // a reduction at the memory side: no load, no wait; one writer an element
+                            // unless K is split, so the sum's order is fixed in that case
+                            asm volatile("red.global.add.f32 [%0], %1;" ::"l"(dst), "f"(v) : "memory");
                         } else {
                             const float u = __uint_as_float(r2[c]);
                             *dst = from_f32<TO>(v / (1.0f + expf(-v)) * u);
