@@ -190,6 +190,7 @@ struct AttnParams {
 __global__ void __launch_bounds__(NTHREADS)
 attn_prefill_kernel(AttnParams p, PagedKV c) {
     extern __shared__ __align__(16) uint8_t smem_raw[];
+    pdl_trigger();
     bf16* Qs = (bf16*)smem_raw;                    // [64][LDS]
     bf16* Ks = Qs + 64 * LDS;                      // [2][64][LDS]
     bf16* Vs = Ks + 2 * KT * LDS;                  // [2][64][LDS]
@@ -267,6 +268,7 @@ attn_prefill_kernel(AttnParams p, PagedKV c) {
 __global__ void __launch_bounds__(NTHREADS)
 attn_decode_kernel(AttnParams p, PagedKV c) {
     extern __shared__ __align__(16) uint8_t smem_raw[];
+    pdl_trigger();
     bf16* Qs = (bf16*)smem_raw;                    // [16][LDS]
     bf16* Ks = Qs + 16 * LDS;                      // [2][64][LDS]
     bf16* Vs = Ks + 2 * KT * LDS;
@@ -357,6 +359,7 @@ attn_decode_kernel(AttnParams p, PagedKV c) {
 
 // merge the slices of a decode step: grid (sequences * heads), HD threads (rounded up to a warp)
 __global__ void attn_combine_kernel(AttnParams p) {
+    pdl_trigger();
     const int sh = blockIdx.x, d = threadIdx.x;
     const int seq = sh / p.nh, head = sh % p.nh;
     const long long base = (long long)sh * p.n_slices;

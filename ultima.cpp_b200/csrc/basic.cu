@@ -17,6 +17,7 @@
 template <typename TT>
 __global__ void embed_kernel(const TT* __restrict__ table, const int* __restrict__ ids,
                              float* __restrict__ x, int width, int vocab, int* status) {
+    pdl_trigger();
     const int t = blockIdx.x;
     const int id = ids[t];
     const bool ok = id >= 0 && id < vocab;
@@ -46,6 +47,7 @@ template <typename TO>
 __global__ void rmsnorm_kernel(const float* __restrict__ x, const int* __restrict__ rows,
                                const float* __restrict__ w, TO* __restrict__ out, int width, float eps) {
     __shared__ float red[33];
+    pdl_trigger();
     const int r = blockIdx.x;
     const float* xr = x + (long long)(rows ? rows[r] : r) * width;
     float ss = 0.f;
@@ -83,6 +85,7 @@ __global__ void qk_prepare_kernel(TA* __restrict__ qkv, const float* __restrict_
                                   const int* __restrict__ tok_seq, TC* __restrict__ kcache,
                                   TC* __restrict__ vcache, PagedKV c, int n_tokens, int nh, float eps,
                                   int write_kv) {
+    pdl_trigger();
     const int lane = threadIdx.x & 31;
     const long long wid = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     const int heads_all = nh + 2 * c.n_kv_heads;
@@ -150,6 +153,7 @@ UB_API int ub_qk_prepare(void* qkv, int act_dtype, const float* qw, const float*
 // ---------------------------------------------------------------------------------------
 template <typename TI, typename TO>
 __global__ void silu_mul_kernel(const TI* __restrict__ gu, TO* __restrict__ out, long long n, int F) {
+    pdl_trigger();
     const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= n) return;
     const long long t = i / F;

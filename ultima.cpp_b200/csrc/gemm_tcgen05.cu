@@ -131,7 +131,8 @@ struct Smem {
     static constexpr int A_BYTES = BM * BK * 2;
     static constexpr int B_BYTES = BN * BK * 2;
     static constexpr int STAGE_BYTES = A_BYTES * (EPI == EPI_SWIGLU ? 2 : 1) + B_BYTES;
-    static constexpr int BUDGET = 200 * 1024;
+    // token tiles of up to 64 leave room for two CTAs on an SM (this kernel's and the next one's)
+    static constexpr int BUDGET = (BN <= 64 ? 110 : 200) * 1024;
     static constexpr int STAGES_RAW = BUDGET / STAGE_BYTES;
     static constexpr int STAGES = STAGES_RAW > 10 ? 10 : STAGES_RAW;
     static constexpr int TOTAL = STAGES * STAGE_BYTES + 1024 /*alignment*/ + 256 /*barriers*/;
@@ -140,7 +141,7 @@ struct Smem {
 };
 
 template <int BN, int EPI, typename TO>
-__global__ void __launch_bounds__(NUM_THREADS, 1)
+__global__ void __launch_bounds__(NUM_THREADS)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_w2,
                const __grid_constant__ CUtensorMap map_a, GemmParams p) {
     using S = Smem<BN, EPI>;
@@ -175,12 +176,29 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    pdl_trigger();                                       // the next kernel may begin its own prologue
 
     if (warp == 0) {
         // ---------------- producer ----------------
+        // Weights do not depend on the kernel before this one: their loads start at once and fill
+        // the ring while that kernel still runs.  Activations are loaded after it has ended.
         if (lane == 0) {
             int armed = 0;
-            for (int i = 0; i < nkb; ++i) {
+            const int pre = min(nkb, S::STAGES);
+            for (int i = 0; i < pre; ++i) {                 // fresh barriers: nothing to wait for
+                uint8_t* st = smem + i * S::STAGE_BYTES;
+                mbar_expect_tx(&full[i], S::STAGE_BYTES);
+                const int kx = (kb0 + i) * BK;
+                tma_load_2d(st, &map_w, &full[i], kx, n0);
+                if (EPI == EPI_SWIGLU) tma_load_2d(st + S::A_BYTES, &map_w2, &full[i], kx, n0);
+            }
+            pdl_wait();
+            for (int i = 0; i < pre; ++i) {
+                uint8_t* st = smem + i * S::STAGE_BYTES;
+                tma_load_2d(st + S::A_BYTES * (EPI == EPI_SWIGLU ? 2 : 1), &map_a, &full[i], (kb0 + i) * BK, t0);
+                armed = i + 1;
+            }
+            for (int i = pre; i < nkb; ++i) {
                 const int s = i % S::STAGES;
                 const uint32_t ph = (i / S::STAGES) & 1;
                 if (!mbar_wait(&empty[s], ph ^ 1, err)) break;
@@ -231,6 +249,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         // ---------------- epilogue: warps 2..5 ----------------
         const int q = warp & 3;                          // the lanes this warp may read: 32 q .. 32 q + 31
         const int n = n0 + q * 32 + lane;                // this thread's weight row = output column
+        pdl_wait();                                      // the output may be read by the kernel before
         bool ok = nkb > 0 ? mbar_wait(acc_full, 0, err) : true;
         tc_fence_after();
         if (ok && nkb > 0) {
@@ -306,6 +325,9 @@ UB_API int ub_tmap_bf16_2d(void* out_map, const void* base, long long rows, long
     return r == CUDA_SUCCESS ? 0 : UB_ERR_ARG;
 }
 
+static int g_use_pdl = 1;
+UB_API void ub_gemm_tc_set_pdl(int on) { g_use_pdl = on ? 1 : 0; }
+
 template <int BN, int EPI, typename TO>
 static int launch_one(const CUtensorMap* mw, const CUtensorMap* mw2, const CUtensorMap* ma, const GemmParams& p,
                       int splits, cudaStream_t st) {
@@ -319,8 +341,18 @@ static int launch_one(const CUtensorMap* mw, const CUtensorMap* mw2, const CUten
     }
     dim3 grid((p.N + BM - 1) / BM, (p.T + BN - 1) / BN, splits);
     if (grid.y > 65535 || grid.z > 65535) return UB_ERR_ARG;
-    kern<<<grid, NUM_THREADS, S::TOTAL, st>>>(*mw, *mw2, *ma, p);
-    UB_LAUNCH_CHECK();
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = dim3(NUM_THREADS);
+    cfg.dynamicSmemBytes = S::TOTAL;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = g_use_pdl ? 1 : 0;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, kern, *mw, *mw2, *ma, p);
+    if (e != cudaSuccess) return (int)e;
     return 0;
 }
 

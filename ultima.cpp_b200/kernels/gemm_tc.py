@@ -26,6 +26,11 @@ def lib():
         L.ub_gemm_tc.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_longlong, c_longlong,
                                  c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p]
         L.ub_gemm_tc.restype = c_int
+        L.ub_gemm_tc_set_pdl.argtypes = [c_int]
+        L.ub_gemm_tc_set_pdl.restype = None
+        import os
+        if os.environ.get("ULTIMA_PDL", "1") == "0":       # for measurements: ordinary launches
+            L.ub_gemm_tc_set_pdl(0)
         _lib = L
     return _lib
 
