@@ -191,6 +191,7 @@ __global__ void __launch_bounds__(NTHREADS)
 attn_prefill_kernel(AttnParams p, PagedKV c) {
     extern __shared__ __align__(16) uint8_t smem_raw[];
     pdl_trigger();
+    pdl_wait();
     bf16* Qs = (bf16*)smem_raw;                    // [64][LDS]
     bf16* Ks = Qs + 64 * LDS;                      // [2][64][LDS]
     bf16* Vs = Ks + 2 * KT * LDS;                  // [2][64][LDS]
@@ -269,6 +270,7 @@ __global__ void __launch_bounds__(NTHREADS)
 attn_decode_kernel(AttnParams p, PagedKV c) {
     extern __shared__ __align__(16) uint8_t smem_raw[];
     pdl_trigger();
+    pdl_wait();
     bf16* Qs = (bf16*)smem_raw;                    // [16][LDS]
     bf16* Ks = Qs + 16 * LDS;                      // [2][64][LDS]
     bf16* Vs = Ks + 2 * KT * LDS;
@@ -360,6 +362,7 @@ attn_decode_kernel(AttnParams p, PagedKV c) {
 // merge the slices of a decode step: grid (sequences * heads), HD threads (rounded up to a warp)
 __global__ void attn_combine_kernel(AttnParams p) {
     pdl_trigger();
+    pdl_wait();
     const int sh = blockIdx.x, d = threadIdx.x;
     const int seq = sh / p.nh, head = sh % p.nh;
     const long long base = (long long)sh * p.n_slices;
@@ -407,14 +410,18 @@ UB_API int ub_attn_mma(int mode, const void* q, long long q_stride, void* out, l
         const int tiles = (max_new * p.group + 63) / 64;
         if (tiles < 1) return 0;
         dim3 grid(tiles, n_seqs, nkv);
-        attn_prefill_kernel<<<grid, NTHREADS, sm_pre, st>>>(p, c);
+        cudaError_t e = ub_launch_dependent(attn_prefill_kernel, grid, dim3(NTHREADS), sm_pre, st, p, c);
+        if (e != cudaSuccess) return (int)e;
     } else {
         if (p.group > 16 || max_new != 1) return UB_ERR_ARG;
         if (p.n_slices > 1 && (!part_o || !part_ml)) return UB_ERR_ARG;
         dim3 grid(p.n_slices, n_seqs, nkv);
-        attn_decode_kernel<<<grid, NTHREADS, sm_dec, st>>>(p, c);
-        UB_LAUNCH_CHECK();
-        if (p.n_slices > 1) attn_combine_kernel<<<n_seqs * nh, ((HD + 31) / 32) * 32, 0, st>>>(p);
+        cudaError_t e = ub_launch_dependent(attn_decode_kernel, grid, dim3(NTHREADS), sm_dec, st, p, c);
+        if (e != cudaSuccess) return (int)e;
+        if (p.n_slices > 1) {
+            e = ub_launch_dependent(attn_combine_kernel, dim3(n_seqs * nh), dim3(((HD + 31) / 32) * 32), 0, st, p);
+            if (e != cudaSuccess) return (int)e;
+        }
     }
     UB_LAUNCH_CHECK();
     return 0;

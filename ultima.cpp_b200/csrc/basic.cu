@@ -18,6 +18,7 @@ template <typename TT>
 __global__ void embed_kernel(const TT* __restrict__ table, const int* __restrict__ ids,
                              float* __restrict__ x, int width, int vocab, int* status) {
     pdl_trigger();
+    pdl_wait();
     const int t = blockIdx.x;
     const int id = ids[t];
     const bool ok = id >= 0 && id < vocab;
@@ -31,13 +32,13 @@ UB_API int ub_embed(const void* table, int table_dtype, const int* ids, float* x
                     int width, int vocab, int* status, cudaStream_t st) {
     if (n_tokens <= 0) return 0;
     const int threads = width >= 1024 ? 256 : 128;
+    cudaError_t e;
     if (table_dtype == UB_F32)
-        embed_kernel<float><<<n_tokens, threads, 0, st>>>((const float*)table, ids, x, width, vocab, status);
+        e = ub_launch_dependent(embed_kernel<float>, dim3(n_tokens), dim3(threads), 0, st, (const float*)table, ids, x, width, vocab, status);
     else if (table_dtype == UB_BF16)
-        embed_kernel<__nv_bfloat16><<<n_tokens, threads, 0, st>>>((const __nv_bfloat16*)table, ids, x, width, vocab, status);
+        e = ub_launch_dependent(embed_kernel<__nv_bfloat16>, dim3(n_tokens), dim3(threads), 0, st, (const __nv_bfloat16*)table, ids, x, width, vocab, status);
     else return UB_ERR_UNSUPPORTED;
-    UB_LAUNCH_CHECK();
-    return 0;
+    return (int)e;
 }
 
 // ---------------------------------------------------------------------------------------
@@ -48,6 +49,7 @@ __global__ void rmsnorm_kernel(const float* __restrict__ x, const int* __restric
                                const float* __restrict__ w, TO* __restrict__ out, int width, float eps) {
     __shared__ float red[33];
     pdl_trigger();
+    pdl_wait();
     const int r = blockIdx.x;
     const float* xr = x + (long long)(rows ? rows[r] : r) * width;
     float ss = 0.f;
@@ -62,13 +64,13 @@ UB_API int ub_rmsnorm(const float* x, const int* rows, const float* w, void* out
                       int n_rows, int width, float eps, cudaStream_t st) {
     if (n_rows <= 0) return 0;
     const int threads = width >= 2048 ? 512 : (width >= 512 ? 256 : 128);
+    cudaError_t e;
     if (out_dtype == UB_F32)
-        rmsnorm_kernel<float><<<n_rows, threads, 0, st>>>(x, rows, w, (float*)out, width, eps);
+        e = ub_launch_dependent(rmsnorm_kernel<float>, dim3(n_rows), dim3(threads), 0, st, x, rows, w, (float*)out, width, eps);
     else if (out_dtype == UB_BF16)
-        rmsnorm_kernel<__nv_bfloat16><<<n_rows, threads, 0, st>>>(x, rows, w, (__nv_bfloat16*)out, width, eps);
+        e = ub_launch_dependent(rmsnorm_kernel<__nv_bfloat16>, dim3(n_rows), dim3(threads), 0, st, x, rows, w, (__nv_bfloat16*)out, width, eps);
     else return UB_ERR_UNSUPPORTED;
-    UB_LAUNCH_CHECK();
-    return 0;
+    return (int)e;
 }
 
 // ---------------------------------------------------------------------------------------
@@ -86,6 +88,7 @@ __global__ void qk_prepare_kernel(TA* __restrict__ qkv, const float* __restrict_
                                   TC* __restrict__ vcache, PagedKV c, int n_tokens, int nh, float eps,
                                   int write_kv) {
     pdl_trigger();
+    pdl_wait();
     const int lane = threadIdx.x & 31;
     const long long wid = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     const int heads_all = nh + 2 * c.n_kv_heads;
@@ -137,15 +140,15 @@ UB_API int ub_qk_prepare(void* qkv, int act_dtype, const float* qw, const float*
     const long long warps = (long long)n_tokens * (nh + 2 * nkv);
     const int wpb = 8;
     const unsigned grid = (unsigned)((warps + wpb - 1) / wpb);
-#define LAUNCH(TA, TC) qk_prepare_kernel<TA, TC><<<grid, wpb * 32, 0, st>>>((TA*)qkv, qw, kw, cs, sn, \
+    cudaError_t e;
+#define LAUNCH(TA, TC) e = ub_launch_dependent(qk_prepare_kernel<TA, TC>, dim3(grid), dim3(wpb * 32), 0, st, (TA*)qkv, qw, kw, cs, sn, \
         tok_pos, tok_seq, (TC*)kcache, (TC*)vcache, c, n_tokens, nh, eps, write_kv)
     if (act_dtype == UB_F32 && cache_dtype == UB_F32) LAUNCH(float, float);
     else if (act_dtype == UB_BF16 && cache_dtype == UB_BF16) LAUNCH(__nv_bfloat16, __nv_bfloat16);
     else if (act_dtype == UB_F32 && cache_dtype == UB_BF16) LAUNCH(float, __nv_bfloat16);
     else return UB_ERR_UNSUPPORTED;
 #undef LAUNCH
-    UB_LAUNCH_CHECK();
-    return 0;
+    return (int)e;
 }
 
 // ---------------------------------------------------------------------------------------

@@ -132,7 +132,7 @@ struct Smem {
     static constexpr int B_BYTES = BN * BK * 2;
     static constexpr int STAGE_BYTES = A_BYTES * (EPI == EPI_SWIGLU ? 2 : 1) + B_BYTES;
     // token tiles of up to 64 leave room for two CTAs on an SM (this kernel's and the next one's)
-    static constexpr int BUDGET = (BN <= 64 ? 110 : 200) * 1024;
+    static constexpr int BUDGET = (BN <= 64 && EPI != EPI_SWIGLU ? 110 : 200) * 1024;
     static constexpr int STAGES_RAW = BUDGET / STAGE_BYTES;
     static constexpr int STAGES = STAGES_RAW > 10 ? 10 : STAGES_RAW;
     static constexpr int TOTAL = STAGES * STAGE_BYTES + 1024 /*alignment*/ + 256 /*barriers*/;

@@ -11,6 +11,8 @@ from .ops import KernelError, _check, _ptr, _stream
 
 SOURCE = "attn_mma.cu"
 N_SMS = 148
+import os as _os
+SLICE_FACTOR = int(_os.environ.get("ULTIMA_SLICE_FACTOR", "2"))
 _libs: dict = {}
 
 
@@ -44,7 +46,7 @@ def decode_slices(n_seqs: int, n_kv_heads: int, longest: int, window) -> int:
     span = longest if not window else min(longest, window + 64)
     tiles = max(1, -(-span // 64))
     ctas = n_seqs * n_kv_heads
-    want = -(-2 * N_SMS // ctas)
+    want = -(-SLICE_FACTOR * N_SMS // ctas)
     n = max(1, min(want, tiles, 64))
     return 1 << (n.bit_length() - 1)            # a power of two: few distinct captured graphs
 

@@ -79,17 +79,24 @@ def token_tile(T: int, epilogue: int) -> int:
     return 256 if T > 192 else 128
 
 
+def cta_slots(bn: int, epilogue: int) -> int:
+    """CTAs of this kernel that the GPU holds at once: two an SM for token tiles of up to 64 (their
+    shared-memory ring is kept to half an SM's), one otherwise."""
+    return 2 * N_SMS if (bn <= 64 and epilogue != EPI_SWIGLU) else N_SMS
+
+
 def k_splits(T: int, N: int, K: int, bn: int, epilogue: int) -> int:
-    """Slices of K, so that a product with few tiles still fills the GPU.  Only the add-into
-    epilogue is split (its slices meet in the float32 residual stream)."""
+    """Slices of K, so that a product with few tiles still fills the GPU, and never more CTAs than
+    the GPU holds at once (a second wave would start only when the first has ended).  Only the
+    add-into epilogue is split here (its slices meet in the float32 residual stream)."""
     if epilogue != EPI_ADD:
         return 1
     tiles = -(-N // 128) * -(-T // bn)
     nkb = -(-K // 64)
-    if tiles >= N_SMS or nkb < 16:
+    slots = cta_slots(bn, epilogue)
+    if tiles * 2 > slots or nkb < 8:
         return 1
-    want = -(-2 * N_SMS // tiles)
-    s = max(1, min(want, nkb // 8, 16))
+    s = max(1, min(slots // tiles, nkb // 4))
     per = -(-nkb // s)
     return -(-nkb // per)
 
