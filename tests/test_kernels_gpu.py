@@ -395,3 +395,64 @@ def test_attn_mma_decode(cfg, slices):
     befores = [0, 63, 64, 300, 700]
     err = _attn_tc_case(cfg["nh"], cfg["nkv"], cfg["hd"], cfg["window"], befores, [1] * 5, seed=cfg["hd"] + 7, slices=slices)
     assert err <= 2 ** -7, (cfg, slices, err)
+
+
+def test_gemm_tc_partial_products_and_their_consumers():
+    """K cut into slices written side by side; qk_prepare and silu_mul add the slices up."""
+    gemm_tc, rt = _tc()
+    ops = _ops()
+    g = torch.Generator().manual_seed(4)
+    T, K, nh, nkv, hd = 5, 1024, 4, 2, 32
+    N = (nh + 2 * nkv) * hd
+    a = torch.randn(T, K, generator=g).to(torch.bfloat16).to(DEV)
+    w = (torch.randn(N, K, generator=g) * 0.05).to(torch.bfloat16).to(DEV)
+    parts = torch.full((4, T, N), float("nan"), device=DEV)
+    gemm_tc.gemm(a, w, parts, ops.EPI_STORE, None, rt, splits=4)
+    ref = a.double() @ w.double().T
+    assert rel_err(parts.sum(0), ref) <= 1e-4
+    assert gemm_tc.store_splits(8, 6144, 4096) > 1 and gemm_tc.store_splits(2048, 6144, 4096) == 1
+    # qk_prepare over the slices == qk_prepare over their sum
+    table = torch.tensor([[0], [1]], dtype=torch.int32, device=DEV)
+    pos = torch.tensor([0, 1, 2, 0, 1], dtype=torch.int32, device=DEV)
+    seq = torch.tensor([0, 0, 0, 1, 1], dtype=torch.int32, device=DEV)
+    qw = (1 + 0.1 * torch.randn(hd, generator=g)).to(DEV)
+    kw = (1 + 0.1 * torch.randn(hd, generator=g)).to(DEV)
+    cos = torch.cos(torch.arange(8)[:, None] * torch.arange(hd // 2)[None] * 0.1).float().to(DEV)
+    sin = torch.sin(torch.arange(8)[:, None] * torch.arange(hd // 2)[None] * 0.1).float().to(DEV)
+    outs = []
+    for src in (parts, parts.sum(0).contiguous()):
+        kc = torch.zeros(2, nkv, 64, hd, dtype=torch.bfloat16, device=DEV)
+        vc = torch.zeros_like(kc)
+        q = torch.zeros(T, nh * hd, dtype=torch.bfloat16, device=DEV)
+        ops.qk_prepare(src, qw, kw, cos, sin, pos, seq, kc, vc, table, 64, 64, nh, nkv, hd, 1e-6, q_out=q)
+        outs.append((q, kc, vc))
+    for x, y in zip(outs[0], outs[1]):
+        assert rel_err(x, y.double()) <= 2 ** -7
+    assert float(outs[0][0].abs().sum()) > 0 and float(outs[0][1].abs().sum()) > 0
+    # silu_mul over slices
+    F = 96
+    gu = torch.randn(3, T, 2 * F, generator=g).to(DEV)
+    out = torch.empty(T, F, dtype=torch.bfloat16, device=DEV)
+    ops.silu_mul(gu, out)
+    sd = gu.double().sum(0)
+    assert rel_err(out, sd[:, :F] / (1 + torch.exp(-sd[:, :F])) * sd[:, F:]) <= 2 ** -8
+
+
+@pytest.mark.parametrize("shape", [(1, 64, 64), (9, 96, 320), (64, 4096, 256), (130, 512, 192), (300, 1024, 640)])
+def test_gemm_tc_interleaved_gate_product(shape):
+    """Blocks of 64 gate rows and 64 up rows alternate in one matrix."""
+    gemm_tc, rt = _tc()
+    ops = _ops()
+    T, K, F = shape
+    g = torch.Generator().manual_seed(F + T)
+    a = torch.randn(T, K, generator=g).to(torch.bfloat16).to(DEV)
+    wg = (torch.randn(F, K, generator=g) * 0.05).to(torch.bfloat16)
+    wu = (torch.randn(F, K, generator=g) * 0.05).to(torch.bfloat16)
+    il = torch.stack([wg.view(F // 64, 64, K), wu.view(F // 64, 64, K)], dim=1).reshape(2 * F, K).contiguous().to(DEV)
+    out = torch.full((T, F), float("nan"), dtype=torch.bfloat16, device=DEV)
+    assert gemm_tc.accepts(a, il, out, ops.EPI_SWIGLU_IL, None)
+    gemm_tc.gemm(a, il, out, ops.EPI_SWIGLU_IL, None, rt)
+    torch.cuda.synchronize()
+    gemm_tc.check_error(rt)
+    gt, up = a.double().cpu() @ wg.double().T, a.double().cpu() @ wu.double().T
+    assert rel_err(out, gt / (1 + torch.exp(-gt)) * up) <= 2 ** -8, shape

@@ -76,12 +76,15 @@ UB_API int ub_rmsnorm(const float* x, const int* rows, const float* w, void* out
 // ---------------------------------------------------------------------------------------
 // per-head norm (optional) + rotation (optional) of q and k, and the write of k and v into
 // the paged cache.  One warp for each (token, head) of the fused [q | k | v] row.
-//   qkv   [T, (nh + 2 nkv) * hd]   q heads are normed and rotated in place
+//   qkv   [parts][T, (nh + 2 nkv) * hd]   the row is the sum of ``n_parts`` partial results
+//                                         (slices of K of the projection), ``part_stride`` apart
+//   q_out [T, *] row stride q_out_stride  normed and rotated q heads (may be qkv itself)
 //   cos, sin  [max_pos, hd/2] float32 (null: no rotation)
 //   qw, kw    [hd] float32 (null: no norm)
 // ---------------------------------------------------------------------------------------
-template <typename TA, typename TC>
-__global__ void qk_prepare_kernel(TA* __restrict__ qkv, const float* __restrict__ qw,
+template <typename TA, typename TQ, typename TC>
+__global__ void qk_prepare_kernel(const TA* qkv, int n_parts, long long part_stride,
+                                  TQ* q_out, long long q_out_stride, const float* __restrict__ qw,
                                   const float* __restrict__ kw, const float* __restrict__ cs,
                                   const float* __restrict__ sn, const int* __restrict__ tok_pos,
                                   const int* __restrict__ tok_seq, TC* __restrict__ kcache,
@@ -95,28 +98,46 @@ __global__ void qk_prepare_kernel(TA* __restrict__ qkv, const float* __restrict_
     if (wid >= (long long)n_tokens * heads_all) return;
     const int t = (int)(wid / heads_all), h = (int)(wid % heads_all);
     const int hd = c.head_dim, half = hd >> 1;
-    TA* row = qkv + ((long long)t * heads_all + h) * hd;
+    const TA* row = qkv + ((long long)t * heads_all + h) * hd;
     const int pos = tok_pos[t];
     const int seq = tok_seq[t];
     if (h >= nh + c.n_kv_heads) {                       // a value head: copy into the cache
         if (!write_kv) return;
         TC* dst = vcache + paged_offset(c, seq, pos, h - nh - c.n_kv_heads);
-        for (int i = lane; i < hd; i += 32) dst[i] = from_f32<TC>(to_f32<TA>(row[i]));
+        for (int i = lane; i < hd; i += 32) {
+            float v = 0.f;
+            for (int p = 0; p < n_parts; ++p) v += to_f32<TA>(row[p * part_stride + i]);
+            dst[i] = from_f32<TC>(v);
+        }
         return;
     }
     const bool is_k = h >= nh;
     if (is_k && !write_kv) return;
     const float* w = is_k ? kw : qw;
+    // a lane's pairs (j, j + half) for j = lane, lane + 32, ...: at most 4 (head sizes up to 256)
+    float va[4], vb[4];
     float ss = 0.f;
-    for (int j = lane; j < half; j += 32) {
-        const float a = to_f32<TA>(row[j]), b = to_f32<TA>(row[j + half]);
-        ss += a * a + b * b;
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+        const int j = lane + u * 32;
+        va[u] = vb[u] = 0.f;
+        if (j < half) {
+            for (int p = 0; p < n_parts; ++p) {
+                va[u] += to_f32<TA>(row[p * part_stride + j]);
+                vb[u] += to_f32<TA>(row[p * part_stride + j + half]);
+            }
+            ss += va[u] * va[u] + vb[u] * vb[u];
+        }
     }
     ss = warp_sum(ss);
     const float inv = w ? 1.0f / sqrtf(ss / (float)hd + eps) : 1.0f;
     TC* dst = is_k ? kcache + paged_offset(c, seq, pos, h - nh) : nullptr;
-    for (int j = lane; j < half; j += 32) {
-        float a = to_f32<TA>(row[j]), b = to_f32<TA>(row[j + half]);
+    TQ* qdst = q_out + (long long)t * q_out_stride + (long long)h * hd;
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+        const int j = lane + u * 32;
+        if (j >= half) continue;
+        float a = va[u], b = vb[u];
         if (w) { a = a * w[j] * inv; b = b * w[j + half] * inv; }
         float ra = a, rb = b;
         if (cs) {
@@ -125,27 +146,30 @@ __global__ void qk_prepare_kernel(TA* __restrict__ qkv, const float* __restrict_
             rb = a * si + b * co;
         }
         if (is_k) { dst[j] = from_f32<TC>(ra); dst[j + half] = from_f32<TC>(rb); }
-        else { row[j] = from_f32<TA>(ra); row[j + half] = from_f32<TA>(rb); }
+        else { qdst[j] = from_f32<TQ>(ra); qdst[j + half] = from_f32<TQ>(rb); }
     }
 }
 
-UB_API int ub_qk_prepare(void* qkv, int act_dtype, const float* qw, const float* kw, const float* cs,
+UB_API int ub_qk_prepare(const void* qkv, int in_dtype, int n_parts, long long part_stride, void* q_out,
+                         int q_dtype, long long q_out_stride, const float* qw, const float* kw, const float* cs,
                          const float* sn, const int* tok_pos, const int* tok_seq, void* kcache,
                          void* vcache, int cache_dtype, const int* table, int pages_per_seq, int ring,
                          int page, int n_tokens, int nh, int nkv, int hd, float eps, int write_kv,
                          cudaStream_t st) {
     if (n_tokens <= 0) return 0;
-    if (hd % 2 != 0 || ring % page != 0) return UB_ERR_ARG;
+    if (hd % 2 != 0 || hd > 256 || ring % page != 0 || n_parts < 1) return UB_ERR_ARG;
     PagedKV c{table, pages_per_seq, ring, page, nkv, hd};
     const long long warps = (long long)n_tokens * (nh + 2 * nkv);
     const int wpb = 8;
     const unsigned grid = (unsigned)((warps + wpb - 1) / wpb);
     cudaError_t e;
-#define LAUNCH(TA, TC) e = ub_launch_dependent(qk_prepare_kernel<TA, TC>, dim3(grid), dim3(wpb * 32), 0, st, (TA*)qkv, qw, kw, cs, sn, \
-        tok_pos, tok_seq, (TC*)kcache, (TC*)vcache, c, n_tokens, nh, eps, write_kv)
-    if (act_dtype == UB_F32 && cache_dtype == UB_F32) LAUNCH(float, float);
-    else if (act_dtype == UB_BF16 && cache_dtype == UB_BF16) LAUNCH(__nv_bfloat16, __nv_bfloat16);
-    else if (act_dtype == UB_F32 && cache_dtype == UB_BF16) LAUNCH(float, __nv_bfloat16);
+#define LAUNCH(TA, TQ, TC) e = ub_launch_dependent(qk_prepare_kernel<TA, TQ, TC>, dim3(grid), dim3(wpb * 32), 0, st, \
+        (const TA*)qkv, n_parts, part_stride, (TQ*)q_out, q_out_stride, qw, kw, cs, sn, tok_pos, tok_seq, \
+        (TC*)kcache, (TC*)vcache, c, n_tokens, nh, eps, write_kv)
+    if (in_dtype == UB_F32 && q_dtype == UB_F32 && cache_dtype == UB_F32) LAUNCH(float, float, float);
+    else if (in_dtype == UB_BF16 && q_dtype == UB_BF16 && cache_dtype == UB_BF16) LAUNCH(__nv_bfloat16, __nv_bfloat16, __nv_bfloat16);
+    else if (in_dtype == UB_F32 && q_dtype == UB_BF16 && cache_dtype == UB_BF16) LAUNCH(float, __nv_bfloat16, __nv_bfloat16);
+    else if (in_dtype == UB_F32 && q_dtype == UB_F32 && cache_dtype == UB_BF16) LAUNCH(float, float, __nv_bfloat16);
     else return UB_ERR_UNSUPPORTED;
 #undef LAUNCH
     return (int)e;
@@ -155,27 +179,37 @@ UB_API int ub_qk_prepare(void* qkv, int act_dtype, const float* qw, const float*
 // out[t, f] = silu(gu[t, f]) * gu[t, F + f]   (gate and up side by side in one row)
 // ---------------------------------------------------------------------------------------
 template <typename TI, typename TO>
-__global__ void silu_mul_kernel(const TI* __restrict__ gu, TO* __restrict__ out, long long n, int F) {
+__global__ void silu_mul_kernel(const TI* __restrict__ gu, int n_parts, long long part_stride, TO* __restrict__ out,
+                                long long n, int F) {
     pdl_trigger();
+    pdl_wait();
     const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= n) return;
     const long long t = i / F;
     const int f = (int)(i % F);
-    const float g = to_f32<TI>(gu[t * 2 * F + f]), u = to_f32<TI>(gu[t * 2 * F + F + f]);
+    float g = 0.f, u = 0.f;
+    for (int p = 0; p < n_parts; ++p) {
+        g += to_f32<TI>(gu[p * part_stride + t * 2 * F + f]);
+        u += to_f32<TI>(gu[p * part_stride + t * 2 * F + F + f]);
+    }
     out[i] = from_f32<TO>(g / (1.0f + expf(-g)) * u);
 }
 
-UB_API int ub_silu_mul(const void* gu, int in_dtype, void* out, int out_dtype, int n_tokens, int F,
-                       cudaStream_t st) {
+// gu: [parts][T, 2F], the sum of the parts is [gate | up]
+UB_API int ub_silu_mul(const void* gu, int in_dtype, int n_parts, long long part_stride, void* out, int out_dtype,
+                       int n_tokens, int F, cudaStream_t st) {
     const long long n = (long long)n_tokens * F;
     if (n <= 0) return 0;
+    if (n_parts < 1) return UB_ERR_ARG;
     const unsigned grid = (unsigned)((n + 255) / 256);
-    if (in_dtype == UB_F32 && out_dtype == UB_F32) silu_mul_kernel<float, float><<<grid, 256, 0, st>>>((const float*)gu, (float*)out, n, F);
-    else if (in_dtype == UB_F32 && out_dtype == UB_BF16) silu_mul_kernel<float, __nv_bfloat16><<<grid, 256, 0, st>>>((const float*)gu, (__nv_bfloat16*)out, n, F);
-    else if (in_dtype == UB_BF16 && out_dtype == UB_BF16) silu_mul_kernel<__nv_bfloat16, __nv_bfloat16><<<grid, 256, 0, st>>>((const __nv_bfloat16*)gu, (__nv_bfloat16*)out, n, F);
+    cudaError_t e;
+#define LAUNCH(TI, TO) e = ub_launch_dependent(silu_mul_kernel<TI, TO>, dim3(grid), dim3(256), 0, st, (const TI*)gu, n_parts, part_stride, (TO*)out, n, F)
+    if (in_dtype == UB_F32 && out_dtype == UB_F32) LAUNCH(float, float);
+    else if (in_dtype == UB_F32 && out_dtype == UB_BF16) LAUNCH(float, __nv_bfloat16);
+    else if (in_dtype == UB_BF16 && out_dtype == UB_BF16) LAUNCH(__nv_bfloat16, __nv_bfloat16);
     else return UB_ERR_UNSUPPORTED;
-    UB_LAUNCH_CHECK();
-    return 0;
+#undef LAUNCH
+    return (int)e;
 }
 
 // ---------------------------------------------------------------------------------------

@@ -22,7 +22,10 @@
 #include "common.cuh"
 #include <cuda.h>
 
-enum : int { EPI_STORE = 0, EPI_ADD = 1, EPI_SWIGLU = 2 };
+// EPI_SWIGLU: two weight tiles (gate rows, up rows) and two accumulators.  EPI_SWIGLU_IL: one weight
+// matrix in which blocks of 64 gate rows and 64 up rows alternate, one accumulator whose lanes
+// 0-63 are gate and 64-127 up of the same 64 features; the halves meet through shared memory.
+enum : int { EPI_STORE = 0, EPI_ADD = 1, EPI_SWIGLU = 2, EPI_SWIGLU_IL = 3 };
 
 constexpr int BM = 128;              // weight rows a tile (MMA M)
 constexpr int BK = 64;               // k columns a stage: 128 bytes of bfloat16
@@ -132,10 +135,11 @@ struct Smem {
     static constexpr int B_BYTES = BN * BK * 2;
     static constexpr int STAGE_BYTES = A_BYTES * (EPI == EPI_SWIGLU ? 2 : 1) + B_BYTES;
     // token tiles of up to 64 leave room for two CTAs on an SM (this kernel's and the next one's)
-    static constexpr int BUDGET = (BN <= 64 && EPI != EPI_SWIGLU ? 110 : 200) * 1024;
+    static constexpr int BUDGET = (BN <= 64 && EPI != EPI_SWIGLU ? (EPI == EPI_SWIGLU_IL ? 106 : 110) : 196) * 1024;
     static constexpr int STAGES_RAW = BUDGET / STAGE_BYTES;
     static constexpr int STAGES = STAGES_RAW > 10 ? 10 : STAGES_RAW;
-    static constexpr int TOTAL = STAGES * STAGE_BYTES + 1024 /*alignment*/ + 256 /*barriers*/;
+    static constexpr int XCH_BYTES = EPI == EPI_SWIGLU_IL ? 64 * 16 * 4 : 0;
+    static constexpr int TOTAL = STAGES * STAGE_BYTES + 1024 /*alignment*/ + 256 /*barriers*/ + XCH_BYTES;
     static constexpr int ACC_COLS = BN * (EPI == EPI_SWIGLU ? 2 : 1);
     static constexpr int TMEM_COLS = ACC_COLS <= 32 ? 32 : ACC_COLS <= 64 ? 64 : ACC_COLS <= 128 ? 128 : ACC_COLS <= 256 ? 256 : 512;
 };
@@ -152,6 +156,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     uint64_t* acc_full = empty + S::STAGES;
     uint32_t* tmem_slot = (uint32_t*)(acc_full + 1);
     volatile int* err = (volatile int*)(tmem_slot + 1);
+    float* xch = (float*)(smem + S::STAGES * S::STAGE_BYTES + 256);       // EPI_SWIGLU_IL only
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int n0 = blockIdx.x * BM;                 // first weight row = first output column
@@ -262,7 +267,28 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                 tmem_ld16(taddr, r);
                 if (EPI == EPI_SWIGLU) tmem_ld16(taddr + BN, r2);
                 tmem_ld_wait();
-                if (n < p.N) {
+                if (EPI == EPI_SWIGLU_IL) {
+                    // lanes 64..127 hold "up" of the features whose "gate" lanes 0..63 hold
+                    const int fl = (q & 1) * 32 + lane;               // feature within the tile's 64
+                    if (q >= 2) {
+#pragma unroll
+                        for (int c = 0; c < 16; ++c) xch[c * 64 + fl] = __uint_as_float(r[c]);
+                    }
+                    asm volatile("bar.sync 1, 128;" ::: "memory");
+                    if (q < 2) {
+                        const int f = blockIdx.x * 64 + fl;
+                        if (f < p.N / 2) {
+#pragma unroll
+                            for (int c = 0; c < 16; ++c) {
+                                const int t = t0 + c0 + c;
+                                if (t >= p.T) break;
+                                const float g = __uint_as_float(r[c]);
+                                out[(long long)t * p.ldo + f] = from_f32<TO>(g / (1.0f + expf(-g)) * xch[c * 64 + fl]);
+                            }
+                        }
+                    }
+                    asm volatile("bar.sync 1, 128;" ::: "memory");
+                } else if (n < p.N) {
 #pragma unroll
                     for (int c = 0; c < 16; ++c) {
                         const int t = t0 + c0 + c;
@@ -366,6 +392,7 @@ static int launch_bn(const CUtensorMap* mw, const CUtensorMap* mw2, const CUtens
         if constexpr (BN <= 128) return launch_one<BN, EPI_SWIGLU, __nv_bfloat16>(mw, mw2, ma, p, splits, st);
         else return UB_ERR_ARG;
     }
+    if (epi == EPI_SWIGLU_IL && o_dtype == UB_BF16) return launch_one<BN, EPI_SWIGLU_IL, __nv_bfloat16>(mw, mw2, ma, p, splits, st);
     return UB_ERR_UNSUPPORTED;
 }
 
@@ -377,7 +404,8 @@ UB_API int ub_gemm_tc(const void* map_w, const void* map_w2, const void* map_a, 
                       cudaStream_t st) {
     if (T <= 0 || N <= 0) return 0;
     if (K <= 0 || splits < 1) return UB_ERR_ARG;
-    if (splits > 1 && epi == EPI_SWIGLU) return UB_ERR_ARG;
+    if (splits > 1 && (epi == EPI_SWIGLU || epi == EPI_SWIGLU_IL)) return UB_ERR_ARG;
+    if (epi == EPI_SWIGLU_IL && (N % 128) != 0) return UB_ERR_ARG;
     if (splits > 1 && epi == EPI_STORE && o_dtype != UB_F32) return UB_ERR_ARG;
     const int nkb = (K + BK - 1) / BK;
     GemmParams p;

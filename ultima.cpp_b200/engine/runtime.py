@@ -95,7 +95,28 @@ class Runtime:
             from ..kernels import gemm_tc
             if gemm_tc.accepts(a, w, out, epilogue, w2):
                 return gemm_tc.gemm(a, w, out, epilogue, w2, self)
+        if epilogue == ops.EPI_SWIGLU_IL:
+            raise ops.KernelError("the interleaved gate/up layout is for the tensor-core product only; "
+                                  "this call does not fit it (operand alignment)")
         return ops.gemm_simt(a, w, out, epilogue, w2)
+
+    def matmul_parts(self, a, w):
+        """a @ w.T as a float32 [parts, T, N] whose sum over the first axis is the product (K is cut
+        into slices so that a product with few tokens fills the GPU), or None when the product
+        is better done whole."""
+        if not (self.use_tensor_cores and a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16):
+            return None
+        from ..kernels import gemm_tc
+        T, N = a.shape[0], w.shape[0]
+        parts = gemm_tc.store_splits(T, N, a.shape[1])
+        if parts <= 1:
+            return None
+        out = self.arena.alloc((parts, T, N), torch.float32)
+        if not gemm_tc.accepts(a, w, out[0], ops.EPI_STORE, None):
+            return None
+        self.launches += 1
+        gemm_tc.gemm(a, w, out, ops.EPI_STORE, None, self, splits=parts)
+        return out
 
     # ---- attention ----------------------------------------------------------------------
     def attention(self, q, kv, out, batch, n_heads, n_kv_heads, head_dim, scale):

@@ -9,7 +9,7 @@ from ctypes import c_int, c_longlong, c_void_p
 import torch
 
 from . import build
-from .ops import EPI_ADD, EPI_STORE, EPI_SWIGLU, BF16, F32, KernelError, _check, _ptr, _stream
+from .ops import EPI_ADD, EPI_STORE, EPI_SWIGLU, EPI_SWIGLU_IL, BF16, F32, KernelError, _check, _ptr, _stream
 
 SOURCE = "gemm_tcgen05.cu"
 N_SMS = 148
@@ -65,6 +65,8 @@ def accepts(a, w, out, epilogue, w2) -> bool:
         return False
     if epilogue == EPI_SWIGLU:
         return w2 is not None and _ok_operand(w2) and out.dtype == torch.bfloat16
+    if epilogue == EPI_SWIGLU_IL:
+        return out.dtype == torch.bfloat16 and w.shape[0] % 128 == 0
     if epilogue == EPI_ADD:
         return out.dtype == torch.float32
     return out.dtype in (torch.bfloat16, torch.float32)
@@ -102,19 +104,43 @@ def k_splits(T: int, N: int, K: int, bn: int, epilogue: int) -> int:
 
 
 def gemm(a, w, out, epilogue, w2, rt, splits: int | None = None, bn: int | None = None):
+    """out: [T, N]; for EPI_SWIGLU_IL [T, N / 2]; for EPI_STORE with ``splits`` > 1 a float32
+    [splits, T, N] whose sum over the first axis is the product."""
     T, K = a.shape
     N = w.shape[0]
-    assert w.shape[1] == K and out.shape == (T, N) and out.stride(1) == 1
+    assert w.shape[1] == K and out.stride(-1) == 1
     bn = bn or token_tile(T, epilogue)
     s = splits or k_splits(T, N, K, bn, epilogue)
+    split_stride = 0
+    if out.dim() == 3:
+        assert epilogue == EPI_STORE and out.dtype == torch.float32 and out.shape == (s, T, N)
+        split_stride, ldo = out.stride(0), out.stride(1)
+    else:
+        assert out.shape == (T, N // 2 if epilogue == EPI_SWIGLU_IL else N)
+        assert s == 1 or epilogue == EPI_ADD
+        ldo = out.stride(0)
     L = lib()
     mw = _tmap(w, 128)
     mw2 = _tmap(w2, 128) if w2 is not None else 0
     ma = _tmap(a, bn)
     err = rt.status[1:2]
-    rc = L.ub_gemm_tc(mw, mw2, ma, _ptr(out), BF16 if out.dtype == torch.bfloat16 else F32, out.stride(0),
-                      0, T, N, K, bn, epilogue, s, _ptr(err), _stream())
+    rc = L.ub_gemm_tc(mw, mw2, ma, _ptr(out), BF16 if out.dtype == torch.bfloat16 else F32, ldo,
+                      split_stride, T, N, K, bn, epilogue, s, _ptr(err), _stream())
     _check(rc, "gemm_tc")
+
+
+def store_splits(T: int, N: int, K: int) -> int:
+    """Slices of K for a product whose result is stored (not added): worth it only with few
+    tokens, where the float32 partial results are small beside the weights."""
+    bn = token_tile(T, EPI_STORE)
+    tiles = -(-N // 128) * -(-T // bn)
+    nkb = -(-K // 64)
+    slots = cta_slots(bn, EPI_STORE)
+    if T > 64 or tiles * 2 > slots or nkb < 8:
+        return 1
+    s = max(1, min(slots // tiles, nkb // 4, max(1, K // (40 * T))))
+    per = -(-nkb // s)
+    return -(-nkb // per)
 
 
 def check_error(rt) -> None:

@@ -13,7 +13,7 @@ import torch
 from . import build
 
 F32, BF16 = 0, 1
-EPI_STORE, EPI_ADD, EPI_SWIGLU = 0, 1, 2
+EPI_STORE, EPI_ADD, EPI_SWIGLU, EPI_SWIGLU_IL = 0, 1, 2, 3
 
 
 class KernelError(RuntimeError):
@@ -70,8 +70,8 @@ def _declare(lib, source: str) -> None:
         "basic.cu": {
             "ub_embed": [P, I, P, P, I, I, I, P, P],
             "ub_rmsnorm": [P, P, P, P, I, I, I, F, P],
-            "ub_qk_prepare": [P, I, P, P, P, P, P, P, P, P, I, P, I, I, I, I, I, I, I, F, I, P],
-            "ub_silu_mul": [P, I, P, I, I, I, P],
+            "ub_qk_prepare": [P, I, I, L, P, I, L, P, P, P, P, P, P, P, P, I, P, I, I, I, I, I, I, I, F, I, P],
+            "ub_silu_mul": [P, I, I, L, P, I, I, I, P],
             "ub_convert": [P, I, P, I, L, P],
             "ub_add_into": [P, P, I, L, P],
             "ub_fill_normal": [P, I, L, U, F, F, P],
@@ -111,30 +111,52 @@ def rmsnorm(x, weight, out, eps, rows=None):
 
 
 def qk_prepare(qkv, q_weight, k_weight, cos, sin, tok_pos, tok_seq, k_cache, v_cache, table,
-               ring, page, n_heads, n_kv_heads, head_dim, eps, write_kv=True):
-    """Per-head norm and rotation of q (in place) and k, and the write of k, v into the cache."""
+               ring, page, n_heads, n_kv_heads, head_dim, eps, write_kv=True, q_out=None):
+    """Per-head norm and rotation of q and k, and the write of k, v into the cache.
+
+    qkv: [T, (heads + 2 kv heads) * head size], or [parts, T, ...] whose sum over parts it is
+    (slices of K of the projection).  q goes to ``q_out`` ([T, heads * head size], any row stride),
+    or back into qkv's q columns when q_out is None (one part only)."""
     _need_cuda(qkv, k_cache, v_cache, table)
-    T = qkv.shape[0]
-    assert qkv.is_contiguous() and qkv.shape[1] == (n_heads + 2 * n_kv_heads) * head_dim
+    width = (n_heads + 2 * n_kv_heads) * head_dim
+    if qkv.dim() == 3:
+        n_parts, T = qkv.shape[0], qkv.shape[1]
+        part_stride = qkv.stride(0)
+        assert qkv.shape[2] == width and qkv.stride(1) == width and qkv.stride(2) == 1
+        assert q_out is not None
+    else:
+        n_parts, T, part_stride = 1, qkv.shape[0], 0
+        assert qkv.is_contiguous() and qkv.shape[1] == width
+    if q_out is None:
+        q_out = qkv
+    assert q_out.stride(1) == 1 and q_out.shape[0] == T
     assert table.dtype == torch.int32 and table.dim() == 2 and table.is_contiguous()
     for v in (q_weight, k_weight, cos, sin):
         assert v is None or (v.dtype == torch.float32 and v.is_contiguous())
     if cos is not None:
         assert cos.shape[1] == head_dim // 2
     _check(_lib("basic.cu").ub_qk_prepare(
-        _ptr(qkv), _code(qkv), _ptr(q_weight), _ptr(k_weight), _ptr(cos), _ptr(sin), _ptr(tok_pos),
+        _ptr(qkv), _code(qkv), n_parts, part_stride, _ptr(q_out), _code(q_out), q_out.stride(0),
+        _ptr(q_weight), _ptr(k_weight), _ptr(cos), _ptr(sin), _ptr(tok_pos),
         _ptr(tok_seq), _ptr(k_cache), _ptr(v_cache), _code(k_cache), _ptr(table), table.shape[1],
         ring, page, T, n_heads, n_kv_heads, head_dim, float(eps), 1 if write_kv else 0, _stream()),
         "qk_prepare")
 
 
 def silu_mul(gate_up, out):
-    """out[t, f] = silu(gate_up[t, f]) * gate_up[t, F + f]."""
+    """out[t, f] = silu(g[t, f]) * g[t, F + f], g being gate_up ([T, 2F]) or the sum over the first
+    axis of gate_up ([parts, T, 2F])."""
     _need_cuda(gate_up, out)
     T, F = out.shape
-    assert gate_up.shape == (T, 2 * F) and gate_up.is_contiguous() and out.is_contiguous()
-    _check(_lib("basic.cu").ub_silu_mul(_ptr(gate_up), _code(gate_up), _ptr(out), _code(out), T, F,
-                                        _stream()), "silu_mul")
+    if gate_up.dim() == 3:
+        n_parts, part_stride = gate_up.shape[0], gate_up.stride(0)
+        assert gate_up.shape[1:] == (T, 2 * F) and gate_up.stride(1) == 2 * F and gate_up.stride(2) == 1
+    else:
+        n_parts, part_stride = 1, 0
+        assert gate_up.shape == (T, 2 * F) and gate_up.is_contiguous()
+    assert out.is_contiguous()
+    _check(_lib("basic.cu").ub_silu_mul(_ptr(gate_up), _code(gate_up), n_parts, part_stride, _ptr(out),
+                                        _code(out), T, F, _stream()), "silu_mul")
 
 
 def convert(src, dst):

@@ -66,16 +66,21 @@ class Attention(Mixer):
     def forward(self, h, residual, batch, cache, rt):
         T = h.shape[0]
         kv = cache.kv
-        qkv = rt.arena.alloc((T, self.q_width + 2 * self.kv_width), rt.dtype)
-        rt.matmul(h, self.wqkv, qkv)
         cos = sin = None
         if self.position is not None:
             cos, sin = self.position.cos, self.position.sin
+        parts = rt.matmul_parts(h, self.wqkv)        # few tokens: K in slices, summed by the next kernel
+        if parts is not None:
+            qkv = parts
+            q = rt.arena.alloc((T, self.q_width), rt.dtype)
+        else:
+            qkv = rt.arena.alloc((T, self.q_width + 2 * self.kv_width), rt.dtype)
+            rt.matmul(h, self.wqkv, qkv)
+            q = qkv[:, :self.q_width]
         rt.launches += 1
         ops.qk_prepare(qkv, self.q_norm, self.k_norm, cos, sin, batch.tok_pos, batch.tok_seq,
                        kv.k, kv.v, kv.table, kv.ring, kv.page, self.nh, self.nkv, self.hd, self.eps,
-                       write_kv=kv.owner)
-        q = qkv[:, :self.q_width]
+                       write_kv=kv.owner, q_out=q)
         o = rt.arena.alloc((T, self.q_width), rt.dtype)
         rt.attention(q, kv, o, batch, self.nh, self.nkv, self.hd, self.scale)
         rt.matmul(o, self.wo, residual, ops.EPI_ADD)

@@ -31,11 +31,23 @@ class GatedSiLU(FeedForward):
         g, u = tensors["gate_proj.weight"], tensors["up_proj.weight"]
         if g.dtype != u.dtype:
             raise ValueError("gate and up projections must share one element type")
-        self.wgu = torch.cat([g, u], dim=0).contiguous()
         self.wd = tensors["down_proj.weight"].contiguous()
+        # On the tensor-core path blocks of 64 gate rows and 64 up rows alternate, so that one
+        # 128-row tile of the product holds both halves of 64 features (see gemm_tcgen05.cu).
+        self.interleaved = (rt.use_tensor_cores and g.dtype == torch.bfloat16 and self.inner % 64 == 0
+                            and self.width % 8 == 0)
+        if self.interleaved:
+            n = self.inner // 64
+            self.wgu = torch.stack([g.view(n, 64, self.width), u.view(n, 64, self.width)], dim=1) \
+                .reshape(2 * self.inner, self.width).contiguous()
+        else:
+            self.wgu = torch.cat([g, u], dim=0).contiguous()
 
     def forward(self, h, residual, batch, rt):
         T = h.shape[0]
         a = rt.arena.alloc((T, self.inner), rt.dtype)
-        rt.matmul(h, self.wgu[:self.inner], a, ops.EPI_SWIGLU, w2=self.wgu[self.inner:])
+        if self.interleaved:
+            rt.matmul(h, self.wgu, a, ops.EPI_SWIGLU_IL)
+        else:
+            rt.matmul(h, self.wgu[:self.inner], a, ops.EPI_SWIGLU, w2=self.wgu[self.inner:])
         rt.matmul(a, self.wd, residual, ops.EPI_ADD)
