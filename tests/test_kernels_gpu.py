@@ -456,3 +456,43 @@ def test_gemm_tc_interleaved_gate_product(shape):
     gemm_tc.check_error(rt)
     gt, up = a.double().cpu() @ wg.double().T, a.double().cpu() @ wu.double().T
     assert rel_err(out, gt / (1 + torch.exp(-gt)) * up) <= 2 ** -8, shape
+
+
+@pytest.mark.parametrize("case", [("store", 2500, 1024, 1200), ("add", 1300, 512, 2100), ("gate_il", 1700, 256, 1280),
+                                  ("gate_two", 1100, 320, 1300), ("store_f32", 700, 128, 5000)])
+def test_gemm_tc_many_tiles_a_cta(case):
+    """More tiles than SMs: CTAs stay and walk over tiles with two accumulators in turn."""
+    gemm_tc, rt = _tc()
+    ops = _ops()
+    kind, T, K, N = case
+    g = torch.Generator().manual_seed(T)
+    a = torch.randn(T, K, generator=g).to(torch.bfloat16).to(DEV)
+    w = (torch.randn(N, K, generator=g) * 0.05).to(torch.bfloat16).to(DEV)
+    ref = a.double() @ w.double().T
+    tol = max(2e-6, K * 2.0 ** -25)
+    if kind == "store":
+        out = torch.full((T, N), float("nan"), dtype=torch.bfloat16, device=DEV)
+        gemm_tc.gemm(a, w, out, ops.EPI_STORE, None, rt)
+        assert rel_err(out, ref) <= 2 ** -8
+    elif kind == "store_f32":
+        out = torch.full((T, N), float("nan"), dtype=torch.float32, device=DEV)
+        gemm_tc.gemm(a, w, out, ops.EPI_STORE, None, rt)
+        assert rel_err(out, ref) <= tol
+    elif kind == "add":
+        acc = torch.randn(T, N, generator=g).to(DEV)
+        want = acc.double() + ref
+        gemm_tc.gemm(a, w, acc, ops.EPI_ADD, None, rt)
+        assert rel_err(acc, want) <= tol
+    elif kind == "gate_il":
+        F = N // 2
+        il = torch.stack([w[:F].view(F // 64, 64, K), w[F:].view(F // 64, 64, K)], dim=1).reshape(N, K).contiguous()
+        out = torch.full((T, F), float("nan"), dtype=torch.bfloat16, device=DEV)
+        gemm_tc.gemm(a, il, out, ops.EPI_SWIGLU_IL, None, rt)
+        assert rel_err(out, ref[:, :F] / (1 + torch.exp(-ref[:, :F])) * ref[:, F:]) <= 2 ** -8
+    else:
+        F = N // 2
+        out = torch.full((T, F), float("nan"), dtype=torch.bfloat16, device=DEV)
+        gemm_tc.gemm(a, w[:F], out, ops.EPI_SWIGLU, w[F:], rt)
+        assert rel_err(out, ref[:, :F] / (1 + torch.exp(-ref[:, :F])) * ref[:, F:]) <= 2 ** -8
+    torch.cuda.synchronize()
+    gemm_tc.check_error(rt)

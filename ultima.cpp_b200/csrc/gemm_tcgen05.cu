@@ -144,6 +144,63 @@ struct Smem {
     static constexpr int TMEM_COLS = ACC_COLS <= 32 ? 32 : ACC_COLS <= 64 ? 64 : ACC_COLS <= 128 ? 128 : ACC_COLS <= 256 ? 256 : 512;
 };
 
+// The epilogue of one tile: this thread's accumulator lane (weight row n0 + 32 q + lane), all token
+// columns, in pieces of 16.  ``tile_w`` is the index of the 128-row weight tile, ``slice`` the K slice.
+template <int BN, int EPI, typename TO>
+__device__ __forceinline__ void epilogue_tile(const GemmParams& p, uint32_t tmem_acc, int q, int lane, int tile_w,
+                                              int t0, int slice, float* xch) {
+    const int n = tile_w * BM + q * 32 + lane;
+    TO* out = (TO*)p.out + (EPI == EPI_STORE ? (long long)slice * p.split_stride : 0);
+#pragma unroll 1
+    for (int c0 = 0; c0 < BN; c0 += 16) {
+        if (t0 + c0 >= p.T) break;               // uniform over the epilogue warps
+        uint32_t r[16], r2[16];
+        const uint32_t taddr = tmem_acc + ((uint32_t)(q * 32) << 16) + (uint32_t)c0;
+        tmem_ld16(taddr, r);
+        if (EPI == EPI_SWIGLU) tmem_ld16(taddr + BN, r2);
+        tmem_ld_wait();
+        if (EPI == EPI_SWIGLU_IL) {
+            // lanes 64..127 hold "up" of the 64 features whose "gate" lanes 0..63 hold.  The halves
+            // swap through shared memory: gate threads finish columns 0..7, up threads 8..15.
+            const int fl = (q & 1) * 32 + lane;               // feature within the tile's 64
+            const bool up = q >= 2;
+#pragma unroll
+            for (int c = 0; c < 8; ++c) xch[((up ? 0 : 8) + c) * 64 + fl] = __uint_as_float(up ? r[c] : r[8 + c]);
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            const int f = tile_w * 64 + fl;
+            if (f < p.N / 2) {
+#pragma unroll
+                for (int c = 0; c < 8; ++c) {
+                    const int col = (up ? 8 : 0) + c;
+                    const int t = t0 + c0 + col;
+                    if (t >= p.T) break;
+                    const float own = __uint_as_float(up ? r[8 + c] : r[c]), other = xch[col * 64 + fl];
+                    const float g = up ? other : own, u = up ? own : other;
+                    out[(long long)t * p.ldo + f] = from_f32<TO>(g / (1.0f + __expf(-g)) * u);
+                }
+            }
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+        } else if (n < p.N) {
+#pragma unroll
+            for (int c = 0; c < 16; ++c) {
+                const int t = t0 + c0 + c;
+                if (t >= p.T) break;
+                const float v = __uint_as_float(r[c]);
+                TO* dst = out + (long long)t * p.ldo + n;
+                if (EPI == EPI_STORE) *dst = from_f32<TO>(v);
+                else if (EPI == EPI_ADD) {
+                    // a reduction at the memory side: no load, no wait; one writer an element
+                    // unless K is split, so the sum's order is fixed in that case
+                    asm volatile("red.global.add.f32 [%0], %1;" ::"l"(dst), "f"(v) : "memory");
+                } else {
+                    const float u = __uint_as_float(r2[c]);
+                    *dst = from_f32<TO>(v / (1.0f + __expf(-v)) * u);
+                }
+            }
+        }
+    }
+}
+
 template <int BN, int EPI, typename TO>
 __global__ void __launch_bounds__(NUM_THREADS)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_w2,
@@ -253,60 +310,158 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     } else {
         // ---------------- epilogue: warps 2..5 ----------------
         const int q = warp & 3;                          // the lanes this warp may read: 32 q .. 32 q + 31
-        const int n = n0 + q * 32 + lane;                // this thread's weight row = output column
         pdl_wait();                                      // the output may be read by the kernel before
         bool ok = nkb > 0 ? mbar_wait(acc_full, 0, err) : true;
         tc_fence_after();
-        if (ok && nkb > 0) {
-            TO* out = (TO*)p.out + (EPI == EPI_STORE ? (long long)blockIdx.z * p.split_stride : 0);
-#pragma unroll 1
-            for (int c0 = 0; c0 < BN; c0 += 16) {
-                if (t0 + c0 >= p.T) break;               // uniform over the warp
-                uint32_t r[16], r2[16];
-                const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)c0;
-                tmem_ld16(taddr, r);
-                if (EPI == EPI_SWIGLU) tmem_ld16(taddr + BN, r2);
-                tmem_ld_wait();
-                if (EPI == EPI_SWIGLU_IL) {
-                    // lanes 64..127 hold "up" of the features whose "gate" lanes 0..63 hold
-                    const int fl = (q & 1) * 32 + lane;               // feature within the tile's 64
-                    if (q >= 2) {
-#pragma unroll
-                        for (int c = 0; c < 16; ++c) xch[c * 64 + fl] = __uint_as_float(r[c]);
-                    }
-                    asm volatile("bar.sync 1, 128;" ::: "memory");
-                    if (q < 2) {
-                        const int f = blockIdx.x * 64 + fl;
-                        if (f < p.N / 2) {
-#pragma unroll
-                            for (int c = 0; c < 16; ++c) {
-                                const int t = t0 + c0 + c;
-                                if (t >= p.T) break;
-                                const float g = __uint_as_float(r[c]);
-                                out[(long long)t * p.ldo + f] = from_f32<TO>(g / (1.0f + expf(-g)) * xch[c * 64 + fl]);
-                            }
-                        }
-                    }
-                    asm volatile("bar.sync 1, 128;" ::: "memory");
-                } else if (n < p.N) {
-#pragma unroll
-                    for (int c = 0; c < 16; ++c) {
-                        const int t = t0 + c0 + c;
-                        if (t >= p.T) break;
-                        const float v = __uint_as_float(r[c]);
-                        TO* dst = out + (long long)t * p.ldo + n;
-                        if (EPI == EPI_STORE) *dst = from_f32<TO>(v);
-                        else if (EPI == EPI_ADD) {
-                            // a reduction at the memory side: no load, no wait; one writer an element
-                            // unless K is split, so the sum's order is fixed in that case
-                            asm volatile("red.global.add.f32 [%0], %1;" ::"l"(dst), "f"(v) : "memory");
-                        } else {
-                            const float u = __uint_as_float(r2[c]);
-                            *dst = from_f32<TO>(v / (1.0f + expf(-v)) * u);
-                        }
-                    }
+        if (ok && nkb > 0) epilogue_tile<BN, EPI, TO>(p, tmem_base, q, lane, blockIdx.x, t0, blockIdx.z, xch);
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, S::TMEM_COLS);
+    }
+    if (threadIdx.x == 0 && *err) atomicExch(p.error, 1);
+}
+
+// ---------------------------------------------------------------------------------------
+// The same product for many tiles a CTA: one CTA an SM walks over tiles c, c + G, c + 2G, ...
+// The ring of stages never drains between tiles, and there are two accumulators in tensor
+// memory, so the epilogue of one tile runs while the MMAs of the next are issued.
+// ---------------------------------------------------------------------------------------
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
+template <int BN, int EPI>
+struct SmemP {
+    static constexpr int A_BYTES = BM * BK * 2;
+    static constexpr int B_BYTES = BN * BK * 2;
+    static constexpr int STAGE_BYTES = A_BYTES * (EPI == EPI_SWIGLU ? 2 : 1) + B_BYTES;
+    static constexpr int STAGES = (196 * 1024) / STAGE_BYTES;
+    static constexpr int XCH_BYTES = EPI == EPI_SWIGLU_IL ? 64 * 16 * 4 : 0;
+    static constexpr int TOTAL = STAGES * STAGE_BYTES + 1024 + 256 + XCH_BYTES;
+    static constexpr int ACC_COLS = BN * (EPI == EPI_SWIGLU ? 2 : 1);
+    static constexpr int TMEM_COLS = 2 * ACC_COLS <= 32 ? 32 : 2 * ACC_COLS <= 64 ? 64 : 2 * ACC_COLS <= 128 ? 128
+                                     : 2 * ACC_COLS <= 256 ? 256 : 512;
+    static_assert(2 * ACC_COLS <= 512, "two accumulators must fit tensor memory");
+};
+
+template <int BN, int EPI, typename TO>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_w2,
+                          const __grid_constant__ CUtensorMap map_a, GemmParams p) {
+    using S = SmemP<BN, EPI>;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint64_t* full = (uint64_t*)(smem + S::STAGES * S::STAGE_BYTES);
+    uint64_t* empty = full + S::STAGES;
+    uint64_t* acc_full = empty + S::STAGES;            // [2]
+    uint64_t* acc_empty = acc_full + 2;                // [2]
+    uint32_t* tmem_slot = (uint32_t*)(acc_empty + 2);
+    volatile int* err = (volatile int*)(tmem_slot + 1);
+    float* xch = (float*)(smem + S::STAGES * S::STAGE_BYTES + 256);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int tiles_w = (p.N + BM - 1) / BM, tiles_t = (p.T + BN - 1) / BN;
+    const int n_tiles = tiles_w * tiles_t;
+    const int nkb = (p.K + BK - 1) / BK;
+    // tile i of this CTA is number blockIdx.x + i * gridDim.x; token tiles vary fastest, so the CTAs
+    // that run together share weight tiles through the L2
+    const int my_tiles = (n_tiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < S::STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+        for (int b = 0; b < 2; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], 4); }
+        *err = 0;
+        fence_barrier_init();
+    }
+    if (warp == 1) { tmem_alloc(tmem_slot, S::TMEM_COLS); tmem_relinquish(); }
+    if (warp == 0 && lane == 0) {
+        prefetch_tmap(&map_w); prefetch_tmap(&map_a);
+        if (EPI == EPI_SWIGLU) prefetch_tmap(&map_w2);
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+    pdl_trigger();
+
+    if (warp == 0) {
+        if (lane == 0) {
+            pdl_wait();
+            long long it = 0;                            // stages filled so far, over all tiles
+            bool ok = true;
+            for (int i = 0; i < my_tiles && ok; ++i) {
+                const int tile = blockIdx.x + i * gridDim.x;
+                const int n0 = (tile / tiles_t) * BM, t0 = (tile % tiles_t) * BN;
+                for (int kb = 0; kb < nkb; ++kb, ++it) {
+                    const int s = (int)(it % S::STAGES);
+                    const uint32_t ph = (uint32_t)((it / S::STAGES) & 1);
+                    ok = mbar_wait(&empty[s], ph ^ 1, err);
+                    if (!ok) break;
+                    uint8_t* st = smem + s * S::STAGE_BYTES;
+                    mbar_expect_tx(&full[s], S::STAGE_BYTES);
+                    tma_load_2d(st, &map_w, &full[s], kb * BK, n0);
+                    if (EPI == EPI_SWIGLU) tma_load_2d(st + S::A_BYTES, &map_w2, &full[s], kb * BK, n0);
+                    tma_load_2d(st + S::A_BYTES * (EPI == EPI_SWIGLU ? 2 : 1), &map_a, &full[s], kb * BK, t0);
                 }
             }
+            if (*err) {
+                for (long long j = it > S::STAGES ? it - S::STAGES : 0; j < it; ++j) {
+                    const long long tstart = clock64();
+                    while (!mbar_try_wait(&full[j % S::STAGES], (uint32_t)((j / S::STAGES) & 1)))
+                        if (clock64() - tstart > WAIT_LIMIT_CYCLES / 8) break;
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            constexpr uint32_t idesc = make_idesc(BN);
+            long long it = 0;
+            bool ok = true;
+            for (int i = 0; i < my_tiles && ok; ++i) {
+                const int buf = i & 1;
+                ok = mbar_wait(&acc_empty[buf], (uint32_t)(((i >> 1) & 1) ^ 1), err);   // the epilogue has read it
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t acc = tmem_base + buf * S::ACC_COLS;
+                for (int kb = 0; kb < nkb; ++kb, ++it) {
+                    const int s = (int)(it % S::STAGES);
+                    const uint32_t ph = (uint32_t)((it / S::STAGES) & 1);
+                    ok = mbar_wait(&full[s], ph, err);
+                    if (!ok) break;
+                    tc_fence_after();
+                    const uint32_t a_addr = smem_u32(smem + s * S::STAGE_BYTES);
+                    const uint32_t b_addr = a_addr + S::A_BYTES * (EPI == EPI_SWIGLU ? 2 : 1);
+                    const uint64_t da = make_desc(a_addr), db = make_desc(b_addr);
+                    const uint64_t da2 = make_desc(a_addr + S::A_BYTES);
+#pragma unroll
+                    for (int k = 0; k < BK / UMMA_K; ++k) {
+                        const uint64_t koff = (uint64_t)((k * UMMA_K * 2) >> 4);
+                        const uint32_t accum = (kb > 0 || k > 0) ? 1u : 0u;
+                        tc_mma_bf16(acc, da + koff, db + koff, idesc, accum);
+                        if (EPI == EPI_SWIGLU) tc_mma_bf16(acc + BN, da2 + koff, db + koff, idesc, accum);
+                    }
+                    tc_commit(&empty[s]);
+                }
+                if (ok) tc_commit(&acc_full[buf]);
+            }
+        }
+    } else {
+        const int q = warp & 3;
+        pdl_wait();
+        bool ok = true;
+        for (int i = 0; i < my_tiles && ok; ++i) {
+            const int buf = i & 1;
+            const int tile = blockIdx.x + i * gridDim.x;
+            ok = mbar_wait(&acc_full[buf], (uint32_t)((i >> 1) & 1), err);
+            if (!ok) break;
+            tc_fence_after();
+            epilogue_tile<BN, EPI, TO>(p, tmem_base + buf * S::ACC_COLS, q, lane, tile / tiles_t, (tile % tiles_t) * BN, 0, xch);
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&acc_empty[buf]);  // four warps: the accumulator may be written again
         }
     }
     tc_fence_before();
@@ -354,9 +509,55 @@ UB_API int ub_tmap_bf16_2d(void* out_map, const void* base, long long rows, long
 static int g_use_pdl = 1;
 UB_API void ub_gemm_tc_set_pdl(int on) { g_use_pdl = on ? 1 : 0; }
 
+static int g_sm_count = 0;
+static int sm_count() {
+    if (!g_sm_count) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&g_sm_count, cudaDevAttrMultiProcessorCount, dev);
+        if (g_sm_count <= 0) g_sm_count = 148;
+    }
+    return g_sm_count;
+}
+
+template <typename Kern>
+static int launch_cfg(Kern kern, dim3 grid, int smem, const CUtensorMap* mw, const CUtensorMap* mw2, const CUtensorMap* ma,
+                      const GemmParams& p, cudaStream_t st) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = dim3(NUM_THREADS);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = g_use_pdl ? 1 : 0;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, kern, *mw, *mw2, *ma, p);
+    return e == cudaSuccess ? 0 : (int)e;
+}
+
+static int g_use_persistent = 1;
+UB_API void ub_gemm_tc_set_persistent(int on) { g_use_persistent = on ? 1 : 0; }
+
 template <int BN, int EPI, typename TO>
 static int launch_one(const CUtensorMap* mw, const CUtensorMap* mw2, const CUtensorMap* ma, const GemmParams& p,
                       int splits, cudaStream_t st) {
+    const int tiles = ((p.N + BM - 1) / BM) * ((p.T + BN - 1) / BN);
+    if constexpr (BN >= 128) {
+        // many tiles, K whole: CTAs that stay and overlap one tile's epilogue with the next tile's MMAs
+        if (g_use_persistent && splits == 1 && tiles > sm_count()) {
+            using SP = SmemP<BN, EPI>;
+            static bool attr_p = false;
+            auto kp = gemm_tc_persistent_kernel<BN, EPI, TO>;
+            if (!attr_p) {
+                cudaError_t e = cudaFuncSetAttribute(kp, cudaFuncAttributeMaxDynamicSharedMemorySize, SP::TOTAL);
+                if (e != cudaSuccess) return (int)e;
+                attr_p = true;
+            }
+            return launch_cfg(kp, dim3(sm_count()), SP::TOTAL, mw, mw2, ma, p, st);
+        }
+    }
     using S = Smem<BN, EPI>;
     static bool attr_done = false;
     auto kern = gemm_tc_kernel<BN, EPI, TO>;
@@ -367,19 +568,7 @@ static int launch_one(const CUtensorMap* mw, const CUtensorMap* mw2, const CUten
     }
     dim3 grid((p.N + BM - 1) / BM, (p.T + BN - 1) / BN, splits);
     if (grid.y > 65535 || grid.z > 65535) return UB_ERR_ARG;
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = grid;
-    cfg.blockDim = dim3(NUM_THREADS);
-    cfg.dynamicSmemBytes = S::TOTAL;
-    cfg.stream = st;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = 1;
-    cfg.attrs = attr;
-    cfg.numAttrs = g_use_pdl ? 1 : 0;
-    cudaError_t e = cudaLaunchKernelEx(&cfg, kern, *mw, *mw2, *ma, p);
-    if (e != cudaSuccess) return (int)e;
-    return 0;
+    return launch_cfg(kern, grid, S::TOTAL, mw, mw2, ma, p, st);
 }
 
 template <int BN>

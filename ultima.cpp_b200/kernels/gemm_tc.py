@@ -31,6 +31,10 @@ def lib():
         import os
         if os.environ.get("ULTIMA_PDL", "1") == "0":       # for measurements: ordinary launches
             L.ub_gemm_tc_set_pdl(0)
+        L.ub_gemm_tc_set_persistent.argtypes = [c_int]
+        L.ub_gemm_tc_set_persistent.restype = None
+        if os.environ.get("ULTIMA_PERSISTENT", "1") == "0":   # for measurements: one tile a CTA
+            L.ub_gemm_tc_set_persistent(0)
         _lib = L
     return _lib
 
