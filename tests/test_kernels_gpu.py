@@ -176,7 +176,8 @@ def test_attention_finds_a_far_key_and_respects_the_window_edge():
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("cfg", [dict(nh=6, nkv=2, hd=48), dict(nh=8, nkv=1, hd=16), dict(nh=2, nkv=2, hd=112)])
+@pytest.mark.parametrize("cfg", [dict(nh=6, nkv=2, hd=48), dict(nh=8, nkv=1, hd=16), dict(nh=2, nkv=2, hd=112),
+                                 dict(nh=4, nkv=2, hd=128), dict(nh=3, nkv=1, hd=64), dict(nh=2, nkv=1, hd=256)])
 def test_qk_prepare_norm_rotation_and_cache_write(cfg, dtype):
     ops = _ops()
     nh, nkv, hd = cfg["nh"], cfg["nkv"], cfg["hd"]
@@ -402,7 +403,7 @@ def test_gemm_tc_partial_products_and_their_consumers():
     gemm_tc, rt = _tc()
     ops = _ops()
     g = torch.Generator().manual_seed(4)
-    T, K, nh, nkv, hd = 5, 1024, 4, 2, 32
+    T, K, nh, nkv, hd = 5, 1024, 4, 2, 128
     N = (nh + 2 * nkv) * hd
     a = torch.randn(T, K, generator=g).to(torch.bfloat16).to(DEV)
     w = (torch.randn(N, K, generator=g) * 0.05).to(torch.bfloat16).to(DEV)
@@ -419,6 +420,8 @@ def test_gemm_tc_partial_products_and_their_consumers():
     kw = (1 + 0.1 * torch.randn(hd, generator=g)).to(DEV)
     cos = torch.cos(torch.arange(8)[:, None] * torch.arange(hd // 2)[None] * 0.1).float().to(DEV)
     sin = torch.sin(torch.arange(8)[:, None] * torch.arange(hd // 2)[None] * 0.1).float().to(DEV)
+    # the same rows through the kernel for any head size (48) give the same numbers where they overlap:
+    # covered by test_qk_prepare_norm_rotation_and_cache_write; here the slices are what is checked
     outs = []
     for src in (parts, parts.sum(0).contiguous()):
         kc = torch.zeros(2, nkv, 64, hd, dtype=torch.bfloat16, device=DEV)

@@ -60,11 +60,54 @@ __global__ void rmsnorm_kernel(const float* __restrict__ x, const int* __restric
         out[(long long)r * width + i] = from_f32<TO>(xr[i] * w[i] * inv);
 }
 
+// The same with rows held in registers: width a multiple of 4, at most 16 values a thread.
+template <typename TO>
+__global__ void rmsnorm_vec_kernel(const float* __restrict__ x, const int* __restrict__ rows,
+                                   const float* __restrict__ w, TO* __restrict__ out, int width, float eps) {
+    __shared__ float red[33];
+    pdl_trigger();
+    pdl_wait();
+    const int r = blockIdx.x;
+    const float4* xr = reinterpret_cast<const float4*>(x + (long long)(rows ? rows[r] : r) * width);
+    const int nv = width >> 2;
+    float4 v[4];
+    float ss = 0.f;
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+        const int i = threadIdx.x + u * blockDim.x;
+        if (i < nv) { v[u] = xr[i]; ss += v[u].x * v[u].x + v[u].y * v[u].y + v[u].z * v[u].z + v[u].w * v[u].w; }
+    }
+    ss = block_sum(ss, red);
+    const float inv = 1.0f / sqrtf(ss / (float)width + eps);
+    const float4* w4 = reinterpret_cast<const float4*>(w);
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+        const int i = threadIdx.x + u * blockDim.x;
+        if (i < nv) {
+            const float4 g = w4[i];
+            const float o[4] = {v[u].x * g.x * inv, v[u].y * g.y * inv, v[u].z * g.z * inv, v[u].w * g.w * inv};
+            store_vec<TO, 4>(out + (long long)r * width + 4 * i, o);
+        }
+    }
+}
+
 UB_API int ub_rmsnorm(const float* x, const int* rows, const float* w, void* out, int out_dtype,
                       int n_rows, int width, float eps, cudaStream_t st) {
     if (n_rows <= 0) return 0;
-    const int threads = width >= 2048 ? 512 : (width >= 512 ? 256 : 128);
     cudaError_t e;
+    const bool aligned = (((uintptr_t)x | (uintptr_t)w | (uintptr_t)out) & 15) == 0;
+    if (width % 4 == 0 && aligned && width <= 16 * 1024) {
+        int threads = 128;
+        while (threads < 1024 && threads * 16 < width) threads <<= 1;
+        if (width >= 2048 && threads < 256) threads = 256;
+        if (out_dtype == UB_F32)
+            e = ub_launch_dependent(rmsnorm_vec_kernel<float>, dim3(n_rows), dim3(threads), 0, st, x, rows, w, (float*)out, width, eps);
+        else if (out_dtype == UB_BF16)
+            e = ub_launch_dependent(rmsnorm_vec_kernel<__nv_bfloat16>, dim3(n_rows), dim3(threads), 0, st, x, rows, w, (__nv_bfloat16*)out, width, eps);
+        else return UB_ERR_UNSUPPORTED;
+        return (int)e;
+    }
+    const int threads = width >= 2048 ? 512 : (width >= 512 ? 256 : 128);
     if (out_dtype == UB_F32)
         e = ub_launch_dependent(rmsnorm_kernel<float>, dim3(n_rows), dim3(threads), 0, st, x, rows, w, (float*)out, width, eps);
     else if (out_dtype == UB_BF16)
@@ -150,6 +193,71 @@ __global__ void qk_prepare_kernel(const TA* qkv, int n_parts, long long part_str
     }
 }
 
+// The same for head sizes of 64, 128 and 256: a lane holds E = hd / 32 neighbouring elements, the
+// lower 16 lanes the first half of the head and the upper 16 the second, so the partner of a
+// rotation pair sits 16 lanes away and every access is one aligned vector.
+template <typename TA, typename TQ, typename TC, int E>
+__global__ void qk_prepare_vec_kernel(const TA* qkv, int n_parts, long long part_stride,
+                                      TQ* q_out, long long q_out_stride, const float* __restrict__ qw,
+                                      const float* __restrict__ kw, const float* __restrict__ cs,
+                                      const float* __restrict__ sn, const int* __restrict__ tok_pos,
+                                      const int* __restrict__ tok_seq, TC* __restrict__ kcache,
+                                      TC* __restrict__ vcache, PagedKV c, int n_tokens, int nh, float eps,
+                                      int write_kv) {
+    pdl_trigger();
+    pdl_wait();
+    const int lane = threadIdx.x & 31;
+    const long long wid = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    const int heads_all = nh + 2 * c.n_kv_heads;
+    if (wid >= (long long)n_tokens * heads_all) return;
+    const int t = (int)(wid / heads_all), h = (int)(wid % heads_all);
+    constexpr int hd = 32 * E, half = hd / 2;
+    const TA* row = qkv + ((long long)t * heads_all + h) * hd + lane * E;
+    const int pos = tok_pos[t];
+    const int seq = tok_seq[t];
+    const bool is_v = h >= nh + c.n_kv_heads, is_k = !is_v && h >= nh;
+    if ((is_v || is_k) && !write_kv) return;
+    float v[E];
+    load_vec<TA, E>(row, v);
+    for (int p = 1; p < n_parts; ++p) {
+        float more[E];
+        load_vec<TA, E>(row + p * part_stride, more);
+#pragma unroll
+        for (int i = 0; i < E; ++i) v[i] += more[i];
+    }
+    if (is_v) {
+        store_vec<TC, E>(vcache + paged_offset(c, seq, pos, h - nh - c.n_kv_heads) + lane * E, v);
+        return;
+    }
+    const float* w = is_k ? kw : qw;
+    if (w) {
+        float ss = 0.f;
+#pragma unroll
+        for (int i = 0; i < E; ++i) ss += v[i] * v[i];
+        ss = warp_sum(ss);
+        const float inv = 1.0f / sqrtf(ss / (float)hd + eps);
+        float g[E];
+        load_vec<float, E>(w + lane * E, g);
+#pragma unroll
+        for (int i = 0; i < E; ++i) v[i] = v[i] * g[i] * inv;
+    }
+    if (cs) {
+        const int j0 = (lane & 15) * E;                          // index of the pair within the half
+        float co[E], si[E];
+        load_vec<float, E>(cs + (long long)pos * half + j0, co);
+        load_vec<float, E>(sn + (long long)pos * half + j0, si);
+        const bool upper = lane >= 16;
+#pragma unroll
+        for (int i = 0; i < E; ++i) {
+            const float other = __shfl_xor_sync(0xffffffffu, v[i], 16);
+            // lower lanes hold a (partner b): a c - b s; upper lanes hold b (partner a): a s + b c
+            v[i] = upper ? other * si[i] + v[i] * co[i] : v[i] * co[i] - other * si[i];
+        }
+    }
+    if (is_k) store_vec<TC, E>(kcache + paged_offset(c, seq, pos, h - nh) + lane * E, v);
+    else store_vec<TQ, E>(q_out + (long long)t * q_out_stride + (long long)h * hd + lane * E, v);
+}
+
 UB_API int ub_qk_prepare(const void* qkv, int in_dtype, int n_parts, long long part_stride, void* q_out,
                          int q_dtype, long long q_out_stride, const float* qw, const float* kw, const float* cs,
                          const float* sn, const int* tok_pos, const int* tok_seq, void* kcache,
@@ -163,15 +271,26 @@ UB_API int ub_qk_prepare(const void* qkv, int in_dtype, int n_parts, long long p
     const int wpb = 8;
     const unsigned grid = (unsigned)((warps + wpb - 1) / wpb);
     cudaError_t e;
-#define LAUNCH(TA, TQ, TC) e = ub_launch_dependent(qk_prepare_kernel<TA, TQ, TC>, dim3(grid), dim3(wpb * 32), 0, st, \
+    const bool aligned = (((uintptr_t)qkv | (uintptr_t)q_out | (uintptr_t)kcache | (uintptr_t)vcache | (uintptr_t)qw |
+                           (uintptr_t)kw | (uintptr_t)cs | (uintptr_t)sn) & 15) == 0 &&
+                         part_stride % 8 == 0 && q_out_stride % 8 == 0;
+    const bool vec = aligned && (hd == 64 || hd == 128 || hd == 256);
+#define LAUNCH_V(TA, TQ, TC, E) e = ub_launch_dependent(qk_prepare_vec_kernel<TA, TQ, TC, E>, dim3(grid), dim3(wpb * 32), 0, st, \
         (const TA*)qkv, n_parts, part_stride, (TQ*)q_out, q_out_stride, qw, kw, cs, sn, tok_pos, tok_seq, \
         (TC*)kcache, (TC*)vcache, c, n_tokens, nh, eps, write_kv)
+#define LAUNCH(TA, TQ, TC) do { \
+        if (vec && hd == 64) LAUNCH_V(TA, TQ, TC, 2); else if (vec && hd == 128) LAUNCH_V(TA, TQ, TC, 4); \
+        else if (vec && hd == 256) LAUNCH_V(TA, TQ, TC, 8); \
+        else e = ub_launch_dependent(qk_prepare_kernel<TA, TQ, TC>, dim3(grid), dim3(wpb * 32), 0, st, \
+        (const TA*)qkv, n_parts, part_stride, (TQ*)q_out, q_out_stride, qw, kw, cs, sn, tok_pos, tok_seq, \
+        (TC*)kcache, (TC*)vcache, c, n_tokens, nh, eps, write_kv); } while (0)
     if (in_dtype == UB_F32 && q_dtype == UB_F32 && cache_dtype == UB_F32) LAUNCH(float, float, float);
     else if (in_dtype == UB_BF16 && q_dtype == UB_BF16 && cache_dtype == UB_BF16) LAUNCH(__nv_bfloat16, __nv_bfloat16, __nv_bfloat16);
     else if (in_dtype == UB_F32 && q_dtype == UB_BF16 && cache_dtype == UB_BF16) LAUNCH(float, __nv_bfloat16, __nv_bfloat16);
     else if (in_dtype == UB_F32 && q_dtype == UB_F32 && cache_dtype == UB_BF16) LAUNCH(float, float, __nv_bfloat16);
     else return UB_ERR_UNSUPPORTED;
 #undef LAUNCH
+#undef LAUNCH_V
     return (int)e;
 }
 

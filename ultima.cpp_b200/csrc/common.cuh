@@ -48,6 +48,36 @@ static inline cudaError_t ub_launch_dependent(void (*kern)(KArgs...), dim3 grid,
     return cudaLaunchKernelEx(&cfg, kern, KArgs(args)...);
 }
 
+// E consecutive elements (E * sizeof(T) bytes: 4, 8, 16 or 32, aligned to min(16, that)) to and
+// from float registers.
+template <typename T, int E>
+__device__ __forceinline__ void load_vec(const T* p, float* out) {
+    constexpr int NB = sizeof(T) * E;
+    static_assert(NB == 4 || NB == 8 || NB % 16 == 0, "vector of 4, 8 or a multiple of 16 bytes");
+    alignas(16) T tmp[E];
+    if constexpr (NB == 4) *reinterpret_cast<uint32_t*>(tmp) = *reinterpret_cast<const uint32_t*>(p);
+    else if constexpr (NB == 8) *reinterpret_cast<uint2*>(tmp) = *reinterpret_cast<const uint2*>(p);
+    else {
+#pragma unroll
+        for (int i = 0; i < NB / 16; ++i) reinterpret_cast<uint4*>(tmp)[i] = reinterpret_cast<const uint4*>(p)[i];
+    }
+#pragma unroll
+    for (int i = 0; i < E; ++i) out[i] = to_f32<T>(tmp[i]);
+}
+template <typename T, int E>
+__device__ __forceinline__ void store_vec(T* p, const float* v) {
+    constexpr int NB = sizeof(T) * E;
+    alignas(16) T tmp[E];
+#pragma unroll
+    for (int i = 0; i < E; ++i) tmp[i] = from_f32<T>(v[i]);
+    if constexpr (NB == 4) *reinterpret_cast<uint32_t*>(p) = *reinterpret_cast<const uint32_t*>(tmp);
+    else if constexpr (NB == 8) *reinterpret_cast<uint2*>(p) = *reinterpret_cast<const uint2*>(tmp);
+    else {
+#pragma unroll
+        for (int i = 0; i < NB / 16; ++i) reinterpret_cast<uint4*>(p)[i] = reinterpret_cast<const uint4*>(tmp)[i];
+    }
+}
+
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
