@@ -191,7 +191,7 @@ def run_ours(args):
     engine = Engine(spec, tensors, dtype="bfloat16", max_tokens=64 * per_seq, max_seqs=64,
                     max_step_tokens=PREFILL_TOKENS, max_context=CONTEXT)
     del tensors
-    sampler = Sampler(dev, cfg.vocab_size)
+    sampler = Sampler(dev, cfg.vocab_size, engine.rt)
     rng = np.random.default_rng(0)
     engine.warm_up()
     print(f"[bench] model ready in {time.time() - t0:.1f} s", file=sys.stderr, flush=True)
@@ -255,7 +255,7 @@ def run_ours(args):
     e2e_val = BATCH * (n_new - 1) / stats.decode_s
     h2d = engine.last_h2d_bytes + BATCH * 64      # the step's batch record and the sampler's records
     e2e = {"value": round(e2e_val, 1), "unit": "tokens/s", "h2d_bytes_per_step": int(h2d),
-           "d2h_bytes_per_step": 4 * BATCH}
+           "d2h_bytes_per_step": 4 * (BATCH + 4)}          # the sampled ids and the kernels' status flags
 
     engine.check_errors()
     out = {

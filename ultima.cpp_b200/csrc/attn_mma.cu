@@ -27,6 +27,13 @@ constexpr int HD = HEAD_DIM;
 constexpr int LDS = HD + 8;                 // shared-memory row stride (elements): no bank conflicts for ldmatrix
 constexpr int KT = 64;                      // keys a tile = positions a page
 constexpr int NTHREADS = 128;
+#ifndef ATTN_DSTAGES
+#define ATTN_DSTAGES 2
+#endif
+#ifndef ATTN_ALIAS
+#define ATTN_ALIAS 0        // 1: the merge buffer lies over the K/V ring (less shared memory, a third CTA an SM: measured slower)
+#endif
+constexpr int DSTAGES = ATTN_DSTAGES;       // K/V tiles in the decode kernel's ring
 constexpr int KSTEPS = HD / 16;
 constexpr int DTILES = HD / 8;
 
@@ -272,9 +279,9 @@ attn_decode_kernel(AttnParams p, PagedKV c) {
     pdl_trigger();
     pdl_wait();
     bf16* Qs = (bf16*)smem_raw;                    // [16][LDS]
-    bf16* Ks = Qs + 16 * LDS;                      // [2][64][LDS]
-    bf16* Vs = Ks + 2 * KT * LDS;
-    float* red = (float*)(Vs + 2 * KT * LDS);      // [4 warps][16 rows][HD + 2]
+    bf16* Ks = Qs + 16 * LDS;                      // [DSTAGES][64][LDS]
+    bf16* Vs = Ks + DSTAGES * KT * LDS;
+    float* red = ATTN_ALIAS ? (float*)Ks : (float*)(Vs + DSTAGES * KT * LDS);   // [4 warps][16 rows][HD + 2]
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int slice = blockIdx.x, seq = blockIdx.y, kvh = blockIdx.z;
     const int G = p.group;
@@ -301,27 +308,32 @@ attn_decode_kernel(AttnParams p, PagedKV c) {
     for (int dt = 0; dt < DTILES; ++dt) o[dt][0] = o[dt][1] = o[dt][2] = o[dt][3] = 0.f;
     float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
 
-    if (t_lo <= t_hi) {
-        load_kv_tile(Ks, Vs, p.kc, p.vc, c, seq, kvh, t_lo * KT, pos, tid);
+    // a ring of DSTAGES tiles: DSTAGES - 1 tiles are on their way while one is used.  One group of
+    // copies is committed for every tile slot, empty past the end, so the count to wait for is fixed.
+#pragma unroll
+    for (int i = 0; i < DSTAGES - 1; ++i) {
+        if (t_lo + i <= t_hi)
+            load_kv_tile(Ks + i * KT * LDS, Vs + i * KT * LDS, p.kc, p.vc, c, seq, kvh, (t_lo + i) * KT, pos, tid);
         cp_async_commit();
     }
     for (int t = t_lo; t <= t_hi; ++t) {
-        const int buf = (t - t_lo) & 1;
-        if (t < t_hi) {
-            load_kv_tile(Ks + (buf ^ 1) * KT * LDS, Vs + (buf ^ 1) * KT * LDS, p.kc, p.vc, c, seq, kvh, (t + 1) * KT, pos, tid);
-            cp_async_commit();
-            cp_async_wait<1>();
-        } else {
-            cp_async_wait<0>();
+        const int buf = (t - t_lo) % DSTAGES;
+        const int ahead = t + DSTAGES - 1;
+        if (ahead <= t_hi) {
+            const int nb = (ahead - t_lo) % DSTAGES;
+            load_kv_tile(Ks + nb * KT * LDS, Vs + nb * KT * LDS, p.kc, p.vc, c, seq, kvh, ahead * KT, pos, tid);
         }
+        cp_async_commit();
+        cp_async_wait<DSTAGES - 1>();
         __syncthreads();
         float s[2][4];
         scores<2>(s, Qs, 0, Ks + buf * KT * LDS, warp * 16, lane);
         softmax_step<2>(s, o, m, l, p.c, row_pos, row_ok, t * KT + warp * 16, p.window, lane);
         weighted_values<2>(o, s, Vs + buf * KT * LDS, warp * 16, lane);
-        __syncthreads();
+        __syncthreads();                             // the slot is filled again at the next step
     }
-    if (t_lo > t_hi) __syncthreads();               // Qs written above; keep the barrier count equal
+    cp_async_wait<0>();
+    __syncthreads();                                 // K/V no longer needed: the merge buffer lies over them
     // merge the four warps: each has (m, l, o) over its keys
     constexpr int RS = HD + 2;
 #pragma unroll
@@ -399,7 +411,8 @@ UB_API int ub_attn_mma(int mode, const void* q, long long q_stride, void* out, l
     p.part_o = part_o; p.part_ml = part_ml; p.n_slices = n_slices < 1 ? 1 : n_slices;
     static bool attr_done = false;
     const size_t sm_pre = (size_t)(64 + 4 * KT) * LDS * sizeof(bf16);
-    const size_t sm_dec = (size_t)(16 + 4 * KT) * LDS * sizeof(bf16) + (size_t)64 * (HD + 2) * sizeof(float);
+    const size_t sm_kv = (size_t)2 * DSTAGES * KT * LDS * sizeof(bf16), sm_red = (size_t)64 * (HD + 2) * sizeof(float);
+    const size_t sm_dec = (size_t)16 * LDS * sizeof(bf16) + (ATTN_ALIAS ? (sm_kv > sm_red ? sm_kv : sm_red) : sm_kv + sm_red);
     if (!attr_done) {
         cudaError_t e = cudaFuncSetAttribute(attn_prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm_pre);
         if (e == cudaSuccess) e = cudaFuncSetAttribute(attn_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm_dec);

@@ -150,6 +150,8 @@ class Engine:
         B = len(slots)
         if len(tokens) != B:
             raise StepError("step: one token list for each slot is needed")
+        if want is None and B and all(len(t) == 1 for t in tokens):
+            return self._step_one_token_each(slots, tokens)
         if want is None:
             want = [[len(t) - 1] if len(t) else [] for t in tokens]
         if len(want) != B:
@@ -225,6 +227,32 @@ class Engine:
         out = torch.empty((n_want, V), dtype=torch.float32, device=self.device)
         out[torch.tensor(order, dtype=torch.long, device=self.device)] = torch.cat(pieces, dim=0)
         return out
+
+    def _step_one_token_each(self, slots, tokens) -> torch.Tensor:
+        """The common decode step, checked with less work: one token a sequence, every logit wanted."""
+        B = len(slots)
+        if len(set(slots)) != B:
+            raise StepError("step: a slot is named twice")
+        V = self.spec.vocab_size
+        ids = [t[0] for t in tokens]
+        if min(ids) < 0 or max(ids) >= V:
+            bad = [i for i in ids if i < 0 or i >= V][0]
+            raise StepError(f"step: token id {bad} is outside the vocabulary [0, {V})")
+        before, after = [], {}
+        for s in slots:
+            self.cache.slots.check(s)
+            n = self.cache.slots.length[s]
+            if n + 1 > self.max_context:
+                raise StepError(f"step: slot {s} would reach {n + 1} positions; the limit is {self.max_context}")
+            before.append(n)
+            if n % 64 == 0:                      # only a sequence at a page's edge needs a new page
+                after[s] = n + 1
+        if after:
+            try:
+                self.cache.can_hold(after)
+            except CacheError as e:
+                raise StepError(str(e)) from e
+        return self._pass(slots, tokens, before, list(range(B)))
 
     def _pass(self, slots, new_tokens, before, want_rows) -> torch.Tensor:
         """One pass through the layers: reserve pages, lay the batch out, run, commit."""

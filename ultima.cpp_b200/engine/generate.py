@@ -89,8 +89,6 @@ def run_batch(engine, sample, prompts: list, params: list, n_predict: list, stop
         while live:
             ids = sample(logits, [params[i] for i in live], [streams[i] for i in live],
                          [len(out[i].tokens) for i in live], [out[i].tokens for i in live])
-            if hasattr(engine, "check_errors"):
-                engine.check_errors()
             now = time.perf_counter()
             if stats:
                 if first:
@@ -173,7 +171,7 @@ class LLM:
             max_tokens = self.max_batch * (-(-int(n_ctx) // page) * page)
         self.engine = Engine.from_dir(model_dir, dtype=dtype, max_tokens=max_tokens, max_context=n_ctx,
                                       max_seqs=self.max_batch, device=device, **engine_kw)
-        self.sampler = Sampler(self.engine.device, self.engine.spec.vocab_size)
+        self.sampler = Sampler(self.engine.device, self.engine.spec.vocab_size, self.engine.rt)
         self.stop_token_ids = tuple(self.engine.spec.stop_token_ids)
         self.last_stats = None
 

@@ -70,7 +70,9 @@ class Runtime:
         self.use_tensor_cores = dtype == torch.bfloat16
         self.launches = 0              # kernels of this library launched through the runtime
         # flags the kernels raise: [0] a token id outside the vocabulary, [1] a wait that ran out
-        self.status = torch.zeros(4, dtype=torch.int32, device=self.device)
+        # (they are the head of a buffer whose tail takes the sampled token ids: one copy brings both)
+        self.status_and_ids = torch.zeros(4 + 4096, dtype=torch.int32, device=self.device)
+        self.status = self.status_and_ids[:4]
 
     def shared(self, key, make):
         """One object for all parts that ask with the same key (rotation tables and the like)."""

@@ -17,7 +17,8 @@ _libs: dict = {}
 
 
 def target(head_dim: int):
-    return (SOURCE, (f"HEAD_DIM={int(head_dim)}",))
+    extra = tuple(x for x in _os.environ.get("ULTIMA_ATTN_DEFINES", "").split(",") if x)
+    return (SOURCE, (f"HEAD_DIM={int(head_dim)}",) + extra)
 
 
 def lib(head_dim: int):

@@ -31,9 +31,44 @@ def uniform_of(stream: int, counter: int) -> float:
 
 
 class Sampler:
-    def __init__(self, device, vocab_size: int):
+    """``runtime`` (optional): the engine's runtime; its status flags then come back with the token
+    ids in the same copy, and a raised flag is an error here."""
+
+    def __init__(self, device, vocab_size: int, runtime=None):
         self.device, self.vocab_size = torch.device(device), int(vocab_size)
+        self.rt = runtime
         self._work = None
+        self._cache_key = None
+        self._cache = None
+        if runtime is not None and getattr(runtime, "status_and_ids", None) is not None:
+            self._out = runtime.status_and_ids
+        else:
+            self._out = torch.zeros(4 + 4096, dtype=torch.int32, device=self.device)
+        self._dummy_i = torch.zeros(1, dtype=torch.int32, device=self.device)
+        self._dummy_f = torch.zeros(1, dtype=torch.float32, device=self.device)
+
+    def _records(self, params: list, streams: list):
+        """The per-row records for these parameters and streams, without counters and history
+        (kept from call to call: a batch samples with the same parameters every step)."""
+        key = (tuple((id(p), p.temperature, p.top_k, p.top_p, p.min_p, p.rep_penalty, p.repeat_last_n,
+                      p.frequency_penalty, p.presence_penalty, p.dry_multiplier, p.dry_last_n, len(p.logit_bias))
+                     for p in params), tuple(streams))
+        if key != self._cache_key:
+            rec = np.zeros(len(params), dtype=ops.SAMPLE_DTYPE)
+            plain = True
+            for i, p in enumerate(params):
+                r = rec[i]
+                r["temperature"], r["top_p"], r["min_p"], r["rep_penalty"] = p.temperature, p.top_p, p.min_p, p.rep_penalty
+                r["freq_penalty"], r["presence_penalty"] = p.frequency_penalty, p.presence_penalty
+                r["dry_multiplier"], r["dry_base"] = p.dry_multiplier, p.dry_base
+                r["top_k"], r["repeat_last_n"], r["dry_last_n"] = p.top_k, p.repeat_last_n, p.dry_last_n
+                r["dry_allowed_len"] = p.dry_allowed_len
+                r["seed"] = streams[i] & _MASK
+                if p.history_window() > 0 or p.logit_bias:
+                    plain = False
+            greedy = all(p.greedy for p in params)
+            self._cache_key, self._cache = key, (rec, plain, greedy)
+        return self._cache
 
     def sample(self, logits: torch.Tensor, params: list, streams: list, counters: list,
                recents: list | None = None) -> list[int]:
@@ -42,37 +77,38 @@ class Sampler:
         n = logits.shape[0]
         if n == 0:
             return []
-        rec = np.zeros(n, dtype=ops.SAMPLE_DTYPE)
-        recent_flat, bias_ids, bias_vals = [], [], []
-        need_work = False
-        for i, p in enumerate(params):
-            r = rec[i]
-            r["temperature"], r["top_p"], r["min_p"], r["rep_penalty"] = p.temperature, p.top_p, p.min_p, p.rep_penalty
-            r["freq_penalty"], r["presence_penalty"] = p.frequency_penalty, p.presence_penalty
-            r["dry_multiplier"], r["dry_base"] = p.dry_multiplier, p.dry_base
-            r["top_k"], r["repeat_last_n"], r["dry_last_n"] = p.top_k, p.repeat_last_n, p.dry_last_n
-            r["dry_allowed_len"] = p.dry_allowed_len
-            r["seed"], r["counter"] = streams[i] & _MASK, counters[i]
-            win = p.history_window()
-            hist = list(recents[i][-win:]) if (recents is not None and win > 0) else []
-            r["n_recent"], r["recent_offset"] = len(hist), len(recent_flat)
-            recent_flat.extend(hist)
-            r["n_bias"], r["bias_offset"] = len(p.logit_bias), len(bias_ids)
-            for k, v in p.logit_bias.items():
-                bias_ids.append(int(k))
-                bias_vals.append(float(v))
-            if not p.greedy or hist or p.logit_bias:
-                need_work = True
+        if n > self._out.numel() - 4:
+            raise ValueError(f"at most {self._out.numel() - 4} rows a call")
+        base, plain, greedy = self._records(params, streams)
+        rec = base.copy()
+        rec["counter"] = np.asarray(counters, dtype=np.uint64)
         dev = self.device
+        recent_dev, bid_dev, bval_dev = self._dummy_i, self._dummy_i, self._dummy_f
+        if not plain:
+            recent_flat, bias_ids, bias_vals = [], [], []
+            for i, p in enumerate(params):
+                win = p.history_window()
+                hist = list(recents[i][-win:]) if (recents is not None and win > 0) else []
+                rec[i]["n_recent"], rec[i]["recent_offset"] = len(hist), len(recent_flat)
+                recent_flat.extend(hist)
+                rec[i]["n_bias"], rec[i]["bias_offset"] = len(p.logit_bias), len(bias_ids)
+                for k, v in p.logit_bias.items():
+                    bias_ids.append(int(k))
+                    bias_vals.append(float(v))
+            if recent_flat:
+                recent_dev = torch.tensor(recent_flat, dtype=torch.int32).to(dev, non_blocking=True)
+            if bias_ids:
+                bid_dev = torch.tensor(bias_ids, dtype=torch.int32).to(dev, non_blocking=True)
+                bval_dev = torch.tensor(bias_vals, dtype=torch.float32).to(dev, non_blocking=True)
         params_dev = torch.from_numpy(rec.view(np.uint8).reshape(-1)).to(dev, non_blocking=True)
-        recent_dev = torch.tensor(recent_flat or [0], dtype=torch.int32).to(dev, non_blocking=True)
-        bid_dev = torch.tensor(bias_ids or [0], dtype=torch.int32).to(dev, non_blocking=True)
-        bval_dev = torch.tensor(bias_vals or [0.0], dtype=torch.float32).to(dev, non_blocking=True)
         work = None
-        if need_work:
+        if not (greedy and plain):
             if self._work is None or self._work.numel() < n * self.vocab_size:
                 self._work = torch.empty(n * self.vocab_size, dtype=torch.float32, device=dev)
             work = self._work
-        out = torch.empty(n, dtype=torch.int32, device=dev)
+        out = self._out[4:4 + n]
         ops.sample(logits, work, params_dev, recent_dev, bid_dev, bval_dev, out)
-        return out.cpu().tolist()
+        host = self._out[:4 + n].cpu().tolist()          # the status flags travel with the ids
+        if self.rt is not None and any(host[:4]):
+            self.rt.check_status()
+        return host[4:]
