@@ -341,7 +341,7 @@ class _B:
     pass
 
 
-def _attn_tc_case(nh, nkv, hd, window, befores, news, seed, slices=None, ring_pages=12):
+def _attn_tc_case(nh, nkv, hd, window, befores, news, seed, slices=None, ring_pages=12, kernel=None):
     """Sequences with ``befores[i]`` cached positions bring ``news[i]`` new tokens."""
     from ultima_b200.kernels import attn_tc
     from ultima_b200.engine import Runtime
@@ -362,8 +362,9 @@ def _attn_tc_case(nh, nkv, hd, window, befores, news, seed, slices=None, ring_pa
     b.n_seqs, b.max_new, b.max_after = len(lens), max(news), max(lens)
     kv = _KV(kc, vc, table, ring_pages * 64, window or None)
     assert attn_tc.accepts(q, kv, hd, nh, nkv)
-    attn_tc.attention(q, kv, out, b, nh, nkv, hd, 1 / math.sqrt(hd), rt, slices=slices)
+    attn_tc.attention(q, kv, out, b, nh, nkv, hd, 1 / math.sqrt(hd), rt, slices=slices, kernel=kernel)
     torch.cuda.synchronize()
+    rt.check_status()
     worst = 0.0
     for s, (bf, n) in enumerate(zip(befores, news)):
         k, v = dense[s]
@@ -382,8 +383,55 @@ def _attn_tc_case(nh, nkv, hd, window, befores, news, seed, slices=None, ring_pa
 def test_attn_mma_prefill(cfg):
     # whole prompts of unequal lengths, and continued prompts (cached positions before the new ones)
     for befores, news in (([0, 0, 0, 0], [1, 17, 64, 200]), ([5, 64, 130, 0], [70, 1, 33, 129])):
-        err = _attn_tc_case(cfg["nh"], cfg["nkv"], cfg["hd"], cfg["window"], befores, news, seed=cfg["hd"])
+        err = _attn_tc_case(cfg["nh"], cfg["nkv"], cfg["hd"], cfg["window"], befores, news, seed=cfg["hd"], kernel="mma")
         assert err <= 2 ** -7, (cfg, befores, news, err)
+
+
+@pytest.mark.parametrize("cfg", [dict(nh=8, nkv=2, hd=128, window=0), dict(nh=8, nkv=1, hd=64, window=0),
+                                 dict(nh=4, nkv=4, hd=128, window=0), dict(nh=4, nkv=2, hd=64, window=50),
+                                 dict(nh=32, nkv=2, hd=128, window=0), dict(nh=2, nkv=1, hd=128, window=130)])
+def test_attn_tcgen05_prefill(cfg):
+    """The tcgen05 prefill kernel: scores and output in tensor memory."""
+    from ultima_b200.kernels import attn_tc
+    assert attn_tc.tcgen05_fits(cfg["hd"], cfg["nh"], cfg["nkv"])
+    for befores, news in (([0, 0, 0, 0], [1, 17, 64, 200]), ([5, 64, 130, 0], [70, 1, 33, 129]), ([0], [700])):
+        err = _attn_tc_case(cfg["nh"], cfg["nkv"], cfg["hd"], cfg["window"], befores, news, seed=cfg["hd"] + 3)
+        assert err <= 2 ** -7, (cfg, befores, news, err)
+
+
+def test_attn_tcgen05_rescales_when_the_maximum_grows():
+    """Keys whose scores grow along the sequence force the reference maximum up again and again."""
+    from ultima_b200.kernels import attn_tc
+    from ultima_b200.engine import Runtime
+    rt = Runtime(DEV, torch.bfloat16)
+    nh = nkv = 1
+    hd, n = 128, 400
+    g = torch.Generator().manual_seed(0)
+    qrow = torch.randn(hd, generator=g)
+    qrow = qrow / qrow.norm()
+    k = torch.randn(n, 1, hd, generator=g) * 0.1
+    k[:, 0] += qrow[None] * torch.linspace(0, 300, n)[:, None]          # scores rise by ~26 log2 units a page
+    v = torch.randn(n, 1, hd, generator=g)
+    q = (qrow[None].repeat(n, 1) * math.sqrt(hd)).to(torch.bfloat16).to(DEV)
+    pages = 7
+    kc = torch.full((pages, 1, 64, hd), float("nan"), dtype=torch.bfloat16)
+    vc = torch.full((pages, 1, 64, hd), float("nan"), dtype=torch.bfloat16)
+    for p_ in range(n):
+        kc[p_ // 64, 0, p_ % 64], vc[p_ // 64, 0, p_ % 64] = k[p_, 0].to(torch.bfloat16), v[p_, 0].to(torch.bfloat16)
+    b = _B()
+    b.seq_start = torch.tensor([0, n], dtype=torch.int32, device=DEV)
+    b.seq_before = torch.tensor([0], dtype=torch.int32, device=DEV)
+    b.n_seqs, b.max_new, b.max_after = 1, n, n
+    kv = _KV(kc.to(DEV), vc.to(DEV), torch.arange(pages, dtype=torch.int32).view(1, -1).to(DEV), pages * 64, None)
+    out = torch.full((n, hd), float("nan"), dtype=torch.bfloat16, device=DEV)
+    attn_tc.attention(q, kv, out, b, nh, nkv, hd, 1 / math.sqrt(hd), rt)
+    torch.cuda.synchronize()
+    rt.check_status()
+    kd, vd = kc[:, 0].reshape(-1, hd)[:n].double(), vc[:, 0].reshape(-1, hd)[:n].double()
+    for t in (0, 63, 64, 200, 399):
+        s = (kd[:t + 1] @ q[t].double().cpu()) / math.sqrt(hd)
+        ref = torch.softmax(s, 0) @ vd[:t + 1]
+        assert rel_err(out[t], ref) <= 2 ** -6, t
 
 
 @pytest.mark.parametrize("cfg", [dict(nh=8, nkv=2, hd=128, window=0), dict(nh=6, nkv=3, hd=48, window=0),

@@ -1,0 +1,375 @@
+// Prefill attention over the paged bfloat16 cache on the fifth-generation tensor cores, for one
+// head size fixed at compile time (-DHEAD_DIM=64 or 128).
+//
+// One CTA takes 128 rows of one KV head, a row being (token, query head of the group), and walks
+// over the cache pages (64 keys) its rows may see.  Scores and the output live in tensor memory:
+//   S_b = Q K^T     tcgen05.mma, both operands from shared memory (TMA, 128-byte swizzle), two
+//                   score buffers so the next tile's scores are formed while this tile's are used
+//   softmax         four warps, one thread a row: tcgen05.ld of the row's 64 scores, mask, running
+//                   maximum and sum in float32, probabilities rounded to bfloat16 and stored back
+//                   over the scores (tcgen05.st), two to a 32-bit column
+//   O += P V        tcgen05.mma with P from tensor memory and V from shared memory (V is the
+//                   N-major operand: rows of keys as TMA wrote them)
+// The maximum a row's exponentials refer to is raised only when the true maximum has grown by more
+// than 2^8 (then the row's output and sum are rescaled in tensor memory), so most tiles cost no
+// pass over the output.  Rows of V the sequence has not reached are zeroed in shared memory.
+// Warp 0 issues TMA, warp 1 issues MMAs and owns the tensor-memory allocation, warps 2-5 are the
+// softmax.  Every wait has a time limit and raises a flag.
+//
+// The arithmetic restated is the reference's per-token loop (src/model/qwen_block.cpp:94-135):
+// scores q.k * scale over the visible positions (p - window, p], max-shifted softmax, weighted
+// sum of values, query head h on KV head h / (heads / kv heads).
+#include "common.cuh"
+#include "tc_common.cuh"
+
+#ifndef HEAD_DIM
+#define HEAD_DIM 128
+#endif
+static_assert(HEAD_DIM == 64 || HEAD_DIM == 128, "this kernel is built for head sizes 64 and 128");
+
+constexpr int HD = HEAD_DIM;
+constexpr int NB = HD / 64;                 // 64-column blocks of a row (one 128-byte swizzle span each)
+constexpr int BM = 128;                     // rows a CTA
+constexpr int BN = 64;                      // keys a tile = positions a page
+constexpr int KV_STAGES = 2;
+constexpr int Q_BYTES = NB * BM * 128;
+constexpr int KV_BYTES = NB * BN * 128;     // one K or V tile
+constexpr int SMEM_BYTES = Q_BYTES + 2 * KV_STAGES * KV_BYTES + 1024 + 256;
+constexpr int TMEM_COLS = 256;              // S0 [0,64) S1 [64,128) O [128, 128 + HD)
+constexpr int O_COL = 128;
+constexpr float RESCALE_STEP = 8.0f;        // log2 units the reference maximum may lag behind
+constexpr int NTHREADS = 192;
+
+typedef __nv_bfloat16 bf16;
+
+struct TcAttnParams {
+    bf16* out; long long o_stride;
+    const int* seq_start; const int* seq_before; const int* table;
+    int pages_per_seq, ring, nkv, group, window;
+    float c;                                  // scale * log2(e)
+    int* error;
+};
+
+__host__ __device__ constexpr uint32_t idesc_bf16(int m, int n, int b_mn_major) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)b_mn_major << 16) | ((uint32_t)(n >> 3) << 17) |
+           ((uint32_t)(m >> 4) << 24);
+}
+// V tile as the N-major B operand: rows of 128 bytes are keys, 8 keys a swizzle atom (1024 bytes)
+__device__ __forceinline__ uint64_t make_desc_mn(uint32_t smem_addr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr & 0x3FFFF) >> 4);
+    d |= (uint64_t)((BN * 128) >> 4) << 16;                // next 64 columns (unused: one block an MMA)
+    d |= (uint64_t)(1024 >> 4) << 32;                      // next 8 keys
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)2 << 61;
+    return d;
+}
+
+__global__ void __launch_bounds__(NTHREADS)
+attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                       const __grid_constant__ CUtensorMap map_v, TcAttnParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    pdl_trigger();
+    pdl_wait();
+    const int seq = blockIdx.y, kvh = blockIdx.z;
+    const int q0 = p.seq_start[seq], q_len = p.seq_start[seq + 1] - q0, before = p.seq_before[seq];
+    const int G = p.group;
+    const int tile = gridDim.x - 1 - blockIdx.x;          // long tiles first
+    const int R0 = tile * BM;
+    if (R0 >= q_len * G) return;
+
+    uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint8_t* q_s = smem;
+    uint8_t* k_s = q_s + Q_BYTES;
+    uint8_t* v_s = k_s + KV_STAGES * KV_BYTES;
+    uint64_t* bars = (uint64_t*)(v_s + KV_STAGES * KV_BYTES);
+    uint64_t* q_full = bars;
+    uint64_t* k_full = bars + 1;
+    uint64_t* k_empty = k_full + KV_STAGES;
+    uint64_t* v_full = k_empty + KV_STAGES;
+    uint64_t* v_empty = v_full + KV_STAGES;
+    uint64_t* s_full = v_empty + KV_STAGES;               // [2]
+    uint64_t* p_full = s_full + 2;                        // [2]
+    uint64_t* pv_done = p_full + 2;                       // [2]
+    uint32_t* tmem_slot = (uint32_t*)(pv_done + 2);
+    volatile int* err = (volatile int*)(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int last_pos = before + q_len - 1;
+    const int tok_first = R0 / G, tok_last = min(q_len - 1, (R0 + BM - 1) / G);
+    const int pos_hi = before + tok_last;
+    int pos_lo = 0;
+    if (p.window > 0) pos_lo = max(0, before + tok_first - p.window + 1);
+    const int t_lo = pos_lo / BN, n_tiles = pos_hi / BN - t_lo + 1;
+
+    if (threadIdx.x == 0) {
+        mbar_init(q_full, 1);
+        for (int s = 0; s < KV_STAGES; ++s) {
+            mbar_init(&k_full[s], 1); mbar_init(&k_empty[s], 1);
+            mbar_init(&v_full[s], 1); mbar_init(&v_empty[s], 1);
+        }
+        for (int b = 0; b < 2; ++b) { mbar_init(&s_full[b], 1); mbar_init(&p_full[b], 128); mbar_init(&pv_done[b], 1); }
+        *err = 0;
+        fence_barrier_init();
+    }
+    if (warp == 1) { tmem_alloc(tmem_slot, TMEM_COLS); tmem_relinquish(); }
+    if (warp == 0 && lane == 0) { prefetch_tmap(&map_q); prefetch_tmap(&map_k); prefetch_tmap(&map_v); }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        // ---------------- TMA ----------------
+        if (lane == 0) {
+            mbar_expect_tx(q_full, Q_BYTES);
+            for (int nb = 0; nb < NB; ++nb)
+                tma_load_3d(q_s + nb * BM * 128, &map_q, q_full, nb * 64, kvh * G, q0 + tok_first);
+            bool ok = true;
+            int armed_k = 0, armed_v = 0;
+            for (int j = 0; j < n_tiles && ok; ++j) {
+                const int s = j % KV_STAGES;
+                const uint32_t ph = (uint32_t)((j / KV_STAGES) & 1);
+                const int posn = (t_lo + j) * BN;
+                const int page = p.table[(long long)seq * p.pages_per_seq + (posn % p.ring) / BN];
+                const int row = (page * p.nkv + kvh) * BN;
+                ok = mbar_wait(&k_empty[s], ph ^ 1, err);
+                if (!ok) break;
+                mbar_expect_tx(&k_full[s], KV_BYTES);
+                for (int nb = 0; nb < NB; ++nb) tma_load_2d(k_s + s * KV_BYTES + nb * BN * 128, &map_k, &k_full[s], nb * 64, row);
+                armed_k = j + 1;
+                ok = mbar_wait(&v_empty[s], ph ^ 1, err);
+                if (!ok) break;
+                mbar_expect_tx(&v_full[s], KV_BYTES);
+                for (int nb = 0; nb < NB; ++nb) tma_load_2d(v_s + s * KV_BYTES + nb * BN * 128, &map_v, &v_full[s], nb * 64, row);
+                armed_v = j + 1;
+            }
+            if (*err) {          // let the copies in flight land before the CTA's memory goes away
+                const long long tstart = clock64();
+                while (!mbar_try_wait(q_full, 0)) if (clock64() - tstart > WAIT_LIMIT_CYCLES / 8) break;
+                for (int j = max(0, armed_k - KV_STAGES); j < armed_k; ++j)
+                    while (!mbar_try_wait(&k_full[j % KV_STAGES], (j / KV_STAGES) & 1)) if (clock64() - tstart > WAIT_LIMIT_CYCLES / 4) break;
+                for (int j = max(0, armed_v - KV_STAGES); j < armed_v; ++j)
+                    while (!mbar_try_wait(&v_full[j % KV_STAGES], (j / KV_STAGES) & 1)) if (clock64() - tstart > WAIT_LIMIT_CYCLES / 4) break;
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA ----------------
+        if (lane == 0) {
+            constexpr uint32_t idesc_qk = idesc_bf16(BM, BN, 0);
+            constexpr uint32_t idesc_pv = idesc_bf16(BM, 64, 1);
+            const uint32_t q_addr = smem_u32(q_s);
+            auto issue_qk = [&](int j) {
+                const int s = j % KV_STAGES;
+                const uint32_t k_addr = smem_u32(k_s + s * KV_BYTES);
+                const uint32_t acc = tmem_base + (uint32_t)((j & 1) * BN);
+#pragma unroll
+                for (int ks = 0; ks < HD / 16; ++ks) {
+                    const uint64_t da = make_desc(q_addr + (ks / 4) * BM * 128) + (uint64_t)(((ks % 4) * 32) >> 4);
+                    const uint64_t db = make_desc(k_addr + (ks / 4) * BN * 128) + (uint64_t)(((ks % 4) * 32) >> 4);
+                    tc_mma_bf16(acc, da, db, idesc_qk, ks > 0 ? 1u : 0u);
+                }
+                tc_commit(&s_full[j & 1]);
+                tc_commit(&k_empty[s]);
+            };
+            bool ok = mbar_wait(q_full, 0, err);
+            if (ok) ok = mbar_wait(&k_full[0], 0, err);
+            if (ok) { tc_fence_after(); issue_qk(0); }
+            for (int j = 0; j < n_tiles && ok; ++j) {
+                if (j + 1 < n_tiles) {
+                    if (j >= 1) ok = mbar_wait(&pv_done[(j + 1) & 1], (uint32_t)(((j - 1) >> 1) & 1), err);   // P of tile j-1 used
+                    if (ok) ok = mbar_wait(&k_full[(j + 1) % KV_STAGES], (uint32_t)(((j + 1) / KV_STAGES) & 1), err);
+                    if (!ok) break;
+                    tc_fence_after();
+                    issue_qk(j + 1);
+                }
+                ok = mbar_wait(&p_full[j & 1], (uint32_t)((j >> 1) & 1), err);
+                if (ok) ok = mbar_wait(&v_full[j % KV_STAGES], (uint32_t)((j / KV_STAGES) & 1), err);
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t v_addr = smem_u32(v_s + (j % KV_STAGES) * KV_BYTES);
+                const uint32_t p_t = tmem_base + (uint32_t)((j & 1) * BN);
+#pragma unroll
+                for (int ks = 0; ks < BN / 16; ++ks) {
+#pragma unroll
+                    for (int nb = 0; nb < NB; ++nb) {
+                        const uint64_t db = make_desc_mn(v_addr + nb * BN * 128 + ks * 16 * 128);
+                        tc_mma_bf16_ts(tmem_base + O_COL + nb * 64, p_t + ks * 8, db, idesc_pv, (j > 0 || ks > 0) ? 1u : 0u);
+                    }
+                }
+                tc_commit(&pv_done[j & 1]);
+                tc_commit(&v_empty[j % KV_STAGES]);
+            }
+        }
+    } else {
+        // ---------------- softmax: one thread a row ----------------
+        const int q = warp & 3;
+        const int r = q * 32 + lane;                       // row of the tile = lane of tensor memory
+        const int R = R0 + r, tok = R / G, g = R % G;
+        const bool row_ok = tok < q_len;
+        const int row_pos = before + tok;
+        const uint32_t lane_addr = tmem_base + ((uint32_t)(q * 32) << 16);
+        const int st = (warp - 2) * 32 + lane;             // 0..127 among the softmax threads
+        float m_ref = -INFINITY, l = 0.f;
+        bool ok = true;
+        for (int j = 0; j < n_tiles && ok; ++j) {
+            const int b = j & 1;
+            const int base = (t_lo + j) * BN;
+            if (base + BN - 1 > last_pos) {
+                // rows of V past the sequence's end hold whatever the page held before: make them zero
+                ok = mbar_wait(&v_full[j % KV_STAGES], (uint32_t)((j / KV_STAGES) & 1), err);
+                if (!ok) break;
+                const int first = last_pos + 1 - base;     // first row to clear (>= 1: the tile holds a valid key)
+                uint8_t* vt = v_s + (j % KV_STAGES) * KV_BYTES;
+                for (int i = st; i < (BN - first) * NB * 8; i += 128) {
+                    const int row = first + i / (NB * 8), rest = i % (NB * 8);
+                    *reinterpret_cast<uint4*>(vt + (rest / 8) * BN * 128 + row * 128 + (rest % 8) * 16) = make_uint4(0, 0, 0, 0);
+                }
+                fence_proxy_async();
+            }
+            ok = mbar_wait(&s_full[b], (uint32_t)((j >> 1) & 1), err);
+            if (!ok) break;
+            tc_fence_after();
+            uint32_t raw[BN];
+            tmem_ld32(lane_addr + (uint32_t)(b * BN), raw);
+            tmem_ld32(lane_addr + (uint32_t)(b * BN + 32), raw + 32);
+            tmem_ld_wait();
+            float mx = -INFINITY;
+#pragma unroll
+            for (int cI = 0; cI < BN; ++cI) {
+                const int kp = base + cI;
+                const bool vis = row_ok && kp <= row_pos && (p.window <= 0 || kp > row_pos - p.window);
+                const float v = vis ? __uint_as_float(raw[cI]) * p.c : -INFINITY;
+                raw[cI] = __float_as_uint(v);
+                mx = fmaxf(mx, v);
+            }
+            // raise the reference maximum only when it lags by more than RESCALE_STEP (or is not set)
+            const bool grow = mx > m_ref + RESCALE_STEP || (m_ref == -INFINITY && mx > -INFINITY);
+            if (__any_sync(0xffffffffu, grow)) {
+                const float m_new = grow ? mx : m_ref;
+                const float f = (m_ref == -INFINITY || !grow) ? (grow ? 0.f : 1.f) : exp2f(m_ref - m_new);
+                if (j > 0) {
+                    ok = mbar_wait(&pv_done[(j - 1) & 1], (uint32_t)(((j - 1) >> 1) & 1), err);   // O is at rest
+                    if (!ok) break;
+                    tc_fence_after();
+#pragma unroll
+                    for (int cb = 0; cb < HD / 32; ++cb) {
+                        uint32_t oo[32];
+                        tmem_ld32(lane_addr + (uint32_t)(O_COL + cb * 32), oo);
+                        tmem_ld_wait();
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) oo[i] = __float_as_uint(__uint_as_float(oo[i]) * f);
+                        tmem_st32(lane_addr + (uint32_t)(O_COL + cb * 32), oo);
+                    }
+                    tmem_st_wait();
+                }
+                l *= f;
+                m_ref = m_new;
+            }
+            const float mb = m_ref == -INFINITY ? 0.f : m_ref;
+            uint32_t packed[BN / 2];
+            float sum = 0.f;
+#pragma unroll
+            for (int cI = 0; cI < BN; cI += 2) {
+                const float p0 = exp2f(__uint_as_float(raw[cI]) - mb), p1 = exp2f(__uint_as_float(raw[cI + 1]) - mb);
+                sum += p0 + p1;
+                __nv_bfloat162 pr = __floats2bfloat162_rn(p0, p1);
+                packed[cI / 2] = *reinterpret_cast<uint32_t*>(&pr);
+            }
+            l += sum;
+            tmem_st32(lane_addr + (uint32_t)(b * BN), packed);
+            tmem_st_wait();
+            tc_fence_before();
+            mbar_arrive(&p_full[b]);
+        }
+        if (ok) ok = mbar_wait(&pv_done[(n_tiles - 1) & 1], (uint32_t)(((n_tiles - 1) >> 1) & 1), err);
+        if (ok) {
+            tc_fence_after();
+            const float inv = l > 0.f ? 1.0f / l : 0.f;
+            bf16* dst = p.out + (long long)(q0 + tok) * p.o_stride + (long long)(kvh * G + g) * HD;
+#pragma unroll
+            for (int cb = 0; cb < HD / 32; ++cb) {
+                uint32_t oo[32];
+                tmem_ld32(lane_addr + (uint32_t)(O_COL + cb * 32), oo);
+                tmem_ld_wait();
+                if (row_ok) {
+#pragma unroll
+                    for (int i = 0; i < 32; i += 8) {
+                        uint4 w;
+                        __nv_bfloat162 a0 = __floats2bfloat162_rn(__uint_as_float(oo[i]) * inv, __uint_as_float(oo[i + 1]) * inv);
+                        __nv_bfloat162 a1 = __floats2bfloat162_rn(__uint_as_float(oo[i + 2]) * inv, __uint_as_float(oo[i + 3]) * inv);
+                        __nv_bfloat162 a2 = __floats2bfloat162_rn(__uint_as_float(oo[i + 4]) * inv, __uint_as_float(oo[i + 5]) * inv);
+                        __nv_bfloat162 a3 = __floats2bfloat162_rn(__uint_as_float(oo[i + 6]) * inv, __uint_as_float(oo[i + 7]) * inv);
+                        w.x = *reinterpret_cast<uint32_t*>(&a0); w.y = *reinterpret_cast<uint32_t*>(&a1);
+                        w.z = *reinterpret_cast<uint32_t*>(&a2); w.w = *reinterpret_cast<uint32_t*>(&a3);
+                        *reinterpret_cast<uint4*>(dst + cb * 32 + i) = w;
+                    }
+                }
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, TMEM_COLS);
+    }
+    if (threadIdx.x == 0 && *err) atomicExch(p.error, 1);
+}
+
+// ---------------------------------------------------------------------------------------
+UB_API int ub_attn_tc_head_dim() { return HD; }
+
+// tensor map of q as [tokens, heads, HD] (row stride q_stride elements), boxes of 64 x group x 128/group
+UB_API int ub_attn_tc_map_q(void* out_map, const void* q, long long n_tokens, int nh, long long q_stride, int group) {
+    EncodeTiledFn enc = tensor_map_encoder();
+    if (!enc) return UB_ERR_UNSUPPORTED;
+    if (((uintptr_t)q & 15) || (q_stride * 2) % 16 != 0 || group < 1 || BM % group != 0 || n_tokens < 1) return UB_ERR_ARG;
+    cuuint64_t dims[3] = {(cuuint64_t)HD, (cuuint64_t)nh, (cuuint64_t)n_tokens};
+    cuuint64_t strides[2] = {(cuuint64_t)HD * 2, (cuuint64_t)q_stride * 2};
+    cuuint32_t box[3] = {64, (cuuint32_t)group, (cuuint32_t)(BM / group)};
+    cuuint32_t estr[3] = {1, 1, 1};
+    CUresult r = enc((CUtensorMap*)out_map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, (void*)q, dims, strides, box, estr,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? 0 : UB_ERR_ARG;
+}
+// tensor map of one run's K or V cache [pages, kv heads, 64, HD] as rows of HD, boxes of 64 x 64
+UB_API int ub_attn_tc_map_kv(void* out_map, const void* cache, long long n_pages, int nkv) {
+    EncodeTiledFn enc = tensor_map_encoder();
+    if (!enc) return UB_ERR_UNSUPPORTED;
+    if (((uintptr_t)cache & 15) || n_pages < 1) return UB_ERR_ARG;
+    cuuint64_t dims[2] = {(cuuint64_t)HD, (cuuint64_t)(n_pages * nkv * BN)};
+    cuuint64_t strides[1] = {(cuuint64_t)HD * 2};
+    cuuint32_t box[2] = {64, (cuuint32_t)BN};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = enc((CUtensorMap*)out_map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (void*)cache, dims, strides, box, estr,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? 0 : UB_ERR_ARG;
+}
+
+UB_API int ub_attn_prefill_tc(const void* map_q, const void* map_k, const void* map_v, void* out, long long o_stride,
+                              const int* seq_start, const int* seq_before, const int* table, int pages_per_seq,
+                              int ring, int page, int n_seqs, int max_new, int nh, int nkv, int window, float scale,
+                              int* error, cudaStream_t st) {
+    if (n_seqs <= 0 || max_new <= 0) return 0;
+    const int group = nh / nkv;
+    if (page != BN || ring % page != 0 || nh % nkv != 0 || BM % group != 0 || (o_stride % 8) != 0 || ((uintptr_t)out & 15))
+        return UB_ERR_ARG;
+    if (n_seqs > 65535 || nkv > 65535) return UB_ERR_ARG;
+    static bool attr_done = false;
+    if (!attr_done) {
+        cudaError_t e = cudaFuncSetAttribute(attn_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+        if (e != cudaSuccess) return (int)e;
+        attr_done = true;
+    }
+    TcAttnParams p;
+    p.out = (bf16*)out; p.o_stride = o_stride; p.seq_start = seq_start; p.seq_before = seq_before; p.table = table;
+    p.pages_per_seq = pages_per_seq; p.ring = ring; p.nkv = nkv; p.group = group; p.window = window;
+    p.c = scale * 1.4426950408889634f; p.error = error;
+    dim3 grid((max_new * group + BM - 1) / BM, n_seqs, nkv);
+    cudaError_t e = ub_launch_dependent(attn_prefill_tc_kernel, grid, dim3(NTHREADS), (size_t)SMEM_BYTES, st,
+                                        *(const CUtensorMap*)map_q, *(const CUtensorMap*)map_k, *(const CUtensorMap*)map_v, p);
+    return (int)e;
+}

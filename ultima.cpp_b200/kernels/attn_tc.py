@@ -36,6 +36,69 @@ def lib(head_dim: int):
     return L
 
 
+TC_SOURCE = "attn_tcgen05.cu"
+_tc_libs: dict = {}
+_tc_maps: dict = {}
+USE_TCGEN05 = _os.environ.get("ULTIMA_ATTN_TCGEN05", "1") != "0"
+
+
+def tc_target(head_dim: int):
+    return (TC_SOURCE, (f"HEAD_DIM={int(head_dim)}",))
+
+
+def tc_lib(head_dim: int):
+    L = _tc_libs.get(head_dim)
+    if L is None:
+        L = build.load(*tc_target(head_dim))
+        L.ub_attn_tc_map_q.argtypes = [c_void_p, c_void_p, c_longlong, c_int, c_longlong, c_int]
+        L.ub_attn_tc_map_q.restype = c_int
+        L.ub_attn_tc_map_kv.argtypes = [c_void_p, c_void_p, c_longlong, c_int]
+        L.ub_attn_tc_map_kv.restype = c_int
+        L.ub_attn_prefill_tc.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p,
+                                         c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p,
+                                         c_void_p]
+        L.ub_attn_prefill_tc.restype = c_int
+        _tc_libs[head_dim] = L
+    return L
+
+
+def tcgen05_fits(head_dim: int, n_heads: int, n_kv_heads: int) -> bool:
+    """The tcgen05 prefill kernel: head sizes 64 and 128, groups that divide its 128 rows."""
+    return USE_TCGEN05 and head_dim in (64, 128) and 128 % (n_heads // n_kv_heads) == 0
+
+
+def _tc_map(key, make):
+    import ctypes
+    hit = _tc_maps.get(key)
+    if hit is not None:
+        return hit[1]
+    raw = ctypes.create_string_buffer(128 + 64)
+    addr = (ctypes.addressof(raw) + 63) & ~63
+    rc = make(addr)
+    if rc != 0:
+        raise KernelError(f"tensor map for attention could not be made (code {rc})")
+    if len(_tc_maps) > 1024:
+        _tc_maps.clear()
+    _tc_maps[key] = (raw, addr)
+    return addr
+
+
+def prefill_tcgen05(q, kv, out, batch, n_heads, n_kv_heads, head_dim, scale, rt):
+    L = tc_lib(head_dim)
+    group = n_heads // n_kv_heads
+    T = q.shape[0]
+    mq = _tc_map(("q", q.data_ptr(), T, n_heads, q.stride(0), group, head_dim),
+                 lambda a: L.ub_attn_tc_map_q(a, q.data_ptr(), T, n_heads, q.stride(0), group))
+    mk = _tc_map(("kv", kv.k.data_ptr(), kv.k.shape[0], n_kv_heads, head_dim),
+                 lambda a: L.ub_attn_tc_map_kv(a, kv.k.data_ptr(), kv.k.shape[0], n_kv_heads))
+    mv = _tc_map(("kv", kv.v.data_ptr(), kv.v.shape[0], n_kv_heads, head_dim),
+                 lambda a: L.ub_attn_tc_map_kv(a, kv.v.data_ptr(), kv.v.shape[0], n_kv_heads))
+    rc = L.ub_attn_prefill_tc(mq, mk, mv, _ptr(out), out.stride(0), _ptr(batch.seq_start), _ptr(batch.seq_before),
+                              _ptr(kv.table), kv.table.shape[1], kv.ring, kv.page, batch.n_seqs, batch.max_new,
+                              n_heads, n_kv_heads, int(kv.window or 0), float(scale), _ptr(rt.status[1:2]), _stream())
+    _check(rc, "attn_prefill_tc")
+
+
 def accepts(q, kv, head_dim, n_heads, n_kv_heads) -> bool:
     return (q.dtype == torch.bfloat16 and kv.k.dtype == torch.bfloat16 and head_dim % 16 == 0
             and 16 <= head_dim <= 256 and kv.page == 64 and q.stride(1) == 1 and q.stride(0) % 8 == 0
@@ -52,11 +115,16 @@ def decode_slices(n_seqs: int, n_kv_heads: int, longest: int, window) -> int:
     return 1 << (n.bit_length() - 1)            # a power of two: few distinct captured graphs
 
 
-def attention(q, kv, out, batch, n_heads, n_kv_heads, head_dim, scale, rt, slices: int | None = None):
+def attention(q, kv, out, batch, n_heads, n_kv_heads, head_dim, scale, rt, slices: int | None = None,
+              kernel: str | None = None):
+    """kernel: None picks (tcgen05 for prompts where it fits, mma.sync otherwise); "mma" forces the latter."""
     L = lib(head_dim)
     assert out.dtype == torch.bfloat16 and out.stride(1) == 1
     group = n_heads // n_kv_heads
     decode = batch.max_new == 1 and group <= 16
+    if (not decode and kernel != "mma" and tcgen05_fits(head_dim, n_heads, n_kv_heads) and out.stride(0) % 8 == 0
+            and out.data_ptr() % 16 == 0 and kv.k.is_contiguous() and kv.v.is_contiguous()):
+        return prefill_tcgen05(q, kv, out, batch, n_heads, n_kv_heads, head_dim, scale, rt)
     part_o = part_ml = None
     n_slices = 1
     if decode:

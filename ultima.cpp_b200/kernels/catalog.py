@@ -8,8 +8,12 @@ PLAIN = [("basic.cu", ()), ("gemm_simt.cu", ()), ("attn_simple.cu", ()), ("sampl
 HEAD_DIMS = (16, 32, 48, 64, 80, 96, 112, 128, 256)
 
 
+TC_HEAD_DIMS = (64, 128)          # head sizes the tcgen05 prefill attention is written for
+
+
 def all_targets() -> list:
-    return list(PLAIN) + [("attn_mma.cu", (f"HEAD_DIM={hd}",)) for hd in HEAD_DIMS]
+    return (list(PLAIN) + [("attn_mma.cu", (f"HEAD_DIM={hd}",)) for hd in HEAD_DIMS]
+            + [("attn_tcgen05.cu", (f"HEAD_DIM={hd}",)) for hd in TC_HEAD_DIMS])
 
 
 def targets_for_model(spec, dtype) -> list:
@@ -20,4 +24,5 @@ def targets_for_model(spec, dtype) -> list:
     if dtype == torch.bfloat16:
         dims = sorted({L.mixer.get("head_dim") for L in spec.layers if L.mixer.get("head_dim")})
         out += [("attn_mma.cu", (f"HEAD_DIM={hd}",)) for hd in dims if hd % 16 == 0 and hd <= 256]
+        out += [("attn_tcgen05.cu", (f"HEAD_DIM={hd}",)) for hd in dims if hd in TC_HEAD_DIMS]
     return out
