@@ -399,6 +399,16 @@ def test_attn_tcgen05_prefill(cfg):
         assert err <= 2 ** -7, (cfg, befores, news, err)
 
 
+@pytest.mark.parametrize("cfg", [dict(nh=8, nkv=2, hd=128, window=0), dict(nh=8, nkv=1, hd=64, window=0),
+                                 dict(nh=16, nkv=1, hd=128, window=0), dict(nh=4, nkv=2, hd=64, window=50)])
+@pytest.mark.parametrize("slices", [None, 1, 3])
+def test_attn_tcgen05_decode(cfg, slices):
+    befores = [0, 63, 64, 300, 700]
+    err = _attn_tc_case(cfg["nh"], cfg["nkv"], cfg["hd"], cfg["window"], befores, [1] * 5, seed=cfg["hd"] + 9,
+                        slices=slices, kernel="tc")
+    assert err <= 2 ** -7, (cfg, slices, err)
+
+
 def test_attn_tcgen05_rescales_when_the_maximum_grows():
     """Keys whose scores grow along the sequence force the reference maximum up again and again."""
     from ultima_b200.kernels import attn_tc

@@ -1,5 +1,5 @@
-// Prefill attention over the paged bfloat16 cache on the fifth-generation tensor cores, for one
-// head size fixed at compile time (-DHEAD_DIM=64 or 128).
+// Attention over the paged bfloat16 cache on the fifth-generation tensor cores, for prompts and for
+// decode steps, for one head size fixed at compile time (-DHEAD_DIM=64 or 128).
 //
 // One CTA takes 128 rows of one KV head, a row being (token, query head of the group), and walks
 // over the cache pages (64 keys) its rows may see.  Scores and the output live in tensor memory:
@@ -31,14 +31,16 @@ constexpr int HD = HEAD_DIM;
 constexpr int NB = HD / 64;                 // 64-column blocks of a row (one 128-byte swizzle span each)
 constexpr int BM = 128;                     // rows a CTA
 constexpr int BN = 64;                      // keys a tile = positions a page
-constexpr int KV_STAGES = 2;
 constexpr int Q_BYTES = NB * BM * 128;
 constexpr int KV_BYTES = NB * BN * 128;     // one K or V tile
-constexpr int SMEM_BYTES = Q_BYTES + 2 * KV_STAGES * KV_BYTES + 1024 + 256;
+constexpr int smem_bytes(int stages) { return Q_BYTES + 2 * stages * KV_BYTES + 1024 + 256; }
 constexpr int TMEM_COLS = 256;              // S0 [0,64) S1 [64,128) O [128, 128 + HD)
 constexpr int O_COL = 128;
 constexpr float RESCALE_STEP = 8.0f;        // log2 units the reference maximum may lag behind
 constexpr int NTHREADS = 192;
+#ifndef DECODE_STAGES
+#define DECODE_STAGES 4                     // K/V tiles in flight in the decode kernel (one CTA an SM)
+#endif
 
 typedef __nv_bfloat16 bf16;
 
@@ -48,6 +50,8 @@ struct TcAttnParams {
     int pages_per_seq, ring, nkv, group, window;
     float c;                                  // scale * log2(e)
     int* error;
+    // decode (one new token a sequence, keys in slices): unnormalised partial results
+    float* part_o; float* part_ml; int n_slices, nh;
 };
 
 __host__ __device__ constexpr uint32_t idesc_bf16(int m, int n, int b_mn_major) {
@@ -65,16 +69,20 @@ __device__ __forceinline__ uint64_t make_desc_mn(uint32_t smem_addr) {
     return d;
 }
 
+// KV_STAGES: K/V tiles in flight.  DECODE: one new token a sequence; blockIdx.x is then a slice of the
+// key range instead of a tile of rows, and with several slices the CTA writes (reference maximum,
+// sum, unnormalised output) for attn_tc_combine_kernel.
+template <int KV_STAGES, bool DECODE>
 __global__ void __launch_bounds__(NTHREADS)
-attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
-                       const __grid_constant__ CUtensorMap map_v, TcAttnParams p) {
+attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+               const __grid_constant__ CUtensorMap map_v, TcAttnParams p) {
     extern __shared__ uint8_t smem_raw[];
     pdl_trigger();
     pdl_wait();
     const int seq = blockIdx.y, kvh = blockIdx.z;
     const int q0 = p.seq_start[seq], q_len = p.seq_start[seq + 1] - q0, before = p.seq_before[seq];
     const int G = p.group;
-    const int tile = gridDim.x - 1 - blockIdx.x;          // long tiles first
+    const int tile = DECODE ? 0 : gridDim.x - 1 - blockIdx.x;          // long tiles first
     const int R0 = tile * BM;
     if (R0 >= q_len * G) return;
 
@@ -100,7 +108,13 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     const int pos_hi = before + tok_last;
     int pos_lo = 0;
     if (p.window > 0) pos_lo = max(0, before + tok_first - p.window + 1);
-    const int t_lo = pos_lo / BN, n_tiles = pos_hi / BN - t_lo + 1;
+    int t_lo = pos_lo / BN, n_tiles = pos_hi / BN - t_lo + 1;
+    if (DECODE) {                                          // this CTA's slice of the tiles (may be empty)
+        const int per = (n_tiles + p.n_slices - 1) / p.n_slices;
+        const int first = min(n_tiles, (int)blockIdx.x * per);
+        n_tiles = min(n_tiles - first, per);
+        t_lo += first;
+    }
 
     if (threadIdx.x == 0) {
         mbar_init(q_full, 1);
@@ -122,9 +136,11 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     if (warp == 0) {
         // ---------------- TMA ----------------
         if (lane == 0) {
-            mbar_expect_tx(q_full, Q_BYTES);
-            for (int nb = 0; nb < NB; ++nb)
-                tma_load_3d(q_s + nb * BM * 128, &map_q, q_full, nb * 64, kvh * G, q0 + tok_first);
+            if (n_tiles > 0) {
+                mbar_expect_tx(q_full, Q_BYTES);
+                for (int nb = 0; nb < NB; ++nb)
+                    tma_load_3d(q_s + nb * BM * 128, &map_q, q_full, nb * 64, kvh * G, q0 + tok_first);
+            }
             bool ok = true;
             int armed_k = 0, armed_v = 0;
             for (int j = 0; j < n_tiles && ok; ++j) {
@@ -146,7 +162,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             }
             if (*err) {          // let the copies in flight land before the CTA's memory goes away
                 const long long tstart = clock64();
-                while (!mbar_try_wait(q_full, 0)) if (clock64() - tstart > WAIT_LIMIT_CYCLES / 8) break;
+                while (n_tiles > 0 && !mbar_try_wait(q_full, 0)) if (clock64() - tstart > WAIT_LIMIT_CYCLES / 8) break;
                 for (int j = max(0, armed_k - KV_STAGES); j < armed_k; ++j)
                     while (!mbar_try_wait(&k_full[j % KV_STAGES], (j / KV_STAGES) & 1)) if (clock64() - tstart > WAIT_LIMIT_CYCLES / 4) break;
                 for (int j = max(0, armed_v - KV_STAGES); j < armed_v; ++j)
@@ -172,9 +188,9 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                 tc_commit(&s_full[j & 1]);
                 tc_commit(&k_empty[s]);
             };
-            bool ok = mbar_wait(q_full, 0, err);
-            if (ok) ok = mbar_wait(&k_full[0], 0, err);
-            if (ok) { tc_fence_after(); issue_qk(0); }
+            bool ok = n_tiles > 0 ? mbar_wait(q_full, 0, err) : true;
+            if (ok && n_tiles > 0) ok = mbar_wait(&k_full[0], 0, err);
+            if (ok && n_tiles > 0) { tc_fence_after(); issue_qk(0); }
             for (int j = 0; j < n_tiles && ok; ++j) {
                 if (j + 1 < n_tiles) {
                     if (j >= 1) ok = mbar_wait(&pv_done[(j + 1) & 1], (uint32_t)(((j - 1) >> 1) & 1), err);   // P of tile j-1 used
@@ -282,17 +298,30 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             tc_fence_before();
             mbar_arrive(&p_full[b]);
         }
-        if (ok) ok = mbar_wait(&pv_done[(n_tiles - 1) & 1], (uint32_t)(((n_tiles - 1) >> 1) & 1), err);
+        if (ok && n_tiles > 0) ok = mbar_wait(&pv_done[(n_tiles - 1) & 1], (uint32_t)(((n_tiles - 1) >> 1) & 1), err);
         if (ok) {
             tc_fence_after();
-            const float inv = l > 0.f ? 1.0f / l : 0.f;
-            bf16* dst = p.out + (long long)(q0 + tok) * p.o_stride + (long long)(kvh * G + g) * HD;
+            const bool partial = DECODE && p.n_slices > 1;
+            const float inv = partial ? 1.0f : (l > 0.f ? 1.0f / l : 0.f);
+            const int head = kvh * G + g;
+            bf16* dst = p.out + (long long)(q0 + tok) * p.o_stride + (long long)head * HD;
+            const long long pi = partial ? ((long long)seq * p.nh + head) * p.n_slices + blockIdx.x : 0;
+            if (partial && row_ok) { p.part_ml[pi * 2] = m_ref; p.part_ml[pi * 2 + 1] = l; }
 #pragma unroll
             for (int cb = 0; cb < HD / 32; ++cb) {
                 uint32_t oo[32];
-                tmem_ld32(lane_addr + (uint32_t)(O_COL + cb * 32), oo);
-                tmem_ld_wait();
-                if (row_ok) {
+                if (n_tiles > 0) {
+                    tmem_ld32(lane_addr + (uint32_t)(O_COL + cb * 32), oo);
+                    tmem_ld_wait();
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) oo[i] = 0;
+                }
+                if (row_ok && partial) {
+#pragma unroll
+                    for (int i = 0; i < 32; i += 4)
+                        *reinterpret_cast<uint4*>(p.part_o + pi * HD + cb * 32 + i) = make_uint4(oo[i], oo[i + 1], oo[i + 2], oo[i + 3]);
+                } else if (row_ok) {
 #pragma unroll
                     for (int i = 0; i < 32; i += 8) {
                         uint4 w;
@@ -349,27 +378,63 @@ UB_API int ub_attn_tc_map_kv(void* out_map, const void* cache, long long n_pages
     return r == CUDA_SUCCESS ? 0 : UB_ERR_ARG;
 }
 
-UB_API int ub_attn_prefill_tc(const void* map_q, const void* map_k, const void* map_v, void* out, long long o_stride,
-                              const int* seq_start, const int* seq_before, const int* table, int pages_per_seq,
-                              int ring, int page, int n_seqs, int max_new, int nh, int nkv, int window, float scale,
-                              int* error, cudaStream_t st) {
+// merge the slices of a decode step: grid (sequences * heads), HD threads
+__global__ void attn_tc_combine_kernel(TcAttnParams p) {
+    pdl_trigger();
+    pdl_wait();
+    const int sh = blockIdx.x, d = threadIdx.x;
+    const int seq = sh / p.nh, head = sh % p.nh;
+    const long long base = (long long)sh * p.n_slices;
+    float mm = -INFINITY;
+    for (int s = 0; s < p.n_slices; ++s) mm = fmaxf(mm, p.part_ml[(base + s) * 2]);
+    float acc = 0.f, ll = 0.f;
+    for (int s = 0; s < p.n_slices; ++s) {
+        const float ms = p.part_ml[(base + s) * 2];
+        const float f = ms == -INFINITY ? 0.f : exp2f(ms - mm);
+        ll += f * p.part_ml[(base + s) * 2 + 1];
+        acc += f * p.part_o[(base + s) * HD + d];
+    }
+    p.out[(long long)p.seq_start[seq] * p.o_stride + (long long)head * HD + d] = __float2bfloat16_rn(acc / ll);
+}
+
+template <int STAGES, bool DECODE>
+static int launch_attn(dim3 grid, const void* map_q, const void* map_k, const void* map_v, const TcAttnParams& p, cudaStream_t st) {
+    static bool attr_done = false;
+    auto kern = attn_tc_kernel<STAGES, DECODE>;
+    if (!attr_done) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes(STAGES));
+        if (e != cudaSuccess) return (int)e;
+        attr_done = true;
+    }
+    cudaError_t e = ub_launch_dependent(kern, grid, dim3(NTHREADS), (size_t)smem_bytes(STAGES), st,
+                                        *(const CUtensorMap*)map_q, *(const CUtensorMap*)map_k, *(const CUtensorMap*)map_v, p);
+    return (int)e;
+}
+
+// mode 0: prompts (any numbers of new tokens); mode 1: one new token a sequence, keys in n_slices slices
+// (part_o: float32 [n_seqs, nh, n_slices, HD], part_ml: [.., 2] when n_slices > 1).
+UB_API int ub_attn_tc(int mode, const void* map_q, const void* map_k, const void* map_v, void* out, long long o_stride,
+                      const int* seq_start, const int* seq_before, const int* table, int pages_per_seq,
+                      int ring, int page, int n_seqs, int max_new, int nh, int nkv, int window, float scale,
+                      int n_slices, float* part_o, float* part_ml, int* error, cudaStream_t st) {
     if (n_seqs <= 0 || max_new <= 0) return 0;
     const int group = nh / nkv;
     if (page != BN || ring % page != 0 || nh % nkv != 0 || BM % group != 0 || (o_stride % 8) != 0 || ((uintptr_t)out & 15))
         return UB_ERR_ARG;
     if (n_seqs > 65535 || nkv > 65535) return UB_ERR_ARG;
-    static bool attr_done = false;
-    if (!attr_done) {
-        cudaError_t e = cudaFuncSetAttribute(attn_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
-        if (e != cudaSuccess) return (int)e;
-        attr_done = true;
-    }
     TcAttnParams p;
     p.out = (bf16*)out; p.o_stride = o_stride; p.seq_start = seq_start; p.seq_before = seq_before; p.table = table;
     p.pages_per_seq = pages_per_seq; p.ring = ring; p.nkv = nkv; p.group = group; p.window = window;
     p.c = scale * 1.4426950408889634f; p.error = error;
-    dim3 grid((max_new * group + BM - 1) / BM, n_seqs, nkv);
-    cudaError_t e = ub_launch_dependent(attn_prefill_tc_kernel, grid, dim3(NTHREADS), (size_t)SMEM_BYTES, st,
-                                        *(const CUtensorMap*)map_q, *(const CUtensorMap*)map_k, *(const CUtensorMap*)map_v, p);
+    p.part_o = part_o; p.part_ml = part_ml; p.n_slices = n_slices < 1 ? 1 : n_slices; p.nh = nh;
+    if (mode == 0) {
+        p.n_slices = 1;
+        return launch_attn<2, false>(dim3((max_new * group + BM - 1) / BM, n_seqs, nkv), map_q, map_k, map_v, p, st);
+    }
+    if (max_new != 1) return UB_ERR_ARG;
+    if (p.n_slices > 1 && (!part_o || !part_ml || ((uintptr_t)part_o & 15))) return UB_ERR_ARG;
+    int rc = launch_attn<DECODE_STAGES, true>(dim3(p.n_slices, n_seqs, nkv), map_q, map_k, map_v, p, st);
+    if (rc != 0 || p.n_slices == 1) return rc;
+    cudaError_t e = ub_launch_dependent(attn_tc_combine_kernel, dim3(n_seqs * nh), dim3(HD), 0, st, p);
     return (int)e;
 }

@@ -40,6 +40,7 @@ TC_SOURCE = "attn_tcgen05.cu"
 _tc_libs: dict = {}
 _tc_maps: dict = {}
 USE_TCGEN05 = _os.environ.get("ULTIMA_ATTN_TCGEN05", "1") != "0"
+USE_TCGEN05_DECODE = _os.environ.get("ULTIMA_ATTN_TCGEN05_DECODE", "0") != "0"
 
 
 def tc_target(head_dim: int):
@@ -54,10 +55,10 @@ def tc_lib(head_dim: int):
         L.ub_attn_tc_map_q.restype = c_int
         L.ub_attn_tc_map_kv.argtypes = [c_void_p, c_void_p, c_longlong, c_int]
         L.ub_attn_tc_map_kv.restype = c_int
-        L.ub_attn_prefill_tc.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p,
-                                         c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p,
-                                         c_void_p]
-        L.ub_attn_prefill_tc.restype = c_int
+        L.ub_attn_tc.argtypes = [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p,
+                                 c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p,
+                                 c_void_p, c_void_p, c_void_p]
+        L.ub_attn_tc.restype = c_int
         _tc_libs[head_dim] = L
     return L
 
@@ -83,7 +84,7 @@ def _tc_map(key, make):
     return addr
 
 
-def prefill_tcgen05(q, kv, out, batch, n_heads, n_kv_heads, head_dim, scale, rt):
+def run_tcgen05(q, kv, out, batch, n_heads, n_kv_heads, head_dim, scale, rt, decode: bool, n_slices: int = 1):
     L = tc_lib(head_dim)
     group = n_heads // n_kv_heads
     T = q.shape[0]
@@ -93,10 +94,15 @@ def prefill_tcgen05(q, kv, out, batch, n_heads, n_kv_heads, head_dim, scale, rt)
                  lambda a: L.ub_attn_tc_map_kv(a, kv.k.data_ptr(), kv.k.shape[0], n_kv_heads))
     mv = _tc_map(("kv", kv.v.data_ptr(), kv.v.shape[0], n_kv_heads, head_dim),
                  lambda a: L.ub_attn_tc_map_kv(a, kv.v.data_ptr(), kv.v.shape[0], n_kv_heads))
-    rc = L.ub_attn_prefill_tc(mq, mk, mv, _ptr(out), out.stride(0), _ptr(batch.seq_start), _ptr(batch.seq_before),
-                              _ptr(kv.table), kv.table.shape[1], kv.ring, kv.page, batch.n_seqs, batch.max_new,
-                              n_heads, n_kv_heads, int(kv.window or 0), float(scale), _ptr(rt.status[1:2]), _stream())
-    _check(rc, "attn_prefill_tc")
+    part_o = part_ml = None
+    if decode and n_slices > 1:
+        part_o = rt.arena.alloc((batch.n_seqs, n_heads, n_slices, head_dim), torch.float32)
+        part_ml = rt.arena.alloc((batch.n_seqs, n_heads, n_slices, 2), torch.float32)
+    rc = L.ub_attn_tc(1 if decode else 0, mq, mk, mv, _ptr(out), out.stride(0), _ptr(batch.seq_start),
+                      _ptr(batch.seq_before), _ptr(kv.table), kv.table.shape[1], kv.ring, kv.page, batch.n_seqs,
+                      batch.max_new, n_heads, n_kv_heads, int(kv.window or 0), float(scale), n_slices,
+                      _ptr(part_o), _ptr(part_ml), _ptr(rt.status[1:2]), _stream())
+    _check(rc, "attn_tc")
 
 
 def accepts(q, kv, head_dim, n_heads, n_kv_heads) -> bool:
@@ -105,12 +111,13 @@ def accepts(q, kv, head_dim, n_heads, n_kv_heads) -> bool:
             and q.data_ptr() % 16 == 0)
 
 
-def decode_slices(n_seqs: int, n_kv_heads: int, longest: int, window) -> int:
-    """Slices of the key range, so that a decode step with few sequences still fills the GPU."""
+def decode_slices(n_seqs: int, n_kv_heads: int, longest: int, window, per_sm: int = SLICE_FACTOR) -> int:
+    """Slices of the key range, so that a decode step with few sequences still fills the GPU
+    (``per_sm`` CTAs an SM)."""
     span = longest if not window else min(longest, window + 64)
     tiles = max(1, -(-span // 64))
     ctas = n_seqs * n_kv_heads
-    want = -(-SLICE_FACTOR * N_SMS // ctas)
+    want = -(-per_sm * N_SMS // ctas)
     n = max(1, min(want, tiles, 64))
     return 1 << (n.bit_length() - 1)            # a power of two: few distinct captured graphs
 
@@ -122,9 +129,13 @@ def attention(q, kv, out, batch, n_heads, n_kv_heads, head_dim, scale, rt, slice
     assert out.dtype == torch.bfloat16 and out.stride(1) == 1
     group = n_heads // n_kv_heads
     decode = batch.max_new == 1 and group <= 16
-    if (not decode and kernel != "mma" and tcgen05_fits(head_dim, n_heads, n_kv_heads) and out.stride(0) % 8 == 0
-            and out.data_ptr() % 16 == 0 and kv.k.is_contiguous() and kv.v.is_contiguous()):
-        return prefill_tcgen05(q, kv, out, batch, n_heads, n_kv_heads, head_dim, scale, rt)
+    tc_ok = (kernel != "mma" and tcgen05_fits(head_dim, n_heads, n_kv_heads) and out.stride(0) % 8 == 0
+             and out.data_ptr() % 16 == 0 and kv.k.is_contiguous() and kv.v.is_contiguous())
+    if tc_ok and not decode:
+        return run_tcgen05(q, kv, out, batch, n_heads, n_kv_heads, head_dim, scale, rt, False)
+    if tc_ok and decode and (USE_TCGEN05_DECODE or kernel == "tc"):
+        n = slices or decode_slices(batch.n_seqs, n_kv_heads, batch.max_after, kv.window, per_sm=1)
+        return run_tcgen05(q, kv, out, batch, n_heads, n_kv_heads, head_dim, scale, rt, True, n)
     part_o = part_ml = None
     n_slices = 1
     if decode:
