@@ -452,7 +452,20 @@ def test_attn_tcgen05_rescales_when_the_maximum_grows():
 def test_attn_mma_decode(cfg, slices):
     # one token a sequence, at unequal lengths: position 0, a page edge, mid page, many pages
     befores = [0, 63, 64, 300, 700]
-    err = _attn_tc_case(cfg["nh"], cfg["nkv"], cfg["hd"], cfg["window"], befores, [1] * 5, seed=cfg["hd"] + 7, slices=slices)
+    err = _attn_tc_case(cfg["nh"], cfg["nkv"], cfg["hd"], cfg["window"], befores, [1] * 5, seed=cfg["hd"] + 7,
+                        slices=slices, kernel="mma")
+    assert err <= 2 ** -7, (cfg, slices, err)
+
+
+@pytest.mark.parametrize("cfg", [dict(nh=8, nkv=2, hd=128, window=0), dict(nh=8, nkv=1, hd=64, window=0),
+                                 dict(nh=2, nkv=2, hd=256, window=0), dict(nh=6, nkv=2, hd=64, window=50),
+                                 dict(nh=32, nkv=2, hd=128, window=0)])
+@pytest.mark.parametrize("slices", [None, 1, 3])
+def test_attn_decode_tma(cfg, slices):
+    """The decode kernel fed by TMA into swizzled shared memory, against the same oracle."""
+    befores = [0, 63, 64, 300, 700]
+    err = _attn_tc_case(cfg["nh"], cfg["nkv"], cfg["hd"], cfg["window"], befores, [1] * 5, seed=cfg["hd"] + 11,
+                        slices=slices, kernel="tma")
     assert err <= 2 ** -7, (cfg, slices, err)
 
 

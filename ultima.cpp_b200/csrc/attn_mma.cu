@@ -440,6 +440,263 @@ UB_API int ub_attn_mma(int mode, const void* q, long long q_stride, void* out, l
     return 0;
 }
 
+
+// ---------------------------------------------------------------------------------------
+// decode with TMA: the same arithmetic as attn_decode_kernel, for head sizes that are multiples
+// of 64.  A fifth warp issues one TMA copy for each 64-column block of a K or V page (128-byte
+// swizzle) into a ring of TSTAGES tiles guarded by mbarriers; the four computing warps never meet
+// at a CTA-wide barrier inside the loop: each waits for a tile, uses its own 16 keys of it and
+// gives the slot back.  ldmatrix addresses undo the swizzle (16-byte piece c of row r lies at
+// piece c ^ (r % 8)), which also makes them free of bank conflicts.
+// ---------------------------------------------------------------------------------------
+#if HEAD_DIM % 64 == 0
+#include "tc_common.cuh"
+
+#ifndef ATTN_TSTAGES
+#define ATTN_TSTAGES 3
+#endif
+constexpr int TSTAGES = ATTN_TSTAGES;
+constexpr int NBLK = HD / 64;                       // 64-column blocks of a row
+constexpr int PAGE_BYTES = KT * HD * 2;             // one K or V page of one KV head
+constexpr int BLK_BYTES = KT * 128;                 // one 64-column block of a page
+constexpr int TMA_THREADS = 160;
+
+// byte offset of element (row, col) in a tile stored as NBLK swizzled blocks of [64 rows][128 bytes]
+__device__ __forceinline__ uint32_t swz(int row, int col) {
+    return (uint32_t)((col >> 6) * BLK_BYTES + row * 128 + ((((col & 63) >> 3) ^ (row & 7)) << 4) + ((col & 7) << 1));
+}
+
+template <int NT>
+__device__ __forceinline__ void scores_swz(float (*s)[4], const bf16* Qs, uint32_t k_base, int key0, int lane) {
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) { s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.f; }
+#pragma unroll
+    for (int ks = 0; ks < KSTEPS; ++ks) {
+        uint32_t a[4];
+        ldsm_x4(smem_addr(Qs + (lane & 15) * LDS + ks * 16 + (lane >> 4) * 8), a[0], a[1], a[2], a[3]);
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) {
+            uint32_t b0, b1;
+            ldsm_x2(k_base + swz(key0 + nt * 8 + (lane & 7), ks * 16 + ((lane >> 3) & 1) * 8), b0, b1);
+            mma_bf16(s[nt], a, b0, b1);
+        }
+    }
+}
+template <int NT>
+__device__ __forceinline__ void weighted_values_swz(float (*o)[4], const float (*s)[4], uint32_t v_base, int key0, int lane) {
+#pragma unroll
+    for (int kk = 0; kk < NT / 2; ++kk) {
+        uint32_t a[4];
+        a[0] = pack_bf16(s[2 * kk][0], s[2 * kk][1]);
+        a[1] = pack_bf16(s[2 * kk][2], s[2 * kk][3]);
+        a[2] = pack_bf16(s[2 * kk + 1][0], s[2 * kk + 1][1]);
+        a[3] = pack_bf16(s[2 * kk + 1][2], s[2 * kk + 1][3]);
+#pragma unroll
+        for (int dt = 0; dt < DTILES; dt += 2) {
+            uint32_t b0, b1, b2, b3;
+            const int row = key0 + kk * 16 + ((lane >> 3) & 1) * 8 + (lane & 7);
+            const int col = dt * 8 + (lane >> 4) * 8;
+            ldsm_x4_trans(v_base + swz(row, col), b0, b1, b2, b3);
+            mma_bf16(o[dt], a, b0, b1);
+            mma_bf16(o[dt + 1], a, b2, b3);
+        }
+    }
+}
+
+struct TmaDecodeParams {
+    AttnParams a;
+    const int* table; int pages_per_seq, ring, nkv;
+    int* error;
+};
+
+__global__ void __launch_bounds__(TMA_THREADS)
+attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v, TmaDecodeParams tp) {
+    extern __shared__ uint8_t smem_raw[];
+    pdl_trigger();
+    pdl_wait();
+    const AttnParams& p = tp.a;
+    uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint8_t* ring = smem;                                  // [TSTAGES][K page | V page]
+    float* red = (float*)smem;                             // the merge buffer lies over the ring, after the loop
+    bf16* Qs = (bf16*)(smem + TSTAGES * 2 * PAGE_BYTES);   // [16][LDS]
+    uint64_t* full = (uint64_t*)(Qs + 16 * LDS);
+    uint64_t* empty = full + TSTAGES;
+    volatile int* err = (volatile int*)(empty + TSTAGES);
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int slice = blockIdx.x, seq = blockIdx.y, kvh = blockIdx.z;
+    const int G = p.group;
+    const int row = p.seq_start[seq];
+    const int pos = p.seq_before[seq];
+    int lo = 0;
+    if (p.window > 0) lo = max(0, pos - p.window + 1);
+    const int t_first = lo / KT, t_last = pos / KT;
+    const int all_tiles = t_last - t_first + 1;
+    const int per = (all_tiles + p.n_slices - 1) / p.n_slices;
+    const int t_lo = t_first + slice * per, t_hi = min(t_last, t_lo + per - 1);
+    const int n_tiles = max(0, t_hi - t_lo + 1);
+
+    if (tid == 0) {
+        for (int s = 0; s < TSTAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 4); }
+        *err = 0;
+        fence_barrier_init();
+    }
+    constexpr int CH = HD / 8;
+    for (int i = tid; i < 16 * CH; i += TMA_THREADS) {
+        const int r = i / CH, ch = i % CH;
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (r < G) v = *reinterpret_cast<const uint4*>(p.q + (long long)row * p.q_stride + (long long)(kvh * G + r) * HD + ch * 8);
+        *reinterpret_cast<uint4*>(Qs + r * LDS + ch * 8) = v;
+    }
+    __syncthreads();
+
+    float o[DTILES][4];
+#pragma unroll
+    for (int dt = 0; dt < DTILES; ++dt) o[dt][0] = o[dt][1] = o[dt][2] = o[dt][3] = 0.f;
+    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+
+    if (warp == 4) {
+        if (lane == 0) {
+            prefetch_tmap(&map_k); prefetch_tmap(&map_v);
+            int armed = 0;
+            for (int j = 0; j < n_tiles; ++j) {
+                const int s = j % TSTAGES;
+                if (!mbar_wait(&empty[s], (uint32_t)(((j / TSTAGES) & 1) ^ 1), err)) break;
+                const int posn = (t_lo + j) * KT;
+                const int page = tp.table[(long long)seq * tp.pages_per_seq + (posn % tp.ring) / KT];
+                const int r0 = (page * tp.nkv + kvh) * KT;
+                uint8_t* st = ring + s * 2 * PAGE_BYTES;
+                mbar_expect_tx(&full[s], 2 * PAGE_BYTES);
+#pragma unroll
+                for (int nb = 0; nb < NBLK; ++nb) {
+                    tma_load_2d(st + nb * BLK_BYTES, &map_k, &full[s], nb * 64, r0);
+                    tma_load_2d(st + PAGE_BYTES + nb * BLK_BYTES, &map_v, &full[s], nb * 64, r0);
+                }
+                armed = j + 1;
+            }
+            if (*err) {
+                const long long tstart = clock64();
+                for (int j = max(0, armed - TSTAGES); j < armed; ++j)
+                    while (!mbar_try_wait(&full[j % TSTAGES], (j / TSTAGES) & 1)) if (clock64() - tstart > WAIT_LIMIT_CYCLES / 4) break;
+            }
+        }
+    } else {
+        int row_pos[2] = {pos, pos};
+        bool row_ok[2] = {(lane >> 2) < G, (lane >> 2) + 8 < G};
+        for (int j = 0; j < n_tiles; ++j) {
+            const int s = j % TSTAGES;
+            if (!mbar_wait(&full[s], (uint32_t)((j / TSTAGES) & 1), err)) break;
+            const uint32_t k_base = smem_u32(ring + s * 2 * PAGE_BYTES), v_base = k_base + PAGE_BYTES;
+            const int base = (t_lo + j) * KT;
+            if (base + KT - 1 > pos) {
+                // this warp's rows of V past the sequence's end: zeros instead of what the page held before
+                for (int i = lane; i < 16 * NBLK * 8; i += 32) {
+                    const int r = warp * 16 + i / (NBLK * 8), rest = i % (NBLK * 8);
+                    if (base + r > pos)
+                        *reinterpret_cast<uint4*>(ring + s * 2 * PAGE_BYTES + PAGE_BYTES + (rest / 8) * BLK_BYTES + r * 128 + (rest % 8) * 16) = make_uint4(0, 0, 0, 0);
+                }
+                __syncwarp();
+            }
+            float sc[2][4];
+            scores_swz<2>(sc, Qs, k_base, warp * 16, lane);
+            softmax_step<2>(sc, o, m, l, p.c, row_pos, row_ok, base + warp * 16, p.window, lane);
+            weighted_values_swz<2>(o, sc, v_base, warp * 16, lane);
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&empty[s]);
+        }
+    }
+    __syncthreads();                                       // every tile is used: the ring becomes the merge buffer
+    constexpr int RS = HD + 2;
+    if (warp < 4) {
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+            float* dst = red + ((warp * 16) + (lane >> 2) + r * 8) * RS;
+#pragma unroll
+            for (int dt = 0; dt < DTILES; ++dt) {
+                dst[dt * 8 + (lane & 3) * 2] = o[dt][2 * r];
+                dst[dt * 8 + (lane & 3) * 2 + 1] = o[dt][2 * r + 1];
+            }
+            if ((lane & 3) == 0) { dst[HD] = m[r]; dst[HD + 1] = l[r]; }
+        }
+    }
+    __syncthreads();
+    for (int i = tid; i < G * HD; i += TMA_THREADS) {
+        const int g = i / HD, d = i % HD;
+        float mm = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) mm = fmaxf(mm, red[(w * 16 + g) * RS + HD]);
+        float acc = 0.f, ll = 0.f;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+            const float mw = red[(w * 16 + g) * RS + HD];
+            const float f = mw == -INFINITY ? 0.f : exp2f(mw - mm);
+            acc += f * red[(w * 16 + g) * RS + d];
+            ll += f * red[(w * 16 + g) * RS + HD + 1];
+        }
+        const int head = kvh * G + g;
+        if (p.n_slices == 1) {
+            p.out[(long long)row * p.o_stride + (long long)head * HD + d] = __float2bfloat16_rn(acc / ll);
+        } else {
+            const long long pi = ((long long)seq * p.nh + head) * p.n_slices + slice;
+            p.part_o[pi * HD + d] = acc;
+            if (d == 0) { p.part_ml[pi * 2] = mm; p.part_ml[pi * 2 + 1] = ll; }
+        }
+    }
+    if (tid == 0 && *err) atomicExch(tp.error, 1);
+}
+
+// tensor map of one run's K or V cache [pages, kv heads, 64, HD] as rows of HD, boxes of 64 columns x 64 rows
+UB_API int ub_attn_map_kv(void* out_map, const void* cache, long long n_pages, int nkv) {
+    EncodeTiledFn enc = tensor_map_encoder();
+    if (!enc) return UB_ERR_UNSUPPORTED;
+    if (((uintptr_t)cache & 15) || n_pages < 1) return UB_ERR_ARG;
+    cuuint64_t dims[2] = {(cuuint64_t)HD, (cuuint64_t)(n_pages * nkv * KT)};
+    cuuint64_t strides[1] = {(cuuint64_t)HD * 2};
+    cuuint32_t box[2] = {64, (cuuint32_t)KT};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = enc((CUtensorMap*)out_map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (void*)cache, dims, strides, box, estr,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? 0 : UB_ERR_ARG;
+}
+
+UB_API int ub_attn_decode_tma_stages() { return TSTAGES; }
+
+// one new token for every sequence, group <= 16; K and V through their tensor maps
+UB_API int ub_attn_decode_tma(const void* map_k, const void* map_v, const void* q, long long q_stride, void* out,
+                              long long o_stride, const int* seq_start, const int* seq_before, const int* table,
+                              int pages_per_seq, int ring, int page, int n_seqs, int nh, int nkv, int window,
+                              float scale, int n_slices, float* part_o, float* part_ml, int* error, cudaStream_t st) {
+    if (n_seqs <= 0) return 0;
+    if (page != KT || ring % page != 0 || nh % nkv != 0 || (q_stride % 8) != 0 || (o_stride % 2) != 0) return UB_ERR_ARG;
+    if (((uintptr_t)q & 15) || ((uintptr_t)out & 3) || n_seqs > 65535 || nkv > 65535 || nh / nkv > 16) return UB_ERR_ARG;
+    TmaDecodeParams tp;
+    AttnParams& p = tp.a;
+    p.q = (const bf16*)q; p.q_stride = q_stride; p.out = (bf16*)out; p.o_stride = o_stride;
+    p.kc = nullptr; p.vc = nullptr; p.seq_start = seq_start; p.seq_before = seq_before;
+    p.nh = nh; p.group = nh / nkv; p.window = window; p.c = scale * 1.4426950408889634f;
+    p.part_o = part_o; p.part_ml = part_ml; p.n_slices = n_slices < 1 ? 1 : n_slices;
+    tp.table = table; tp.pages_per_seq = pages_per_seq; tp.ring = ring; tp.nkv = nkv; tp.error = error;
+    if (p.n_slices > 1 && (!part_o || !part_ml)) return UB_ERR_ARG;
+    const size_t sm_ring = (size_t)TSTAGES * 2 * PAGE_BYTES, sm_red = (size_t)64 * (HD + 2) * sizeof(float);
+    const size_t sm = (sm_ring > sm_red ? sm_ring : sm_red) + (size_t)16 * LDS * sizeof(bf16) + 2 * TSTAGES * 8 + 16 + 1024;
+    static bool attr_done = false;
+    if (!attr_done) {
+        cudaError_t e = cudaFuncSetAttribute(attn_decode_tma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm);
+        if (e != cudaSuccess) return (int)e;
+        attr_done = true;
+    }
+    cudaError_t e = ub_launch_dependent(attn_decode_tma_kernel, dim3(p.n_slices, n_seqs, nkv), dim3(TMA_THREADS), sm, st,
+                                        *(const CUtensorMap*)map_k, *(const CUtensorMap*)map_v, tp);
+    if (e != cudaSuccess) return (int)e;
+    if (p.n_slices > 1) {
+        e = ub_launch_dependent(attn_combine_kernel, dim3(n_seqs * nh), dim3(((HD + 31) / 32) * 32), 0, st, p);
+        if (e != cudaSuccess) return (int)e;
+    }
+    return 0;
+}
+#endif   // HEAD_DIM % 64 == 0
+
 // ---------------------------------------------------------------------------------------
 // decode attention without any allocation: see attn_noalloc.h
 // ---------------------------------------------------------------------------------------

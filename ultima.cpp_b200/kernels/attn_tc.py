@@ -13,6 +13,7 @@ SOURCE = "attn_mma.cu"
 N_SMS = 148
 import os as _os
 SLICE_FACTOR = int(_os.environ.get("ULTIMA_SLICE_FACTOR", "2"))
+SLICE_CAP = int(_os.environ.get("ULTIMA_SLICE_CAP", "16"))
 _libs: dict = {}
 
 
@@ -32,6 +33,13 @@ def lib(head_dim: int):
         L.ub_attn_head_dim.restype = c_int
         if L.ub_attn_head_dim() != head_dim:
             raise KernelError(f"attention library was built for head size {L.ub_attn_head_dim()}, not {head_dim}")
+        if head_dim % 64 == 0:
+            L.ub_attn_map_kv.argtypes = [c_void_p, c_void_p, c_longlong, c_int]
+            L.ub_attn_map_kv.restype = c_int
+            L.ub_attn_decode_tma.argtypes = [c_void_p, c_void_p, c_void_p, c_longlong, c_void_p, c_longlong, c_void_p,
+                                             c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+                                             c_float, c_int, c_void_p, c_void_p, c_void_p, c_void_p]
+            L.ub_attn_decode_tma.restype = c_int
         _libs[head_dim] = L
     return L
 
@@ -41,6 +49,7 @@ _tc_libs: dict = {}
 _tc_maps: dict = {}
 USE_TCGEN05 = _os.environ.get("ULTIMA_ATTN_TCGEN05", "1") != "0"
 USE_TCGEN05_DECODE = _os.environ.get("ULTIMA_ATTN_TCGEN05_DECODE", "0") != "0"
+USE_TMA_DECODE = _os.environ.get("ULTIMA_ATTN_TMA_DECODE", "1") != "0"
 
 
 def tc_target(head_dim: int):
@@ -118,7 +127,7 @@ def decode_slices(n_seqs: int, n_kv_heads: int, longest: int, window, per_sm: in
     tiles = max(1, -(-span // 64))
     ctas = n_seqs * n_kv_heads
     want = -(-per_sm * N_SMS // ctas)
-    n = max(1, min(want, tiles, 64))
+    n = max(1, min(want, tiles, SLICE_CAP))
     return 1 << (n.bit_length() - 1)            # a power of two: few distinct captured graphs
 
 
@@ -138,11 +147,23 @@ def attention(q, kv, out, batch, n_heads, n_kv_heads, head_dim, scale, rt, slice
         return run_tcgen05(q, kv, out, batch, n_heads, n_kv_heads, head_dim, scale, rt, True, n)
     part_o = part_ml = None
     n_slices = 1
+    tma = (decode and head_dim % 64 == 0 and kernel in (None, "tma") and (USE_TMA_DECODE or kernel == "tma")
+           and kv.k.is_contiguous() and kv.v.is_contiguous())
     if decode:
         n_slices = slices or decode_slices(batch.n_seqs, n_kv_heads, batch.max_after, kv.window)
         if n_slices > 1:
             part_o = rt.arena.alloc((batch.n_seqs, n_heads, n_slices, head_dim), torch.float32)
             part_ml = rt.arena.alloc((batch.n_seqs, n_heads, n_slices, 2), torch.float32)
+    if tma:
+        mk = _tc_map(("kvd", kv.k.data_ptr(), kv.k.shape[0], n_kv_heads, head_dim),
+                     lambda a: L.ub_attn_map_kv(a, kv.k.data_ptr(), kv.k.shape[0], n_kv_heads))
+        mv = _tc_map(("kvd", kv.v.data_ptr(), kv.v.shape[0], n_kv_heads, head_dim),
+                     lambda a: L.ub_attn_map_kv(a, kv.v.data_ptr(), kv.v.shape[0], n_kv_heads))
+        rc = L.ub_attn_decode_tma(mk, mv, _ptr(q), q.stride(0), _ptr(out), out.stride(0), _ptr(batch.seq_start),
+                                  _ptr(batch.seq_before), _ptr(kv.table), kv.table.shape[1], kv.ring, kv.page,
+                                  batch.n_seqs, n_heads, n_kv_heads, int(kv.window or 0), float(scale), n_slices,
+                                  _ptr(part_o), _ptr(part_ml), _ptr(rt.status[1:2]), _stream())
+        return _check(rc, "attn_decode_tma")
     rc = L.ub_attn_mma(1 if decode else 0, _ptr(q), q.stride(0), _ptr(out), out.stride(0), _ptr(kv.k), _ptr(kv.v),
                        _ptr(batch.seq_start), _ptr(batch.seq_before), _ptr(kv.table), kv.table.shape[1], kv.ring,
                        kv.page, batch.n_seqs, batch.max_new, n_heads, n_kv_heads, int(kv.window or 0), float(scale),

@@ -142,7 +142,8 @@ def store_splits(T: int, N: int, K: int) -> int:
     slots = cta_slots(bn, EPI_STORE)
     if T > 64 or tiles * 2 > slots or nkb < 8:
         return 1
-    s = max(1, min(slots // tiles, nkb // 4, max(1, K // (40 * T))))
+    # the float32 partial results (written, then read) stay below a quarter of the weight bytes
+    s = max(1, min(slots // tiles, nkb // 4, max(1, K // (16 * T))))
     per = -(-nkb // s)
     return -(-nkb // per)
 
