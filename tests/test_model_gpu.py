@@ -167,3 +167,24 @@ def test_passes_inside_a_step_change_nothing(model_dirs, plain_models, dtype):
     for t in ids:
         _check(out[o:o + len(t)], _plain_logits(plain_models, name, t), dtype, name, "passes")
         o += len(t)
+
+
+def test_weights_stored_in_32_bit_stay_32_bit_on_the_bfloat16_path(model_dirs, plain_models):
+    """A folder whose tensors are float32, run with dtype bfloat16: the weights are not rounded (their
+    products run on the CUDA-core kernel), activations and cache are bfloat16."""
+    import plain_qwen3 as P
+    import torch
+    from ultima_b200.engine import Engine
+    name = "B"
+    eng = Engine.from_dir(model_dirs(name, "float32"), dtype="bfloat16", max_tokens=1024, poison_cache=True)
+    att = eng.model.layers[0].mixer
+    assert att.wqkv.dtype == torch.float32 and eng.model.head.weight.dtype == torch.float32
+    assert eng.cache.kv_groups[0].k.dtype == torch.bfloat16
+    cfg, w = plain_models(name, "float32")
+    ids = random_ids(77, 50, TINY[name]["vocab_size"])
+    s = eng.open(1)
+    rows = [eng.step(s, [ids[:40]], [list(range(40))]).cpu().numpy()]
+    for t in range(40, 50):
+        rows.append(eng.step(s, [[ids[t]]], [[0]]).cpu().numpy())
+    eng.close(s)
+    _check(np.concatenate(rows), P.forward(cfg, w, ids), "bfloat16", name, "float32 weights on the bfloat16 path")

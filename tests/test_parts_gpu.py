@@ -302,3 +302,141 @@ def test_toy_mixer_with_state_is_registered_built_and_stepped():
         eng.close(slots)
         for i in range(3):
             assert np.abs(np.concatenate(got[i]) - refs[i]).max() < 3e-5, (round_, i)
+
+
+# ---------------------------------------------------------------------------------------
+# toy parts of the other families, defined here: a feed-forward with routing, another position
+# encoding; they never become a model of anyone's
+# ---------------------------------------------------------------------------------------
+def _register_toy_routed_ffn():
+    from ultima_b200.parts import FeedForward, register_part
+    from ultima_b200.weights import WeightSpec
+    from ultima_b200.kernels import ops
+
+    @register_part("feed_forward", "toy_top1_experts", replace=True)
+    class Top1Experts(FeedForward):
+        """A router picks one of ``n_experts`` small gated feed-forwards for every token (router
+        logits in float32); tokens are grouped by expert on the host and each group runs the
+        library's products."""
+
+        def __init__(self, width: int, inner: int, n_experts: int):
+            self.width, self.inner, self.n = width, inner, n_experts
+
+        def weight_specs(self):
+            s = [WeightSpec("router.weight", (self.n, self.width), "matrix", ("normal", 0.5))]
+            for e in range(self.n):
+                s += [WeightSpec(f"experts.{e}.gate.weight", (self.inner, self.width), "matrix", ("normal", 0.2)),
+                      WeightSpec(f"experts.{e}.up.weight", (self.inner, self.width), "matrix", ("normal", 0.2)),
+                      WeightSpec(f"experts.{e}.down.weight", (self.width, self.inner), "matrix", ("normal", 0.2))]
+            return s
+
+        def bind(self, tensors, rt):
+            self.router = tensors["router.weight"].float().contiguous()
+            self.experts = [(tensors[f"experts.{e}.gate.weight"].contiguous(), tensors[f"experts.{e}.up.weight"].contiguous(),
+                             tensors[f"experts.{e}.down.weight"].contiguous()) for e in range(self.n)]
+
+        def forward(self, h, residual, batch, rt):
+            T = h.shape[0]
+            logits = torch.empty(T, self.n, dtype=torch.float32, device=h.device)
+            ops.gemm_simt(h.float().contiguous(), self.router, logits)           # router in 32-bit
+            choice = logits.argmax(-1)
+            for e, (g, u, d) in enumerate(self.experts):
+                rows = (choice == e).nonzero().flatten()
+                if rows.numel() == 0:
+                    continue
+                x = h[rows].contiguous()
+                a = torch.empty(rows.numel(), self.inner, dtype=h.dtype, device=h.device)
+                ops.gemm_simt(x, g, a, ops.EPI_SWIGLU, w2=u)
+                y = torch.zeros(rows.numel(), self.width, dtype=torch.float32, device=h.device)
+                ops.gemm_simt(a, d, y, ops.EPI_ADD)
+                residual.index_add_(0, rows, y)
+    return Top1Experts
+
+
+def _register_toy_position():
+    from ultima_b200.parts import Position, register_part
+
+    @register_part("position", "toy_slow_rotary", replace=True)
+    class SlowRotary(Position):
+        """Half-split rotation with angle pos * scale / (j + 1): another table, the same kernel."""
+
+        def __init__(self, head_dim: int, scale: float, max_positions: int):
+            self.head_dim, self.scale, self.max_positions = head_dim, scale, max_positions
+            self.cos = self.sin = None
+
+        def bind(self, tensors, rt):
+            half = self.head_dim // 2
+            ang = torch.arange(self.max_positions, dtype=torch.float64)[:, None] * self.scale / \
+                (torch.arange(half, dtype=torch.float64)[None] + 1)
+            self.cos, self.sin = torch.cos(ang).float().to(rt.device), torch.sin(ang).float().to(rt.device)
+    return SlowRotary
+
+
+def test_toy_routed_feed_forward_and_another_position_encoding():
+    from ultima_b200.engine import Engine
+    from ultima_b200.parts import LayerSpec, ModelSpec, Run, part
+    from ultima_b200.weights import random_tensors
+    _register_toy_routed_ffn()
+    _register_toy_position()
+    width, vocab, hd, n_exp = 48, 61, 16, 3
+    norm = part("rms", width=width, eps=1e-5)
+    pos = part("toy_slow_rotary", head_dim=hd, scale=0.3, max_positions=128)
+    att = part("attention", width=width, n_heads=3, n_kv_heads=3, head_dim=hd, qk_norm=True, eps=1e-5, position=pos)
+    layers = (LayerSpec(part("pre_norm"), att, part("toy_top1_experts", width=width, inner=40, n_experts=n_exp), norm, norm, prefix="a."),
+              LayerSpec(part("pre_norm"), att, part("gated_silu", width=width, inner=64), norm, norm, prefix="b."))
+    spec = ModelSpec(width=width, vocab_size=vocab, max_positions=128,
+                     embedding=part("token_table", vocab_size=vocab, width=width), embedding_name="emb.",
+                     layers=layers, runs=(Run(0), Run(1)), final_norm=norm, final_norm_name="fn.",
+                     head=part("linear", vocab_size=vocab, width=width, tied=True), head_name="head.")
+    tensors = {k: v.to(DEV) for k, v in random_tensors(spec.weight_specs(), 9).items()}
+    eng = Engine(spec, tensors, dtype="float32", max_tokens=512, max_seqs=2, poison_cache=True)
+    assert not eng.use_graphs                                  # the toy part does host work: no capture
+
+    def plain(ids):
+        t = {k: v.double().cpu() for k, v in tensors.items()}
+        n = len(ids)
+        x = t["emb.weight"][ids]
+        rms = lambda x, w: x * w / torch.sqrt((x * x).mean(-1, keepdim=True) + 1e-5)
+        half = hd // 2
+        ang = torch.arange(n, dtype=torch.float64)[:, None] * 0.3 / (torch.arange(half, dtype=torch.float64)[None] + 1)
+        def rot(v):                                           # v [n, heads, hd]
+            a, b = v[..., :half], v[..., half:]
+            c, s_ = torch.cos(ang)[:, None], torch.sin(ang)[:, None]
+            return torch.cat([a * c - b * s_, a * s_ + b * c], -1)
+        used = set()
+        for p in ("a.", "b."):
+            h = rms(x, t[p + "mixer_norm.weight"])
+            q = rot(rms((h @ t[p + "mixer.q_proj.weight"].T).view(n, 3, hd), t[p + "mixer.q_norm.weight"]))
+            k = rot(rms((h @ t[p + "mixer.k_proj.weight"].T).view(n, 3, hd), t[p + "mixer.k_norm.weight"]))
+            v = (h @ t[p + "mixer.v_proj.weight"].T).view(n, 3, hd)
+            o = torch.zeros(n, 3, hd, dtype=torch.float64)
+            for r in range(n):
+                for hh in range(3):
+                    s_ = (k[:r + 1, hh] @ q[r, hh]) / math.sqrt(hd)
+                    o[r, hh] = torch.softmax(s_, 0) @ v[:r + 1, hh]
+            x = x + o.view(n, 3 * hd) @ t[p + "mixer.o_proj.weight"].T
+            h = rms(x, t[p + "feed_forward_norm.weight"])
+            if p == "a.":
+                choice = (h @ t["a.feed_forward.router.weight"].T).argmax(-1)
+                y = torch.zeros_like(x)
+                for r in range(n):
+                    e = int(choice[r])
+                    used.add(e)
+                    g = h[r] @ t[f"a.feed_forward.experts.{e}.gate.weight"].T
+                    u_ = h[r] @ t[f"a.feed_forward.experts.{e}.up.weight"].T
+                    y[r] = (g / (1 + torch.exp(-g)) * u_) @ t[f"a.feed_forward.experts.{e}.down.weight"].T
+                x = x + y
+            else:
+                g, u_ = h @ t["b.feed_forward.gate_proj.weight"].T, h @ t["b.feed_forward.up_proj.weight"].T
+                x = x + (g / (1 + torch.exp(-g)) * u_) @ t["b.feed_forward.down_proj.weight"].T
+        return (rms(x, t["fn.weight"]) @ t["emb.weight"].T).numpy(), used
+
+    ids = random_ids(4, 40, vocab)
+    ref, used = plain(ids)
+    assert len(used) >= 2                                      # the router does route
+    s = eng.open(1)
+    got = [eng.step(s, [ids[:25]], [list(range(25))]).cpu().numpy()]
+    for t_ in range(25, 40):
+        got.append(eng.step(s, [[ids[t_]]], [[0]]).cpu().numpy())
+    eng.close(s)
+    assert np.abs(np.concatenate(got) - ref).max() < 3e-5
