@@ -570,3 +570,44 @@ def test_gemm_tc_many_tiles_a_cta(case):
         assert rel_err(out, ref[:, :F] / (1 + torch.exp(-ref[:, :F])) * ref[:, F:]) <= 2 ** -8
     torch.cuda.synchronize()
     gemm_tc.check_error(rt)
+
+
+@pytest.mark.parametrize("kernel,new", [("mma", 1), ("mma", 2), ("tma", 1), (None, 2), ("tc", 1)])
+def test_tensor_core_attention_finds_a_far_key_and_respects_the_window_edge(kernel, new):
+    """As for the plain kernel: one key among hundreds stands out; a window that ends one short of it
+    must not see it, a window that just reaches it must.  ``new`` = 1 runs the decode kernels, 2 the
+    prompt kernels (mma.sync, TMA-fed, tcgen05)."""
+    from ultima_b200.kernels import attn_tc
+    from ultima_b200.engine import Runtime
+    rt = Runtime(DEV, torch.bfloat16)
+    nh, nkv, hd, n = 2, 1, 64, 700
+    g = torch.Generator().manual_seed(3)
+    k = torch.randn(n, nkv, hd, generator=g) * 0.1
+    v = torch.randn(n, nkv, hd, generator=g) * 0.1
+    qv = torch.randn(nh * hd, generator=g) * 0.1
+    far = 213
+    k[far, 0] = qv[:hd] * 400.0
+    v[far, 0] = 5.0
+    ring_pages = 11
+    kc = torch.full((ring_pages, nkv, 64, hd), float("nan"), dtype=torch.bfloat16)
+    vc = torch.full((ring_pages, nkv, 64, hd), float("nan"), dtype=torch.bfloat16)
+    for p_ in range(n):
+        kc[p_ // 64, :, p_ % 64], vc[p_ // 64, :, p_ % 64] = k[p_].to(torch.bfloat16), v[p_].to(torch.bfloat16)
+    table = torch.arange(ring_pages, dtype=torch.int32).view(1, -1).to(DEV)
+    q = qv[None].repeat(new, 1).to(torch.bfloat16).to(DEV)
+    b = _B()
+    b.seq_start = torch.tensor([0, new], dtype=torch.int32, device=DEV)
+    b.seq_before = torch.tensor([n - new], dtype=torch.int32, device=DEV)
+    b.n_seqs, b.max_new, b.max_after = 1, new, n
+
+    def run(window):
+        out = torch.full((new, nh * hd), float("nan"), dtype=torch.bfloat16, device=DEV)
+        kv = _KV(kc.to(DEV), vc.to(DEV), table, ring_pages * 64, window or None)
+        attn_tc.attention(q, kv, out, b, nh, nkv, hd, 1 / math.sqrt(hd), rt, kernel=kernel)
+        torch.cuda.synchronize()
+        rt.check_status()
+        return out[new - 1, :hd].float()                       # head 0 of the token at position n - 1
+
+    assert float(run(0).min()) > 4.9
+    assert float(run(n - 1 - far).abs().max()) < 1.0           # the window ends one short of the far key
+    assert float(run(n - far).min()) > 4.9                     # the window just reaches it
