@@ -32,6 +32,14 @@ QWEN3_8B = dict(architectures=["Qwen3ForCausalLM"], model_type="qwen3", vocab_si
                 hidden_act="silu")
 PROMPT, CONTEXT, BATCH, PREFILL_TOKENS = 2048, 8192, 8, 2048
 
+# the other two workloads the baseline names (layer sizes of Qwen3-14B and Qwen3-32B, random weights)
+OTHER = {
+    "14b": dict(sizes=dict(hidden_size=5120, intermediate_size=17408, num_hidden_layers=40, num_attention_heads=40,
+                           num_key_value_heads=8, head_dim=128), batch=16, prompt=("uniform", 128, 4096), decode=256),
+    "32b": dict(sizes=dict(hidden_size=5120, intermediate_size=25600, num_hidden_layers=64, num_attention_heads=64,
+                           num_key_value_heads=8, head_dim=128), batch=8, prompt=("fixed", 4096, 4096), decode=512),
+}
+
 
 def peaks():
     p = os.path.join(ROOT, "MEASURED_PEAKS.json")
@@ -151,6 +159,7 @@ def timed_decode(engine, sampler, batch, steps, warmup, rng, real_prefill):
 
 
 def sampler_params(sampler, params, device):
+    """Records of greedy sampling for ``len(params)`` rows, on the device."""
     import numpy as np
     import torch
     from ultima_b200.kernels import ops
@@ -280,6 +289,83 @@ def run_ours(args):
     return 0
 
 
+def run_other(args):
+    """Qwen3-14B / Qwen3-32B layer sizes: a batch of prompts (run one after another), then decode steps."""
+    import numpy as np
+    import torch
+    import ultima_b200 as u
+    from ultima_b200.engine import Engine
+    from ultima_b200.sampling import Sampler
+    from ultima_b200.weights import random_tensors_on_device
+    w = OTHER[args.config]
+    pk = peaks()
+    d = dict(QWEN3_8B)
+    d.update(w["sizes"])
+    if args.layers:
+        d["num_hidden_layers"] = args.layers
+    cfg = u.config_from_dict(d)
+    dev = torch.device("cuda:0")
+    spec = u.model_spec_for(cfg)
+    rng = np.random.default_rng(0)
+    kind, lo, hi = w["prompt"]
+    B, steps = w["batch"], (args.steps if args.steps_given else w["decode"])
+    lens = [int(x) for x in (rng.integers(lo, hi + 1, size=B) if kind == "uniform" else [hi] * B)]
+    per_seq = [-(-(n + steps + 8) // 64) * 64 for n in lens]
+    engine = Engine(spec, random_tensors_on_device(spec.weight_specs(), 0, torch.bfloat16, dev), dtype="bfloat16",
+                    max_tokens=sum(per_seq), max_seqs=B, max_step_tokens=4096, max_context=CONTEXT)
+    sampler = Sampler(dev, cfg.vocab_size, engine.rt)
+    engine.warm_up()
+    slots = engine.open(B)
+    prompts = [rng.integers(0, cfg.vocab_size, size=n).tolist() for n in lens]
+    engine.step([slots[0]], [prompts[0][:64]], [[]])            # warm the prompt kernels
+    engine.close([slots[0]])
+    slots[0] = engine.open(1)[0]
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    e0.record()
+    for i in range(B):
+        engine.step([slots[i]], [prompts[i]], [[]])
+    e1.record()
+    torch.cuda.synchronize()
+    pre_ms = e0.elapsed_time(e1)
+    toks = rng.integers(0, cfg.vocab_size, size=(args.warmup + steps, B))
+    prm = sampler_params(sampler, [None] * B, dev)
+    out_ids = torch.empty(B, dtype=torch.int32, device=dev)
+    def one(i):
+        sampler_launch(engine.step(slots, [[int(t)] for t in toks[i]], None, borrow=True), prm, out_ids)
+    for i in range(args.warmup):
+        one(i)
+    clocks = ClockSampler()
+    clocks.start()
+    torch.cuda.synchronize()
+    e0.record()
+    for i in range(args.warmup, args.warmup + steps):
+        one(i)
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1)
+    clk = clocks.stop()
+    engine.check_errors()
+    mean_ctx = sum(lens) / B + args.warmup + steps / 2
+    step_bytes = weight_bytes(cfg) + B * mean_ctx * kv_bytes_per_token(cfg, 2)
+    achieved = step_bytes / (ms / steps * 1e-3) / 1e9
+    pf = sum(prefill_flops(cfg, n) for n in lens)
+    print(json.dumps({
+        "metric": f"decode tokens/s, Qwen3-{args.config.upper()} sizes, bf16, batch {B}", "value": round(B * steps / ms * 1e3, 1),
+        "unit": "tokens/s", "n_gpus": 1, "steps": steps, "warmup": args.warmup, "ms_per_step": round(ms / steps, 4),
+        "higher_is_better": True, "dtype": "bf16", "data": "synthetic: random weights from a seed, random token ids",
+        "config": {"model": f"Qwen3-{args.config.upper()} sizes", "layers": cfg.num_hidden_layers, "hidden": cfg.hidden_size,
+                   "heads": cfg.num_attention_heads, "kv_heads": cfg.num_key_value_heads, "head_dim": cfg.head_dim,
+                   "intermediate": cfg.intermediate_size, "vocab": cfg.vocab_size, "global_batch": B,
+                   "prompt_tokens": sum(lens), "prompt_min": min(lens), "prompt_max": max(lens), "peaks": pk["source"]},
+        "prefill": {"value": round(sum(lens) / pre_ms * 1e3, 1), "tokens": sum(lens), "ms": round(pre_ms, 2),
+                    "frac": round(pf / (pre_ms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)},
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
+                     "frac": round(achieved / pk["hbm_gbs"], 4)},
+        "clocks": clk, "impl": "ours"}), flush=True)
+    return 0
+
+
 def run_reference(args):
     why = ("the reference is a CPU-only C++/CMake program with no Python package, no CUDA code and a "
            "Windows-only model loader; the offline pip install of it fails (no setup.py or pyproject.toml)")
@@ -290,7 +376,9 @@ def run_reference(args):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--steps", type=int, default=None)
+    ap.add_argument("--config", default="8b", choices=["8b", "14b", "32b"],
+                    help="8b: the default run; 14b, 32b: the baseline's other two workloads")
     ap.add_argument("--warmup", type=int, default=4)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--layers", type=int, default=0, help="fewer layers than the configuration (named in config)")
@@ -306,6 +394,11 @@ def main():
         return 2
     if args.warmup < 3:
         args.warmup = 3
+    args.steps_given = args.steps is not None
+    if args.steps is None:
+        args.steps = 64
+    if args.config != "8b":
+        return run_other(args)
     return run_ours(args)
 
 

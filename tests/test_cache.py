@@ -137,3 +137,26 @@ def test_random_churn_never_loses_or_doubles_a_page():
             for s, n in live.items():
                 assert len(g.pages_of[s]) == g.pages_needed(n)
         assert sorted(live) == [s for s in range(c.n_slots) if c.slots.in_use[s]]
+
+
+def test_truncate_gives_pages_back_and_refuses_what_cannot_go_back():
+    c = Cache([KVNeed(2, 16)], [None], max_tokens=8 * PAGE, max_context=512, n_slots=2, step_chunk=64,
+              dtype=torch.float32, device="cpu")
+    s = c.acquire()
+    c.reserve(s, 200)
+    c.commit(s, 200)
+    assert c.pages_held() == 4
+    c.truncate(s, 70)
+    assert c.length(s) == 70 and c.pages_held() == 2
+    with pytest.raises(CacheError, match="cannot truncate"):
+        c.truncate(s, 71)
+    c.truncate(s, 0)
+    assert c.pages_held() == 0 and c.kv_groups[0].pool.n_free == 8
+    w = _cache()
+    s = w.acquire()
+    w.reserve(s, 100)
+    w.commit(s, 100)
+    with pytest.raises(CacheError, match="only be truncated to its start"):
+        w.truncate(s, 50)
+    w.truncate(s, 0)
+    assert w.pages_held() == 0

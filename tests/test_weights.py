@@ -125,3 +125,22 @@ def test_reads_files_of_the_safetensors_package(tmp_path):
     q = str(tmp_path / "z.safetensors")
     write_safetensors(q, {"w": a})
     assert torch.equal(st.load_file(q)["w"], a)
+
+
+def test_sharded_folder_is_read_through_its_index(tmp_path):
+    cfg, d = _folder(tmp_path, d=TINY_A, dtype="float32")
+    f = open_safetensors(os.path.join(d, "model.safetensors"))
+    tensors = {n: f.tensor(n).clone() for n in f.names()}
+    f.close()
+    os.remove(os.path.join(d, "model.safetensors"))
+    names = sorted(tensors)
+    parts = {"model-00001-of-00002.safetensors": names[:len(names) // 2],
+             "model-00002-of-00002.safetensors": names[len(names) // 2:]}
+    weight_map = {}
+    for fn, ns in parts.items():
+        write_safetensors(os.path.join(d, fn), {n: tensors[n] for n in ns})
+        weight_map.update({n: fn for n in ns})
+    with open(os.path.join(d, "model.safetensors.index.json"), "w") as fh:
+        json.dump({"metadata": {}, "weight_map": weight_map}, fh)
+    got = load_weights(d, u.model_spec_for(cfg).weight_specs(), torch.float32)
+    assert all(torch.equal(got[n], tensors[n]) for n in names)

@@ -20,7 +20,7 @@ def __getattr__(name):
         return importlib.import_module(f"{__name__}.{name}")
     if name in ("Engine", "StepError"):
         return getattr(importlib.import_module(f"{__name__}.engine"), name)
-    if name in ("LLM", "Generation", "generate"):
+    if name in ("LLM", "Generation", "generate", "load"):
         return getattr(importlib.import_module(f"{__name__}.engine.generate"), name)
     if name in ("SamplingParams", "Sampler"):
         return getattr(importlib.import_module(f"{__name__}.sampling"), name)

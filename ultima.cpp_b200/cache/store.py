@@ -178,6 +178,25 @@ class Cache:
             if more > 0:
                 g.pages_of[slot].extend(g.pool.take(more))
 
+    def truncate(self, slot: int, length: int) -> None:
+        """Forget the positions from ``length`` on (prefix reuse: the reference truncates a slot to
+        the common prefix of its tokens and a new prompt, src/kv_cache/kv_cache.cpp:141-157).  A
+        sequence with windowed or state-carrying runs cannot go back (the reference forbids it for
+        its recurrent models, include/ultima/model/imodel.hpp:193-202), except to its start."""
+        self.slots.check(slot)
+        if not (0 <= length <= self.slots.length[slot]):
+            raise CacheError(f"cannot truncate slot {slot} of length {self.slots.length[slot]} to {length}")
+        if length > 0 and (self.state_groups or any(g.need.window is not None for g in self.kv_groups)):
+            raise CacheError("a sequence with a window or with state can only be truncated to its start")
+        for g in self.kv_groups:
+            keep = g.pages_needed(length)
+            g.pool.give_back(g.pages_of[slot][keep:])
+            del g.pages_of[slot][keep:]
+        if length == 0:
+            for g in self.state_groups:
+                g.data[:, slot].zero_()
+        self.slots.length[slot] = length
+
     def commit(self, slot: int, n_new: int) -> None:
         self.slots.check(slot)
         self.slots.length[slot] += n_new

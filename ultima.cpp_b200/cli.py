@@ -12,6 +12,7 @@ request's tokens: ``--prompt "1,2,3"``; several prompts are separated by ``;`` a
              [--show-tokens] [--dtype bfloat16|float32] [--top-k K] [--top-p P] [--min-p P]
              [--repeat-penalty R] [--repeat-last-n N] [--stop-ids a,b] [--n-threads N]
   ultima replay ...                          same as bin/trace_run
+  ultima bench ...                           same as bench.py (throughput at Qwen3-8B layer sizes)
 """
 from __future__ import annotations
 
@@ -108,6 +109,9 @@ def cmd_run(argv) -> int:
                   f"({opt['n_ctx']})", file=sys.stderr)
             return 1
     llm = LLM(model_dir, dtype=opt["dtype"], n_ctx=opt["n_ctx"], max_batch=max(1, len(prompts)))
+    mem = llm.engine.memory_report()
+    print(f"[weights {mem['weights'] / 2**20:.1f} MiB | cache {mem['cache'] / 2**20:.1f} MiB for {mem['cache_positions']} "
+          f"positions in {mem['slots']} slots | scratch {mem['scratch'] / 2**20:.1f} MiB]", file=sys.stderr)
     sp = SamplingParams(temperature=opt["temp"], top_k=opt["top_k"], top_p=opt["top_p"], min_p=opt["min_p"],
                         rep_penalty=opt["repeat_penalty"], repeat_last_n=opt["repeat_last_n"])
     stop = None if opt["stop_ids"] is None else [int(x) for x in opt["stop_ids"].replace(",", " ").split()]
@@ -144,6 +148,13 @@ def main(argv=None) -> int:
         if cmd == "replay":
             from .engine.trace import main as replay_main
             return replay_main(rest)
+        if cmd == "bench":
+            import os
+            import runpy
+            root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+            sys.argv = ["bench.py"] + rest
+            runpy.run_path(os.path.join(root, "bench.py"), run_name="__main__")
+            return 0
     except (ValueError, RuntimeError, OSError) as e:
         print(f"ultima {cmd}: {e}", file=sys.stderr)
         return 1

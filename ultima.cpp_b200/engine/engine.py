@@ -81,7 +81,8 @@ class Engine:
         self.last_h2d_bytes = 0
         # decode steps (one token a sequence, every logit wanted) are captured as CUDA graphs,
         # one for each (number of sequences, slices of the key range); parts must allow it
-        self.use_graphs = bool(use_graphs) and all(
+        from .model import TRACE as _tracing
+        self.use_graphs = bool(use_graphs) and not _tracing and all(
             getattr(L.mixer, "graph_safe", False) and getattr(L.feed_forward, "graph_safe", False)
             for L in self.model.layers)
         self._graphs: dict = {}
@@ -138,6 +139,25 @@ class Engine:
 
     def length(self, slot: int) -> int:
         return self.cache.length(slot)
+
+    def truncate(self, slot: int, length: int) -> None:
+        """Keep the first ``length`` positions of a slot (to continue from a shared prefix)."""
+        self.cache.truncate(slot, length)
+
+    def memory_report(self) -> dict:
+        """Bytes held on the device: weights, cache, scratch."""
+        seen, weights = set(), 0
+        def add(t):
+            nonlocal weights
+            if isinstance(t, torch.Tensor) and t.is_cuda and t.data_ptr() not in seen:
+                seen.add(t.data_ptr())
+                weights += t.numel() * t.element_size()
+        for part in [self.model.embedding, self.model.final_norm, self.model.head] + \
+                [p for L in self.model.layers for p in (L.mixer, L.feed_forward, L.mixer_norm, L.feed_forward_norm)]:
+            for v in vars(part).values():
+                add(v)
+        return {"weights": weights, "cache": self.cache.nbytes(), "scratch": self.rt.arena._buf.numel(),
+                "cache_positions": self.max_tokens, "slots": self.cache.n_slots}
 
     # ---- the step ----------------------------------------------------------------------
     def step(self, slots, tokens, want=None, borrow: bool = False) -> torch.Tensor:

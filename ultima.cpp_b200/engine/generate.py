@@ -188,3 +188,18 @@ class LLM:
         res = generate(self.engine, self.sampler.sample, [list(map(int, p)) for p in prompts], sampling,
                        n_predict, stop, seed=seed, max_batch=self.max_batch, stats=self.last_stats)
         return res[0] if single else res
+
+    # the step function and the slots of the engine underneath, for callers that drive it themselves
+    def step(self, slots, tokens, want=None):
+        return self.engine.step(slots, tokens, want)
+
+    def acquire(self, n: int = 1) -> list:
+        return self.engine.open(n)
+
+    def release(self, slots) -> None:
+        self.engine.close(slots)
+
+
+def load(model_dir: str, dtype: str = "bfloat16", max_ctx: int = 512, max_batch: int = 64, **kw) -> LLM:
+    """Load a model folder; the same as ``LLM(model_dir, dtype=dtype, n_ctx=max_ctx, max_batch=max_batch)``."""
+    return LLM(model_dir, dtype=dtype, n_ctx=max_ctx, max_batch=max_batch, **kw)

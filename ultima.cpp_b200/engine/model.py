@@ -2,9 +2,20 @@
 one step over the run list."""
 from __future__ import annotations
 
+import os
+import sys
 from dataclasses import dataclass
 
 import torch
+
+# ULTIMA_TRACE=1: a line for every run of a layer with the sum of the residual stream behind it, in
+# the form of the reference's trace ("name-layer = {n} sum = ...", src/model/qwen_block.cpp:29-42),
+# so that two runs (32-bit and bfloat16, or two ways of cutting a prompt) can be compared line by line.
+TRACE = os.environ.get("ULTIMA_TRACE", "") not in ("", "0")
+
+
+def _trace(name: str, index: int, x: torch.Tensor) -> None:
+    print(f"{name}-{index} = {{{x.numel()}}} sum = {x.double().sum().item():.6f}", file=sys.stderr, flush=True)
 
 from ..parts.base import ModelSpec, build_part
 
@@ -64,9 +75,13 @@ class Model:
         rt = self.rt
         rt.arena.reset(0)
         x = self.embedding.forward(batch.tok_ids, rt)
+        if TRACE:
+            _trace("embd", 0, x)
         for i, r in enumerate(self.spec.runs):
             layer = self.layers[r.layer]
             layer.arrangement.run(layer, x, batch, cache.run_cache(i, batch.tables), rt)
+            if TRACE:
+                _trace("l_out", i, x)
         if batch.want_rows.numel() == 0:
             return torch.empty((0, self.spec.vocab_size), dtype=torch.float32, device=rt.device)
         h = self.final_norm.forward(x, rt, rows=batch.want_rows)
