@@ -389,7 +389,9 @@ def test_attn_mma_prefill(cfg):
 
 @pytest.mark.parametrize("cfg", [dict(nh=8, nkv=2, hd=128, window=0), dict(nh=8, nkv=1, hd=64, window=0),
                                  dict(nh=4, nkv=4, hd=128, window=0), dict(nh=4, nkv=2, hd=64, window=50),
-                                 dict(nh=32, nkv=2, hd=128, window=0), dict(nh=2, nkv=1, hd=128, window=130)])
+                                 dict(nh=32, nkv=2, hd=128, window=0), dict(nh=2, nkv=1, hd=128, window=130),
+                                 dict(nh=10, nkv=2, hd=128, window=0), dict(nh=6, nkv=2, hd=64, window=0),
+                                 dict(nh=7, nkv=1, hd=64, window=33)])
 def test_attn_tcgen05_prefill(cfg):
     """The tcgen05 prefill kernel: scores and output in tensor memory."""
     from ultima_b200.kernels import attn_tc

@@ -82,9 +82,10 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
     const int seq = blockIdx.y, kvh = blockIdx.z;
     const int q0 = p.seq_start[seq], q_len = p.seq_start[seq + 1] - q0, before = p.seq_before[seq];
     const int G = p.group;
+    const int TPB = BM / G;                                // tokens a tile: TPB * G of the 128 rows are in use
     const int tile = DECODE ? 0 : gridDim.x - 1 - blockIdx.x;          // long tiles first
-    const int R0 = tile * BM;
-    if (R0 >= q_len * G) return;
+    const int tok_first = tile * TPB;
+    if (tok_first >= q_len) return;
 
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint8_t* q_s = smem;
@@ -104,7 +105,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int last_pos = before + q_len - 1;
-    const int tok_first = R0 / G, tok_last = min(q_len - 1, (R0 + BM - 1) / G);
+    const int tok_last = min(q_len - 1, tok_first + TPB - 1);
     const int pos_hi = before + tok_last;
     int pos_lo = 0;
     if (p.window > 0) pos_lo = max(0, before + tok_first - p.window + 1);
@@ -137,7 +138,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
         // ---------------- TMA ----------------
         if (lane == 0) {
             if (n_tiles > 0) {
-                mbar_expect_tx(q_full, Q_BYTES);
+                mbar_expect_tx(q_full, NB * TPB * G * 128);
                 for (int nb = 0; nb < NB; ++nb)
                     tma_load_3d(q_s + nb * BM * 128, &map_q, q_full, nb * 64, kvh * G, q0 + tok_first);
             }
@@ -221,8 +222,8 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
         // ---------------- softmax: one thread a row ----------------
         const int q = warp & 3;
         const int r = q * 32 + lane;                       // row of the tile = lane of tensor memory
-        const int R = R0 + r, tok = R / G, g = R % G;
-        const bool row_ok = tok < q_len;
+        const int tok = tok_first + r / G, g = r % G;
+        const bool row_ok = r < TPB * G && tok < q_len;
         const int row_pos = before + tok;
         const uint32_t lane_addr = tmem_base + ((uint32_t)(q * 32) << 16);
         const int st = (warp - 2) * 32 + lane;             // 0..127 among the softmax threads
@@ -349,11 +350,11 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
 // ---------------------------------------------------------------------------------------
 UB_API int ub_attn_tc_head_dim() { return HD; }
 
-// tensor map of q as [tokens, heads, HD] (row stride q_stride elements), boxes of 64 x group x 128/group
+// tensor map of q as [tokens, heads, HD] (row stride q_stride elements), boxes of 64 x group x floor(128/group)
 UB_API int ub_attn_tc_map_q(void* out_map, const void* q, long long n_tokens, int nh, long long q_stride, int group) {
     EncodeTiledFn enc = tensor_map_encoder();
     if (!enc) return UB_ERR_UNSUPPORTED;
-    if (((uintptr_t)q & 15) || (q_stride * 2) % 16 != 0 || group < 1 || BM % group != 0 || n_tokens < 1) return UB_ERR_ARG;
+    if (((uintptr_t)q & 15) || (q_stride * 2) % 16 != 0 || group < 1 || group > BM || n_tokens < 1) return UB_ERR_ARG;
     cuuint64_t dims[3] = {(cuuint64_t)HD, (cuuint64_t)nh, (cuuint64_t)n_tokens};
     cuuint64_t strides[2] = {(cuuint64_t)HD * 2, (cuuint64_t)q_stride * 2};
     cuuint32_t box[3] = {64, (cuuint32_t)group, (cuuint32_t)(BM / group)};
@@ -419,7 +420,7 @@ UB_API int ub_attn_tc(int mode, const void* map_q, const void* map_k, const void
                       int n_slices, float* part_o, float* part_ml, int* error, cudaStream_t st) {
     if (n_seqs <= 0 || max_new <= 0) return 0;
     const int group = nh / nkv;
-    if (page != BN || ring % page != 0 || nh % nkv != 0 || BM % group != 0 || (o_stride % 8) != 0 || ((uintptr_t)out & 15))
+    if (page != BN || ring % page != 0 || nh % nkv != 0 || group > BM || (o_stride % 8) != 0 || ((uintptr_t)out & 15))
         return UB_ERR_ARG;
     if (n_seqs > 65535 || nkv > 65535) return UB_ERR_ARG;
     TcAttnParams p;
@@ -429,7 +430,8 @@ UB_API int ub_attn_tc(int mode, const void* map_q, const void* map_k, const void
     p.part_o = part_o; p.part_ml = part_ml; p.n_slices = n_slices < 1 ? 1 : n_slices; p.nh = nh;
     if (mode == 0) {
         p.n_slices = 1;
-        return launch_attn<2, false>(dim3((max_new * group + BM - 1) / BM, n_seqs, nkv), map_q, map_k, map_v, p, st);
+        const int tpb = BM / group;
+        return launch_attn<2, false>(dim3((max_new + tpb - 1) / tpb, n_seqs, nkv), map_q, map_k, map_v, p, st);
     }
     if (max_new != 1) return UB_ERR_ARG;
     if (p.n_slices > 1 && (!part_o || !part_ml || ((uintptr_t)part_o & 15))) return UB_ERR_ARG;

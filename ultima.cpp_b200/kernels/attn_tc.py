@@ -73,8 +73,8 @@ def tc_lib(head_dim: int):
 
 
 def tcgen05_fits(head_dim: int, n_heads: int, n_kv_heads: int) -> bool:
-    """The tcgen05 prefill kernel: head sizes 64 and 128, groups that divide its 128 rows."""
-    return USE_TCGEN05 and head_dim in (64, 128) and 128 % (n_heads // n_kv_heads) == 0
+    """The tcgen05 kernel: head sizes 64 and 128, groups of up to 128 query heads a KV head."""
+    return USE_TCGEN05 and head_dim in (64, 128) and n_heads // n_kv_heads <= 128
 
 
 def _tc_map(key, make):
