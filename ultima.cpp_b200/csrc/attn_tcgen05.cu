@@ -58,6 +58,12 @@ __host__ __device__ constexpr uint32_t idesc_bf16(int m, int n, int b_mn_major) 
     return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)b_mn_major << 16) | ((uint32_t)(n >> 3) << 17) |
            ((uint32_t)(m >> 4) << 24);
 }
+// 2^x by the special-function unit (relative error 2^-22; -inf gives 0)
+__device__ __forceinline__ float ex2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
 // V tile as the N-major B operand: rows of 128 bytes are keys, 8 keys a swizzle atom (1024 bytes)
 __device__ __forceinline__ uint64_t make_desc_mn(uint32_t smem_addr) {
     uint64_t d = 0;
@@ -251,15 +257,24 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
             tmem_ld32(lane_addr + (uint32_t)(b * BN), raw);
             tmem_ld32(lane_addr + (uint32_t)(b * BN + 32), raw + 32);
             tmem_ld_wait();
+            // scores stay raw (q.k); the scale goes into the exponent: p = 2^(s c - m).  A tile that
+            // every row of the CTA sees whole needs no mask.
             float mx = -INFINITY;
+            const bool whole = row_ok && base + BN - 1 <= before + tok_first && p.window <= 0 && r < TPB * G;
+            if (__all_sync(0xffffffffu, whole)) {
 #pragma unroll
-            for (int cI = 0; cI < BN; ++cI) {
-                const int kp = base + cI;
-                const bool vis = row_ok && kp <= row_pos && (p.window <= 0 || kp > row_pos - p.window);
-                const float v = vis ? __uint_as_float(raw[cI]) * p.c : -INFINITY;
-                raw[cI] = __float_as_uint(v);
-                mx = fmaxf(mx, v);
+                for (int cI = 0; cI < BN; ++cI) mx = fmaxf(mx, __uint_as_float(raw[cI]));
+            } else {
+#pragma unroll
+                for (int cI = 0; cI < BN; ++cI) {
+                    const int kp = base + cI;
+                    const bool vis = row_ok && kp <= row_pos && (p.window <= 0 || kp > row_pos - p.window);
+                    const float v = vis ? __uint_as_float(raw[cI]) : -INFINITY;
+                    raw[cI] = __float_as_uint(v);
+                    mx = fmaxf(mx, v);
+                }
             }
+            mx *= p.c;                                       // c > 0: the maximum in exponent units
             // raise the reference maximum only when it lags by more than RESCALE_STEP (or is not set)
             const bool grow = mx > m_ref + RESCALE_STEP || (m_ref == -INFINITY && mx > -INFINITY);
             if (__any_sync(0xffffffffu, grow)) {
@@ -288,7 +303,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
             float sum = 0.f;
 #pragma unroll
             for (int cI = 0; cI < BN; cI += 2) {
-                const float p0 = exp2f(__uint_as_float(raw[cI]) - mb), p1 = exp2f(__uint_as_float(raw[cI + 1]) - mb);
+                const float p0 = ex2(fmaf(__uint_as_float(raw[cI]), p.c, -mb)), p1 = ex2(fmaf(__uint_as_float(raw[cI + 1]), p.c, -mb));
                 sum += p0 + p1;
                 __nv_bfloat162 pr = __floats2bfloat162_rn(p0, p1);
                 packed[cI / 2] = *reinterpret_cast<uint32_t*>(&pr);
