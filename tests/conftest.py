@@ -33,7 +33,17 @@ TINY_C = dict(architectures=["Qwen3ForCausalLM"], model_type="qwen3", vocab_size
               head_dim=48, rms_norm_eps=3e-6, rope_theta=500000.0, max_position_embeddings=512,
               tie_word_embeddings=False, hidden_act="silu", use_sliding_window=True, sliding_window=20,
               layer_types=["sliding_attention", "full_attention", "sliding_attention", "full_attention"])
-TINY = {"A": TINY_A, "B": TINY_B, "C": TINY_C}
+# two more with the head sizes the TMA-fed and tcgen05 attention kernels are built for (64, 128)
+TINY_D = dict(architectures=["Qwen3ForCausalLM"], model_type="qwen3", vocab_size=300, hidden_size=128,
+              intermediate_size=256, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2,
+              head_dim=64, rms_norm_eps=1e-6, rope_theta=10000.0, max_position_embeddings=512,
+              tie_word_embeddings=True, hidden_act="silu", use_sliding_window=True, sliding_window=40,
+              layer_types=["full_attention", "sliding_attention"])
+TINY_E = dict(architectures=["Qwen3ForCausalLM"], model_type="qwen3", vocab_size=401, hidden_size=192,
+              intermediate_size=448, num_hidden_layers=2, num_attention_heads=3, num_key_value_heads=1,
+              head_dim=128, rms_norm_eps=1e-5, rope_theta=1000000.0, max_position_embeddings=512,
+              tie_word_embeddings=False, hidden_act="silu")
+TINY = {"A": TINY_A, "B": TINY_B, "C": TINY_C, "D": TINY_D, "E": TINY_E}
 
 
 def make_model_dir(tmp, name: str, dtype: str, seed: int = 7) -> str:

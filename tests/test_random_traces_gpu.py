@@ -1,0 +1,76 @@
+"""Random traces: batches of random sizes, prompts and decode lengths, random wanted places, one
+batch after another in a small cache, through the engine in both element types, every wanted logit
+against the plain implementation.  Seeds are fixed; a failure names the request and the place."""
+import numpy as np
+import pytest
+
+from conftest import TINY, close_enough
+
+pytestmark = pytest.mark.gpu
+
+
+def _trace(rng, vocab, max_len):
+    """A list of batches; a batch is a list of (token ids, prompt length)."""
+    batches = []
+    for _ in range(int(rng.integers(3, 6))):
+        reqs = []
+        for _ in range(int(rng.integers(1, 6))):
+            prompt = int(rng.choice([1, 2, 5, 31, 63, 64, 65, 100, 129]))
+            decode = int(rng.choice([0, 1, 3, 10, 33]))
+            n = min(max_len, prompt + decode)
+            prompt = min(prompt, n)
+            reqs.append((rng.integers(0, vocab, size=n).tolist(), prompt))
+        batches.append(reqs)
+    return batches
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name,seed", [("A", 0), ("B", 1), ("C", 2), ("C", 3), ("D", 4), ("D", 5), ("E", 6), ("E", 7)])
+def test_random_traces(model_dirs, plain_models, name, seed, dtype):
+    import plain_qwen3 as P
+    from ultima_b200.engine import Engine
+    cfg, w = plain_models(name, "bfloat16")
+    V, max_len = cfg["vocab_size"], min(cfg["max_position_embeddings"], 170)
+    rng = np.random.default_rng(seed)
+    eng = Engine.from_dir(model_dirs(name, "bfloat16"), dtype=dtype, max_tokens=5 * 192, max_seqs=5,
+                          max_step_tokens=int(rng.choice([48, 4096])), poison_cache=True)
+    refs = {}
+    for b, reqs in enumerate(_trace(rng, V, max_len)):
+        slots = eng.open(len(reqs))
+        # prompts together, with a random subset of places wanted (always the last one)
+        want = []
+        for ids, p in reqs:
+            k = int(rng.integers(0, min(p, 4)))
+            want.append(sorted(set(rng.integers(0, p, size=k).tolist()) | {p - 1}))
+        out = eng.step(slots, [ids[:p] for ids, p in reqs], want).cpu().numpy()
+        got = {i: {} for i in range(len(reqs))}
+        o = 0
+        for i, wl in enumerate(want):
+            for pl in wl:
+                got[i][pl] = out[o]
+                o += 1
+        live = list(range(len(reqs)))
+        t = 0
+        while True:
+            for i in [i for i in live if reqs[i][1] + t >= len(reqs[i][0])]:
+                eng.close([slots[i]])                     # shorter requests end earlier
+                live.remove(i)
+            if not live:
+                break
+            out = eng.step([slots[i] for i in live], [[reqs[i][0][reqs[i][1] + t]] for i in live]).cpu().numpy()
+            for j, i in enumerate(live):
+                got[i][reqs[i][1] + t] = out[j]
+            t += 1
+        assert eng.cache.pages_held() == 0
+        for i, (ids, p) in enumerate(reqs):
+            key = tuple(ids)
+            if key not in refs:
+                refs[key] = P.forward(cfg, w, ids)
+            places = sorted(got[i])
+            g = np.stack([got[i][pl] for pl in places])
+            err, bound = close_enough(g, refs[key][places], dtype, cfg["num_hidden_layers"])
+            if err > bound:
+                bad = places[int(np.argmax(np.abs(g - refs[key][places]).max(axis=1)))]
+                pytest.fail(f"[{name} {dtype} seed {seed}] batch {b} request {i} (prompt {p}, {len(ids)} tokens): "
+                            f"error {err:.3e} > {bound:.3e}, worst at place {bad}")
+    eng.check_errors()
