@@ -534,7 +534,7 @@ def test_gemm_tc_interleaved_gate_product(shape):
     assert rel_err(out, gt / (1 + torch.exp(-gt)) * up) <= 2 ** -8, shape
 
 
-@pytest.mark.parametrize("case", [("store", 2500, 1024, 1200), ("add", 1300, 512, 2100), ("gate_il", 1700, 256, 1280),
+@pytest.mark.parametrize("case", [("store", 2500, 1024, 1200), ("add", 2500, 512, 2100), ("add", 5000, 128, 1100), ("gate_il", 1700, 256, 1280),
                                   ("gate_two", 1100, 320, 1300), ("store_f32", 700, 128, 5000)])
 def test_gemm_tc_many_tiles_a_cta(case):
     """More tiles than SMs: CTAs stay and walk over tiles with two accumulators in turn."""

@@ -44,6 +44,7 @@ struct GemmParams {
     int T, N, K;
     int kb_per_split;     // 64-column blocks of K a slice
     int atomic;           // EPI_ADD: add with atomics (K is split)
+    int share_tail;       // persistent EPI_ADD: the tiles of the last, part-empty round are shared out by k blocks
     int* error;           // raised on a timeout
 };
 
@@ -247,6 +248,37 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
 // The ring of stages never drains between tiles, and there are two accumulators in tensor
 // memory, so the epilogue of one tile runs while the MMAs of the next are issued.
 // ---------------------------------------------------------------------------------------
+// The pieces of work of one CTA of the persistent kernel, the same sequence for each of its roles:
+// whole tiles in turn (tile c, c + G, ...) for the full rounds; the tiles of the last round, which
+// would leave some CTAs idle, are (for the adding epilogue) shared out in equal runs of
+// (tile, k block) units, so a CTA may take the end of one tile and the beginning of the next, and
+// the pieces of a tile meet in the float32 matrix they are added into.
+struct Pieces {
+    int nkb, tile, tile_end, step;
+    long long u, u_end;
+    __device__ Pieces(int n_tiles, int nkb_, int share_tail) : nkb(nkb_) {
+        step = gridDim.x;
+        tile = blockIdx.x;
+        tile_end = share_tail ? (n_tiles / step) * step : n_tiles;       // tiles of the full rounds
+        const long long units = (long long)(n_tiles - tile_end) * nkb;
+        u = (long long)tile_end * nkb + units * blockIdx.x / gridDim.x;
+        u_end = (long long)tile_end * nkb + units * (blockIdx.x + 1) / gridDim.x;
+    }
+    __device__ bool next(int& t, int& kb0, int& kb1) {
+        if (tile < tile_end) {
+            t = tile; kb0 = 0; kb1 = nkb;
+            tile += step;
+            return true;
+        }
+        if (u >= u_end) return false;
+        t = (int)(u / nkb);
+        kb0 = (int)(u % nkb);
+        kb1 = (int)min((long long)nkb, kb0 + (u_end - u));
+        u += kb1 - kb0;
+        return true;
+    }
+};
+
 template <int BN, int EPI>
 struct SmemP {
     static constexpr int A_BYTES = BM * BK * 2;
@@ -280,9 +312,8 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const __gri
     const int tiles_w = (p.N + BM - 1) / BM, tiles_t = (p.T + BN - 1) / BN;
     const int n_tiles = tiles_w * tiles_t;
     const int nkb = (p.K + BK - 1) / BK;
-    // tile i of this CTA is number blockIdx.x + i * gridDim.x; token tiles vary fastest, so the CTAs
-    // that run together share weight tiles through the L2
-    const int my_tiles = (n_tiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;
+    // token tiles vary fastest in the numbering of tiles, so the CTAs that run together share weight
+    // tiles through the L2
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < S::STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
@@ -306,10 +337,11 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const __gri
             pdl_wait();
             long long it = 0;                            // stages filled so far, over all tiles
             bool ok = true;
-            for (int i = 0; i < my_tiles && ok; ++i) {
-                const int tile = blockIdx.x + i * gridDim.x;
+            Pieces pieces(n_tiles, nkb, p.share_tail);
+            int tile, kb0, kb1;
+            while (ok && pieces.next(tile, kb0, kb1)) {
                 const int n0 = (tile / tiles_t) * BM, t0 = (tile % tiles_t) * BN;
-                for (int kb = 0; kb < nkb; ++kb, ++it) {
+                for (int kb = kb0; kb < kb1; ++kb, ++it) {
                     const int s = (int)(it % S::STAGES);
                     const uint32_t ph = (uint32_t)((it / S::STAGES) & 1);
                     ok = mbar_wait(&empty[s], ph ^ 1, err);
@@ -334,13 +366,15 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const __gri
             constexpr uint32_t idesc = make_idesc(BN);
             long long it = 0;
             bool ok = true;
-            for (int i = 0; i < my_tiles && ok; ++i) {
+            Pieces pieces(n_tiles, nkb, p.share_tail);
+            int tile, kb0, kb1;
+            for (int i = 0; ok && pieces.next(tile, kb0, kb1); ++i) {
                 const int buf = i & 1;
                 ok = mbar_wait(&acc_empty[buf], (uint32_t)(((i >> 1) & 1) ^ 1), err);   // the epilogue has read it
                 if (!ok) break;
                 tc_fence_after();
                 const uint32_t acc = tmem_base + buf * S::ACC_COLS;
-                for (int kb = 0; kb < nkb; ++kb, ++it) {
+                for (int kb = kb0; kb < kb1; ++kb, ++it) {
                     const int s = (int)(it % S::STAGES);
                     const uint32_t ph = (uint32_t)((it / S::STAGES) & 1);
                     ok = mbar_wait(&full[s], ph, err);
@@ -353,7 +387,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const __gri
 #pragma unroll
                     for (int k = 0; k < BK / UMMA_K; ++k) {
                         const uint64_t koff = (uint64_t)((k * UMMA_K * 2) >> 4);
-                        const uint32_t accum = (kb > 0 || k > 0) ? 1u : 0u;
+                        const uint32_t accum = (kb > kb0 || k > 0) ? 1u : 0u;
                         tc_mma_bf16(acc, da + koff, db + koff, idesc, accum);
                         if (EPI == EPI_SWIGLU) tc_mma_bf16(acc + BN, da2 + koff, db + koff, idesc, accum);
                     }
@@ -366,9 +400,10 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const __gri
         const int q = warp & 3;
         pdl_wait();
         bool ok = true;
-        for (int i = 0; i < my_tiles && ok; ++i) {
+        Pieces pieces(n_tiles, nkb, p.share_tail);
+        int tile, kb0, kb1;
+        for (int i = 0; ok && pieces.next(tile, kb0, kb1); ++i) {
             const int buf = i & 1;
-            const int tile = blockIdx.x + i * gridDim.x;
             ok = mbar_wait(&acc_full[buf], (uint32_t)((i >> 1) & 1), err);
             if (!ok) break;
             tc_fence_after();
@@ -443,6 +478,8 @@ static int launch_cfg(Kern kern, dim3 grid, int smem, const CUtensorMap* mw, con
 }
 
 static int g_use_persistent = 1;
+static int g_share_tail = 1;
+UB_API void ub_gemm_tc_set_share_tail(int on) { g_share_tail = on ? 1 : 0; }
 UB_API void ub_gemm_tc_set_persistent(int on) { g_use_persistent = on ? 1 : 0; }
 
 template <int BN, int EPI, typename TO>
@@ -453,6 +490,8 @@ static int launch_one(const CUtensorMap* mw, const CUtensorMap* mw2, const CUten
         // many tiles, K whole: CTAs that stay and overlap one tile's epilogue with the next tile's MMAs
         if (g_use_persistent && splits == 1 && tiles > sm_count()) {
             using SP = SmemP<BN, EPI>;
+            GemmParams pp = p;
+            pp.share_tail = (EPI == EPI_ADD && g_share_tail && tiles % sm_count() != 0) ? 1 : 0;
             static bool attr_p = false;
             auto kp = gemm_tc_persistent_kernel<BN, EPI, TO>;
             if (!attr_p) {
@@ -460,7 +499,7 @@ static int launch_one(const CUtensorMap* mw, const CUtensorMap* mw2, const CUten
                 if (e != cudaSuccess) return (int)e;
                 attr_p = true;
             }
-            return launch_cfg(kp, dim3(sm_count()), SP::TOTAL, mw, mw2, ma, p, st);
+            return launch_cfg(kp, dim3(sm_count()), SP::TOTAL, mw, mw2, ma, pp, st);
         }
     }
     using S = Smem<BN, EPI>;
@@ -507,6 +546,7 @@ UB_API int ub_gemm_tc(const void* map_w, const void* map_w2, const void* map_a, 
     p.T = T; p.N = N; p.K = K;
     p.kb_per_split = (nkb + splits - 1) / splits;
     p.atomic = (epi == EPI_ADD && splits > 1) ? 1 : 0;
+    p.share_tail = 0;
     p.error = error;
     if ((long long)(splits - 1) * p.kb_per_split >= nkb) return UB_ERR_ARG;      // an empty slice
     const CUtensorMap* mw = (const CUtensorMap*)map_w;

@@ -35,6 +35,10 @@ def lib():
         L.ub_gemm_tc_set_persistent.restype = None
         if os.environ.get("ULTIMA_PERSISTENT", "1") == "0":   # for measurements: one tile a CTA
             L.ub_gemm_tc_set_persistent(0)
+        L.ub_gemm_tc_set_share_tail.argtypes = [c_int]
+        L.ub_gemm_tc_set_share_tail.restype = None
+        if os.environ.get("ULTIMA_SHARE_TAIL", "1") == "0":   # for measurements: whole tiles only
+            L.ub_gemm_tc_set_share_tail(0)
         _lib = L
     return _lib
 
