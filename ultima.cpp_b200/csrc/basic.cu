@@ -206,56 +206,60 @@ __global__ void qk_prepare_vec_kernel(const TA* qkv, int n_parts, long long part
                                       int write_kv) {
     pdl_trigger();
     pdl_wait();
-    const int lane = threadIdx.x & 31;
-    const long long wid = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    // blockIdx.x is the token; the warps of its blocks take the token's heads in turn, so what belongs
+    // to the token (its position, the cosines and sines of that position, the norm weights) is fetched
+    // once a warp
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, n_warps = blockDim.x >> 5;
     const int heads_all = nh + 2 * c.n_kv_heads;
-    if (wid >= (long long)n_tokens * heads_all) return;
-    const int t = (int)(wid / heads_all), h = (int)(wid % heads_all);
+    const int t = blockIdx.x;
     constexpr int hd = 32 * E, half = hd / 2;
-    const TA* row = qkv + ((long long)t * heads_all + h) * hd + lane * E;
     const int pos = tok_pos[t];
     const int seq = tok_seq[t];
-    const bool is_v = h >= nh + c.n_kv_heads, is_k = !is_v && h >= nh;
-    if ((is_v || is_k) && !write_kv) return;
-    float v[E];
-    load_vec<TA, E>(row, v);
-    for (int p = 1; p < n_parts; ++p) {
-        float more[E];
-        load_vec<TA, E>(row + p * part_stride, more);
-#pragma unroll
-        for (int i = 0; i < E; ++i) v[i] += more[i];
-    }
-    if (is_v) {
-        store_vec<TC, E>(vcache + paged_offset(c, seq, pos, h - nh - c.n_kv_heads) + lane * E, v);
-        return;
-    }
-    const float* w = is_k ? kw : qw;
-    if (w) {
-        float ss = 0.f;
-#pragma unroll
-        for (int i = 0; i < E; ++i) ss += v[i] * v[i];
-        ss = warp_sum(ss);
-        const float inv = 1.0f / sqrtf(ss / (float)hd + eps);
-        float g[E];
-        load_vec<float, E>(w + lane * E, g);
-#pragma unroll
-        for (int i = 0; i < E; ++i) v[i] = v[i] * g[i] * inv;
-    }
+    float co[E], si[E], gq[E], gk[E];
     if (cs) {
         const int j0 = (lane & 15) * E;                          // index of the pair within the half
-        float co[E], si[E];
         load_vec<float, E>(cs + (long long)pos * half + j0, co);
         load_vec<float, E>(sn + (long long)pos * half + j0, si);
-        const bool upper = lane >= 16;
-#pragma unroll
-        for (int i = 0; i < E; ++i) {
-            const float other = __shfl_xor_sync(0xffffffffu, v[i], 16);
-            // lower lanes hold a (partner b): a c - b s; upper lanes hold b (partner a): a s + b c
-            v[i] = upper ? other * si[i] + v[i] * co[i] : v[i] * co[i] - other * si[i];
-        }
     }
-    if (is_k) store_vec<TC, E>(kcache + paged_offset(c, seq, pos, h - nh) + lane * E, v);
-    else store_vec<TQ, E>(q_out + (long long)t * q_out_stride + (long long)h * hd + lane * E, v);
+    if (qw) load_vec<float, E>(qw + lane * E, gq);
+    if (kw) load_vec<float, E>(kw + lane * E, gk);
+    const bool upper = lane >= 16;
+    for (int h = blockIdx.y * n_warps + warp; h < heads_all; h += n_warps * gridDim.y) {
+        const bool is_v = h >= nh + c.n_kv_heads, is_k = !is_v && h >= nh;
+        if ((is_v || is_k) && !write_kv) continue;
+        const TA* row = qkv + ((long long)t * heads_all + h) * hd + lane * E;
+        float v[E];
+        load_vec<TA, E>(row, v);
+        for (int p = 1; p < n_parts; ++p) {
+            float more[E];
+            load_vec<TA, E>(row + p * part_stride, more);
+#pragma unroll
+            for (int i = 0; i < E; ++i) v[i] += more[i];
+        }
+        if (is_v) {
+            store_vec<TC, E>(vcache + paged_offset(c, seq, pos, h - nh - c.n_kv_heads) + lane * E, v);
+            continue;
+        }
+        if (is_k ? kw != nullptr : qw != nullptr) {
+            float ss = 0.f;
+#pragma unroll
+            for (int i = 0; i < E; ++i) ss += v[i] * v[i];
+            ss = warp_sum(ss);
+            const float inv = 1.0f / sqrtf(ss / (float)hd + eps);
+#pragma unroll
+            for (int i = 0; i < E; ++i) v[i] = v[i] * (is_k ? gk[i] : gq[i]) * inv;
+        }
+        if (cs) {
+#pragma unroll
+            for (int i = 0; i < E; ++i) {
+                const float other = __shfl_xor_sync(0xffffffffu, v[i], 16);
+                // lower lanes hold a (partner b): a c - b s; upper lanes hold b (partner a): a s + b c
+                v[i] = upper ? other * si[i] + v[i] * co[i] : v[i] * co[i] - other * si[i];
+            }
+        }
+        if (is_k) store_vec<TC, E>(kcache + paged_offset(c, seq, pos, h - nh) + lane * E, v);
+        else store_vec<TQ, E>(q_out + (long long)t * q_out_stride + (long long)h * hd + lane * E, v);
+    }
 }
 
 UB_API int ub_qk_prepare(const void* qkv, int in_dtype, int n_parts, long long part_stride, void* q_out,
@@ -275,7 +279,11 @@ UB_API int ub_qk_prepare(const void* qkv, int in_dtype, int n_parts, long long p
                            (uintptr_t)kw | (uintptr_t)cs | (uintptr_t)sn) & 15) == 0 &&
                          part_stride % 8 == 0 && q_out_stride % 8 == 0;
     const bool vec = aligned && (hd == 64 || hd == 128 || hd == 256);
-#define LAUNCH_V(TA, TQ, TC, E) e = ub_launch_dependent(qk_prepare_vec_kernel<TA, TQ, TC, E>, dim3(grid), dim3(wpb * 32), 0, st, \
+    // the vector kernel: blocks of 8 warps; with many tokens one block a token (its warps loop over
+    // the heads), with few tokens a warp a head
+    const int heads_all = nh + 2 * nkv;
+    const dim3 vgrid(n_tokens, n_tokens >= 256 ? 1 : (heads_all + 7) / 8);
+#define LAUNCH_V(TA, TQ, TC, E) e = ub_launch_dependent(qk_prepare_vec_kernel<TA, TQ, TC, E>, vgrid, dim3(256), 0, st, \
         (const TA*)qkv, n_parts, part_stride, (TQ*)q_out, q_out_stride, qw, kw, cs, sn, tok_pos, tok_seq, \
         (TC*)kcache, (TC*)vcache, c, n_tokens, nh, eps, write_kv)
 #define LAUNCH(TA, TQ, TC) do { \
