@@ -262,7 +262,8 @@ def run_ours(args):
     stats = LoopStats()
     generate(engine, sampler.sample, prompts, SamplingParams(), n_new, (), max_batch=BATCH, stats=stats)
     e2e_val = BATCH * (n_new - 1) / stats.decode_s
-    h2d = engine.last_h2d_bytes + BATCH * 64      # the step's batch record and the sampler's records
+    h2d = engine.last_h2d_bytes                   # the step's record (ids, positions, page tables); the
+    # sampler's records stay on the device while a batch samples with the same parameters
     e2e = {"value": round(e2e_val, 1), "unit": "tokens/s", "h2d_bytes_per_step": int(h2d),
            "d2h_bytes_per_step": 4 * (BATCH + 4)}          # the sampled ids and the kernels' status flags
 

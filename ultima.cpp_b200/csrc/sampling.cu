@@ -48,7 +48,7 @@ __global__ void __launch_bounds__(ST)
 sample_kernel(const float* __restrict__ logits, long long ld, float* __restrict__ work, int V,
               const SampleParams* __restrict__ params, const int* __restrict__ recent_all,
               const int* __restrict__ bias_ids, const float* __restrict__ bias_vals,
-              int* __restrict__ out_ids) {
+              int* __restrict__ out_ids, unsigned long long counter_add) {
     __shared__ float red[33];
     __shared__ float seg[ST];
     __shared__ int best_idx_s[32];
@@ -196,7 +196,7 @@ sample_kernel(const float* __restrict__ logits, long long ld, float* __restrict_
         float run = 0.f;
         for (int i = 0; i < ST; ++i) { const float s = seg[i]; seg[i] = run; run += s; }
         red[0] = run;
-        const unsigned long long r = mix64s(p.seed ^ mix64s(p.counter + 0x632BE59BD9B4E019ull));
+        const unsigned long long r = mix64s(p.seed ^ mix64s(p.counter + counter_add + 0x632BE59BD9B4E019ull));
         red[1] = (float)(unsigned)(r >> 40) * (1.0f / 16777216.0f);
         best_idx_s[1] = imax;                     // fallback: the maximum
     }
@@ -221,13 +221,15 @@ sample_kernel(const float* __restrict__ logits, long long ld, float* __restrict_
     if (tid == 0) out_ids[row] = best_idx_s[1];
 }
 
+// ``counter_add`` is added to every row's counter (a batch whose rows have drawn equally often can
+// keep its records on the device and pass the count here).
 UB_API int ub_sample(const float* logits, long long ld, float* work, int n_rows, int V,
                      const void* params, const int* recent, const int* bias_ids, const float* bias_vals,
-                     int* out_ids, cudaStream_t st) {
+                     int* out_ids, unsigned long long counter_add, cudaStream_t st) {
     if (n_rows <= 0) return 0;
     if (V <= 0) return UB_ERR_ARG;
     sample_kernel<<<n_rows, ST, 0, st>>>(logits, ld, work, V, (const SampleParams*)params, recent,
-                                         bias_ids, bias_vals, out_ids);
+                                         bias_ids, bias_vals, out_ids, counter_add);
     UB_LAUNCH_CHECK();
     return 0;
 }

@@ -115,3 +115,49 @@ def build_step_batch(slots, new_tokens, before, want_rows, tables_np, device, ri
                      tables=tables, max_new=int(lens.max()) if B else 0,
                      max_after=int((lens + before).max()) if B else 0,
                      host={"lens": lens, "before": before, "n_ints": total})
+
+
+class DecodeRecord:
+    """The step record of a decode step of ``B`` sequences (one token each, every logit wanted), laid
+    out once: the same parts in the same places as ``build_step_batch`` makes, in one device buffer
+    that a captured graph reads.  From step to step only the token ids, the positions, the lengths
+    before the step and (at page edges) the tables change."""
+
+    def __init__(self, B: int, table_widths: list, device, ring: PinnedRing):
+        self.B, self.device, self.ring = B, device, ring
+        sizes = [B, B, B, B + 1, B, B, B] + [B * w for w in table_widths]
+        self.offs, o = [], 0
+        for n in sizes:
+            self.offs.append(o)
+            o += -(-n // 4) * 4
+        self.total = max(o, 4)
+        self.sizes, self.table_widths = sizes, list(table_widths)
+        self.host = np.zeros(self.total, dtype=np.int32)
+        ar = np.arange(B + 1, dtype=np.int32)
+        self.host[self.offs[2]:self.offs[2] + B] = ar[:B]            # sequence of each token
+        self.host[self.offs[3]:self.offs[3] + B + 1] = ar             # first row of each sequence
+        self.host[self.offs[6]:self.offs[6] + B] = ar[:B]            # every row is wanted
+        self.static = torch.zeros(self.total, dtype=torch.int32, device=device)
+        v = [self.static[off:off + n] for off, n in zip(self.offs, sizes)]
+        tables = [v[7 + i].view(B, w) for i, w in enumerate(table_widths)]
+        self.batch = StepBatch(n_tokens=B, n_seqs=B, tok_ids=v[0], tok_pos=v[1], tok_seq=v[2], seq_start=v[3],
+                               seq_before=v[4], seq_slot=v[5], want_rows=v[6], tables=tables, max_new=1,
+                               max_after=0, host={"n_ints": self.total})
+
+    def update(self, slots, ids, before, tables_np) -> StepBatch:
+        h, o, B = self.host, self.offs, self.B
+        h[o[0]:o[0] + B] = ids
+        h[o[1]:o[1] + B] = before
+        h[o[4]:o[4] + B] = before
+        h[o[5]:o[5] + B] = slots
+        for i, t in enumerate(tables_np):
+            h[o[7 + i]:o[7 + i] + t.size] = t.reshape(-1)
+        idx, pinned = self.ring.take(self.total)
+        pinned.numpy()[:self.total] = h
+        self.static.copy_(pinned[:self.total], non_blocking=True)
+        self.ring.copied(idx)
+        b = self.batch
+        b.max_after = int(max(before)) + 1
+        b.host["lens"] = np.ones(B, dtype=np.int64)
+        b.host["before"] = np.asarray(before, dtype=np.int32)
+        return b

@@ -20,7 +20,7 @@ from ..cache import Cache, CacheError, PAGE
 from ..config.base import config_from_dir, find_architecture
 from ..parts.base import KVNeed, ModelSpec
 from ..weights import load_weights
-from .batch import PinnedRing, build_step_batch
+from .batch import DecodeRecord, PinnedRing, build_step_batch
 from .model import Model
 from .runtime import Runtime
 
@@ -304,23 +304,23 @@ class Engine:
         B = len(slots)
         longest = max(before) + 1
         key = self._decode_key(B, longest)
+        ids = [t[0] for t in new_tokens]
         entry = self._graphs.get(key)
         if entry is None:
-            n_ints = 8 * (-(-(B + 1) // 4) * 4) + sum(-(-t.size // 4) * 4 for t in tables)
-            static = torch.zeros(n_ints, dtype=torch.int32, device=self.device)
-            batch = build_step_batch(slots, new_tokens, before, want_rows, tables, self.device, self._ring, static)
+            record = DecodeRecord(B, [t.shape[1] for t in tables], self.device, self._ring)
+            batch = record.update(slots, ids, before, tables)
             self.model.forward(batch, self.cache)              # warm: libraries, tensor maps, scratch
             torch.cuda.synchronize(self.device)
             graph = torch.cuda.CUDAGraph()
             l0 = self.rt.launches
             with torch.cuda.graph(graph):
                 logits = self.model.forward(batch, self.cache)
-            entry = (graph, static, logits, batch, self.rt.launches - l0)
+            entry = (graph, record, logits, self.rt.launches - l0)
             self.rt.launches = l0
             self._graphs[key] = entry
-        graph, static, logits, _, n_launch = entry
-        batch = build_step_batch(slots, new_tokens, before, want_rows, tables, self.device, self._ring, static)
-        self.last_h2d_bytes = batch.host["n_ints"] * 4
+        graph, record, logits, n_launch = entry
+        record.update(slots, ids, before, tables)
+        self.last_h2d_bytes = record.total * 4
         graph.replay()
         self.rt.launches += n_launch
         return logits if getattr(self, "_borrow", False) else logits.clone()

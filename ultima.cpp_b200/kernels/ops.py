@@ -78,7 +78,7 @@ def _declare(lib, source: str) -> None:
         },
         "gemm_simt.cu": {"ub_gemm_simt": [P, I, P, P, I, P, I, I, I, I, L, L, L, I, P]},
         "attn_simple.cu": {"ub_attn_simple": [P, L, I, P, P, I, P, L, P, P, P, I, I, I, I, I, I, I, I, F, P]},
-        "sampling.cu": {"ub_sample": [P, L, P, I, I, P, P, P, P, P, P], "ub_sample_params_size": []},
+        "sampling.cu": {"ub_sample": [P, L, P, I, I, P, P, P, P, P, U, P], "ub_sample_params_size": []},
     }.get(source, {})
     for name, args in sigs.items():
         fn = getattr(lib, name)
@@ -218,9 +218,9 @@ SAMPLE_DTYPE = np.dtype([
     ("bias_offset", "<i4"), ("seed", "<u8"), ("counter", "<u8")])
 
 
-def sample(logits, work, params_dev, recent, bias_ids, bias_vals, out_ids):
+def sample(logits, work, params_dev, recent, bias_ids, bias_vals, out_ids, counter_add: int = 0):
     """One token id for each row of float32 ``logits``; ``params_dev`` holds one record of
-    SAMPLE_DTYPE a row (as bytes on the device)."""
+    SAMPLE_DTYPE a row (as bytes on the device); ``counter_add`` is added to every row's counter."""
     _need_cuda(logits, work, params_dev, out_ids)
     lib = _lib("sampling.cu")
     assert lib.ub_sample_params_size() == SAMPLE_DTYPE.itemsize
@@ -229,5 +229,5 @@ def sample(logits, work, params_dev, recent, bias_ids, bias_vals, out_ids):
     assert work is None or (work.dtype == torch.float32 and work.is_contiguous() and work.numel() >= n * V)
     assert out_ids.dtype == torch.int32 and out_ids.numel() >= n
     _check(lib.ub_sample(_ptr(logits), logits.stride(0), _ptr(work), n, V, _ptr(params_dev),
-                         _ptr(recent), _ptr(bias_ids), _ptr(bias_vals), _ptr(out_ids), _stream()),
+                         _ptr(recent), _ptr(bias_ids), _ptr(bias_vals), _ptr(out_ids), int(counter_add), _stream()),
            "sample")

@@ -67,7 +67,10 @@ class Sampler:
                 if p.history_window() > 0 or p.logit_bias:
                     plain = False
             greedy = all(p.greedy for p in params)
-            self._cache_key, self._cache = key, (rec, plain, greedy)
+            dev = None
+            if plain:          # nothing changes from step to step but the counters: keep the records on the device
+                dev = torch.from_numpy(rec.view(np.uint8).reshape(-1).copy()).to(self.device)
+            self._cache_key, self._cache = key, (rec, plain, greedy, dev)
         return self._cache
 
     def sample(self, logits: torch.Tensor, params: list, streams: list, counters: list,
@@ -79,10 +82,13 @@ class Sampler:
             return []
         if n > self._out.numel() - 4:
             raise ValueError(f"at most {self._out.numel() - 4} rows a call")
-        base, plain, greedy = self._records(params, streams)
-        rec = base.copy()
-        rec["counter"] = np.asarray(counters, dtype=np.uint64)
+        base, plain, greedy, base_dev = self._records(params, streams)
         dev = self.device
+        same = plain and all(c == counters[0] for c in counters)
+        rec = None
+        if not same:
+            rec = base.copy()
+            rec["counter"] = np.asarray(counters, dtype=np.uint64)
         recent_dev, bid_dev, bval_dev = self._dummy_i, self._dummy_i, self._dummy_f
         if not plain:
             recent_flat, bias_ids, bias_vals = [], [], []
@@ -100,14 +106,17 @@ class Sampler:
             if bias_ids:
                 bid_dev = torch.tensor(bias_ids, dtype=torch.int32).to(dev, non_blocking=True)
                 bval_dev = torch.tensor(bias_vals, dtype=torch.float32).to(dev, non_blocking=True)
-        params_dev = torch.from_numpy(rec.view(np.uint8).reshape(-1)).to(dev, non_blocking=True)
+        if same:               # rows that have drawn equally often: the records stay, the count is an argument
+            params_dev, counter_add = base_dev, int(counters[0])
+        else:
+            params_dev, counter_add = torch.from_numpy(rec.view(np.uint8).reshape(-1)).to(dev, non_blocking=True), 0
         work = None
         if not (greedy and plain):
             if self._work is None or self._work.numel() < n * self.vocab_size:
                 self._work = torch.empty(n * self.vocab_size, dtype=torch.float32, device=dev)
             work = self._work
         out = self._out[4:4 + n]
-        ops.sample(logits, work, params_dev, recent_dev, bid_dev, bval_dev, out)
+        ops.sample(logits, work, params_dev, recent_dev, bid_dev, bval_dev, out, counter_add)
         host = self._out[:4 + n].cpu().tolist()          # the status flags travel with the ids
         if self.rt is not None and any(host[:4]):
             self.rt.check_status()
