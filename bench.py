@@ -122,17 +122,17 @@ def fill_cache(engine, slots, n_tokens):
         engine.cache.commit(s, n_tokens)
 
 
-def timed_decode(engine, sampler, batch, steps, warmup, rng, real_prefill):
+def timed_decode(engine, sampler, batch, steps, warmup, rng, real_prefill, prompt_len=PROMPT):
     import torch
     from ultima_b200.sampling import SamplingParams
     V = engine.spec.vocab_size
     slots = engine.open(batch)
     if real_prefill:
-        prompts = [rng.integers(0, V, size=PROMPT).tolist() for _ in range(batch)]
+        prompts = [rng.integers(0, V, size=prompt_len).tolist() for _ in range(batch)]
         for i in range(batch):             # one prompt a step keeps scratch memory small
             engine.step([slots[i]], [prompts[i]], [[]])
     else:
-        fill_cache(engine, slots, PROMPT)
+        fill_cache(engine, slots, prompt_len)
     toks = rng.integers(0, V, size=(warmup + steps, batch))
     params = [SamplingParams()] * batch
     out_ids = torch.empty(batch, dtype=torch.int32, device=engine.device)
@@ -196,9 +196,11 @@ def run_ours(args):
     t0 = time.time()
     tensors = random_tensors_on_device(spec.weight_specs(), 0, torch.bfloat16, dev)
     # the cache holds the largest point: 64 sequences of a 2,048-token prompt plus the steps
-    per_seq = -(-(PROMPT + args.warmup + args.steps + 64) // 64) * 64
-    engine = Engine(spec, tensors, dtype="bfloat16", max_tokens=64 * per_seq, max_seqs=64,
-                    max_step_tokens=PREFILL_TOKENS, max_context=CONTEXT)
+    per_seq = -(-(max(args.prompt, PROMPT) + args.warmup + args.steps + 64) // 64) * 64
+    n_seq = max(64, args.batch) if args.only == "all" else args.batch
+    engine = Engine(spec, tensors, dtype="bfloat16", max_tokens=max(n_seq * per_seq, args.prefill_tokens + 64),
+                    max_seqs=n_seq, max_step_tokens=max(PREFILL_TOKENS, min(args.prefill_tokens, 8192)),
+                    max_context=max(CONTEXT, args.prompt + args.steps + args.warmup + 64, args.prefill_tokens))
     del tensors
     sampler = Sampler(dev, cfg.vocab_size, engine.rt)
     rng = np.random.default_rng(0)
@@ -207,15 +209,18 @@ def run_ours(args):
 
     if args.only == "decode":
         ms, launches, ctx = timed_decode(engine, sampler, args.batch, args.steps, args.warmup, rng,
-                                         real_prefill=not args.fast_fill)
+                                         real_prefill=not args.fast_fill, prompt_len=args.prompt)
         engine.check_errors()
+        sb = weight_bytes(cfg) + args.batch * (ctx - args.steps / 2) * kv_bytes_per_token(cfg, 2)
         print(json.dumps({"only": "decode", "batch": args.batch, "layers": cfg.num_hidden_layers,
                           "ms_per_step": round(ms / args.steps, 4), "context": int(ctx),
+                          "hbm_frac": round(sb / (ms / args.steps * 1e-3) / 1e9 / pk["hbm_gbs"], 4),
                           "value": round(args.batch * args.steps / ms * 1e3, 1), "gpu_launches": int(launches)}))
         return 0
 
     # prefill of one 2,048-token prompt
-    prompt = rng.integers(0, cfg.vocab_size, size=PREFILL_TOKENS).tolist()
+    PT = args.prefill_tokens
+    prompt = rng.integers(0, cfg.vocab_size, size=PT).tolist()
     pre_ms = []
     for i in range(2 + 3):
         s = engine.open(1)
@@ -229,8 +234,8 @@ def run_ours(args):
         if i >= 2:
             pre_ms.append(e0.elapsed_time(e1))
     pms = statistics.median(pre_ms)
-    pf = prefill_flops(cfg, PREFILL_TOKENS)
-    prefill = {"value": round(PREFILL_TOKENS / pms * 1e3, 1), "tokens": PREFILL_TOKENS, "ms": round(pms, 3),
+    pf = prefill_flops(cfg, PT)
+    prefill = {"value": round(PT / pms * 1e3, 1), "tokens": PT, "ms": round(pms, 3),
                "frac": round(pf / (pms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)}
     print(f"[bench] prefill {prefill}", file=sys.stderr, flush=True)
     if args.only == "prefill":
@@ -387,6 +392,8 @@ def main():
                     help="a part of the run only (for profiling); the JSON line then holds that part")
     ap.add_argument("--batch", type=int, default=BATCH, help="sequences of the decode step")
     ap.add_argument("--fast-fill", action="store_true", help="do not run the prompts; mark the cache as filled")
+    ap.add_argument("--prompt", type=int, default=PROMPT, help="positions each sequence holds before the timed steps")
+    ap.add_argument("--prefill-tokens", type=int, default=PREFILL_TOKENS, help="tokens of the timed prompt")
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference(args)
