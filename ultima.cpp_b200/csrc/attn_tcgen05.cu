@@ -52,6 +52,7 @@ struct TcAttnParams {
     int* error;
     // decode (one new token a sequence, keys in slices): unnormalised partial results
     float* part_o; float* part_ml; int n_slices, nh;
+    int n_seqs, n_row_tiles;                  // prompts: the grid is n_row_tiles * n_seqs * nkv blocks
 };
 
 __host__ __device__ constexpr uint32_t idesc_bf16(int m, int n, int b_mn_major) {
@@ -85,11 +86,15 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
     extern __shared__ uint8_t smem_raw[];
     pdl_trigger();
     pdl_wait();
-    const int seq = blockIdx.y, kvh = blockIdx.z;
+    // prompts: a one-dimensional grid numbered so that the blocks with the most keys to visit (the
+    // last tiles of the rows, of every sequence and KV head) are handed out first
+    const int per_tile = p.n_seqs * p.nkv;
+    const int seq = DECODE ? blockIdx.y : (blockIdx.x % per_tile) / p.nkv;
+    const int kvh = DECODE ? blockIdx.z : blockIdx.x % p.nkv;
     const int q0 = p.seq_start[seq], q_len = p.seq_start[seq + 1] - q0, before = p.seq_before[seq];
     const int G = p.group;
     const int TPB = BM / G;                                // tokens a tile: TPB * G of the 128 rows are in use
-    const int tile = DECODE ? 0 : gridDim.x - 1 - blockIdx.x;          // long tiles first
+    const int tile = DECODE ? 0 : p.n_row_tiles - 1 - blockIdx.x / per_tile;
     const int tok_first = tile * TPB;
     if (tok_first >= q_len) return;
 
@@ -443,10 +448,15 @@ UB_API int ub_attn_tc(int mode, const void* map_q, const void* map_k, const void
     p.pages_per_seq = pages_per_seq; p.ring = ring; p.nkv = nkv; p.group = group; p.window = window;
     p.c = scale * 1.4426950408889634f; p.error = error;
     p.part_o = part_o; p.part_ml = part_ml; p.n_slices = n_slices < 1 ? 1 : n_slices; p.nh = nh;
+    p.n_seqs = n_seqs; p.n_row_tiles = 1;
     if (mode == 0) {
         p.n_slices = 1;
         const int tpb = BM / group;
-        return launch_attn<2, false>(dim3((max_new + tpb - 1) / tpb, n_seqs, nkv), map_q, map_k, map_v, p, st);
+        p.n_seqs = n_seqs;
+        p.n_row_tiles = (max_new + tpb - 1) / tpb;
+        const long long blocks = (long long)p.n_row_tiles * n_seqs * nkv;
+        if (blocks > 0x7fffffffll) return UB_ERR_ARG;
+        return launch_attn<2, false>(dim3((unsigned)blocks), map_q, map_k, map_v, p, st);
     }
     if (max_new != 1) return UB_ERR_ARG;
     if (p.n_slices > 1 && (!part_o || !part_ml || ((uintptr_t)part_o & 15))) return UB_ERR_ARG;
