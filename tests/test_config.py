@@ -112,3 +112,19 @@ def test_model_description_is_data():
     assert names["lm_head.weight"] == (777, 80)
     tied = u.model_spec_for(config_from_dict(TINY_A))
     assert "lm_head.weight" not in {s.name for s in tied.weight_specs()}
+
+
+def test_stop_tokens_come_from_both_json_files(tmp_path):
+    d = dict(TINY_A, eos_token_id=7)
+    with open(tmp_path / "config.json", "w") as f:
+        json.dump(d, f)
+    assert u.config_from_dir(str(tmp_path)).eos_token_id == (7,)
+    with open(tmp_path / "generation_config.json", "w") as f:
+        json.dump({"eos_token_id": [9, 7, 11], "temperature": 0.6}, f)
+    cfg = u.config_from_dir(str(tmp_path))
+    assert cfg.eos_token_id == (7, 9, 11)
+    assert u.model_spec_for(cfg).stop_token_ids == (7, 9, 11)
+    with open(tmp_path / "generation_config.json", "w") as f:
+        json.dump({"eos_token_id": "x"}, f)
+    with pytest.raises(ConfigError, match="eos_token_id"):
+        u.config_from_dir(str(tmp_path))

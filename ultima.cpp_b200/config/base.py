@@ -88,5 +88,31 @@ def config_from_dict(data: dict):
     return entry.config_cls.from_dict(data)
 
 
+def _stop_ids_of(value) -> list:
+    if value is None:
+        return []
+    if isinstance(value, int):
+        return [value]
+    if isinstance(value, (list, tuple)) and all(isinstance(v, int) for v in value):
+        return list(value)
+    raise ConfigError(f"eos_token_id must be an integer or a list of integers, got {value!r}")
+
+
 def config_from_dir(model_dir: str):
-    return config_from_dict(read_config_json(model_dir))
+    """The folder's config.json, typed.  A generation_config.json beside it may name further
+    stop tokens under ``eos_token_id``; they are added to config.json's own."""
+    data = read_config_json(model_dir)
+    path = os.path.join(model_dir, "generation_config.json")
+    if os.path.isfile(path):
+        with open(path, "r", encoding="utf-8") as f:
+            try:
+                extra = json.load(f)
+            except json.JSONDecodeError as e:
+                raise ConfigError(f"{path} is not valid JSON: {e}") from e
+        if isinstance(extra, dict) and extra.get("eos_token_id") is not None:
+            ids = _stop_ids_of(data.get("eos_token_id"))
+            for v in _stop_ids_of(extra["eos_token_id"]):
+                if v not in ids:
+                    ids.append(v)
+            data = dict(data, eos_token_id=ids)
+    return config_from_dict(data)
