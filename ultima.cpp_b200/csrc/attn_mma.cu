@@ -513,7 +513,6 @@ __global__ void __launch_bounds__(TMA_THREADS)
 attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v, TmaDecodeParams tp) {
     extern __shared__ uint8_t smem_raw[];
     pdl_trigger();
-    pdl_wait();
     const AttnParams& p = tp.a;
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint8_t* ring = smem;                                  // [TSTAGES][K page | V page]
@@ -541,6 +540,29 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
         *err = 0;
         fence_barrier_init();
     }
+    __syncthreads();
+    // One page of keys and values into stage j % TSTAGES of the ring.
+    auto load_tile = [&](int j) {
+        const int s = j % TSTAGES;
+        const int posn = (t_lo + j) * KT;
+        const int page = tp.table[(long long)seq * tp.pages_per_seq + (posn % tp.ring) / KT];
+        const int r0 = (page * tp.nkv + kvh) * KT;
+        uint8_t* st = ring + s * 2 * PAGE_BYTES;
+        mbar_expect_tx(&full[s], 2 * PAGE_BYTES);
+#pragma unroll
+        for (int nb = 0; nb < NBLK; ++nb) {
+            tma_load_2d(st + nb * BLK_BYTES, &map_k, &full[s], nb * 64, r0);
+            tma_load_2d(st + PAGE_BYTES + nb * BLK_BYTES, &map_v, &full[s], nb * 64, r0);
+        }
+    };
+    // The pages before the one that takes this step's key and value were written by earlier steps:
+    // their copies start while the kernel that prepares q and writes the new key still runs.
+    int early = 0;
+    if (warp == 4 && lane == 0) {
+        prefetch_tmap(&map_k); prefetch_tmap(&map_v);
+        while (early < n_tiles && early < TSTAGES && t_lo + early < t_last) { load_tile(early); ++early; }
+    }
+    pdl_wait();
     constexpr int CH = HD / 8;
     for (int i = tid; i < 16 * CH; i += TMA_THREADS) {
         const int r = i / CH, ch = i % CH;
@@ -557,21 +579,11 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
 
     if (warp == 4) {
         if (lane == 0) {
-            prefetch_tmap(&map_k); prefetch_tmap(&map_v);
-            int armed = 0;
-            for (int j = 0; j < n_tiles; ++j) {
+            int armed = early;
+            for (int j = early; j < n_tiles; ++j) {
                 const int s = j % TSTAGES;
                 if (!mbar_wait(&empty[s], (uint32_t)(((j / TSTAGES) & 1) ^ 1), err)) break;
-                const int posn = (t_lo + j) * KT;
-                const int page = tp.table[(long long)seq * tp.pages_per_seq + (posn % tp.ring) / KT];
-                const int r0 = (page * tp.nkv + kvh) * KT;
-                uint8_t* st = ring + s * 2 * PAGE_BYTES;
-                mbar_expect_tx(&full[s], 2 * PAGE_BYTES);
-#pragma unroll
-                for (int nb = 0; nb < NBLK; ++nb) {
-                    tma_load_2d(st + nb * BLK_BYTES, &map_k, &full[s], nb * 64, r0);
-                    tma_load_2d(st + PAGE_BYTES + nb * BLK_BYTES, &map_v, &full[s], nb * 64, r0);
-                }
+                load_tile(j);
                 armed = j + 1;
             }
             if (*err) {

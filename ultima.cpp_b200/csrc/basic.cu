@@ -66,10 +66,18 @@ __global__ void rmsnorm_vec_kernel(const float* __restrict__ x, const int* __res
                                    const float* __restrict__ w, TO* __restrict__ out, int width, float eps) {
     __shared__ float red[33];
     pdl_trigger();
-    pdl_wait();
+    // the weights and the row index are there before the kernel that writes x has ended
     const int r = blockIdx.x;
-    const float4* xr = reinterpret_cast<const float4*>(x + (long long)(rows ? rows[r] : r) * width);
     const int nv = width >> 2;
+    const float4* w4 = reinterpret_cast<const float4*>(w);
+    float4 g[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+        const int i = threadIdx.x + u * blockDim.x;
+        if (i < nv) g[u] = w4[i];
+    }
+    const float4* xr = reinterpret_cast<const float4*>(x + (long long)(rows ? rows[r] : r) * width);
+    pdl_wait();
     float4 v[4];
     float ss = 0.f;
 #pragma unroll
@@ -79,13 +87,11 @@ __global__ void rmsnorm_vec_kernel(const float* __restrict__ x, const int* __res
     }
     ss = block_sum(ss, red);
     const float inv = 1.0f / sqrtf(ss / (float)width + eps);
-    const float4* w4 = reinterpret_cast<const float4*>(w);
 #pragma unroll
     for (int u = 0; u < 4; ++u) {
         const int i = threadIdx.x + u * blockDim.x;
         if (i < nv) {
-            const float4 g = w4[i];
-            const float o[4] = {v[u].x * g.x * inv, v[u].y * g.y * inv, v[u].z * g.z * inv, v[u].w * g.w * inv};
+            const float o[4] = {v[u].x * g[u].x * inv, v[u].y * g[u].y * inv, v[u].z * g[u].z * inv, v[u].w * g[u].w * inv};
             store_vec<TO, 4>(out + (long long)r * width + 4 * i, o);
         }
     }
@@ -205,10 +211,9 @@ __global__ void qk_prepare_vec_kernel(const TA* qkv, int n_parts, long long part
                                       TC* __restrict__ vcache, PagedKV c, int n_tokens, int nh, float eps,
                                       int write_kv) {
     pdl_trigger();
-    pdl_wait();
     // blockIdx.x is the token; the warps of its blocks take the token's heads in turn, so what belongs
     // to the token (its position, the cosines and sines of that position, the norm weights) is fetched
-    // once a warp
+    // once a warp, and before the kernel that writes qkv has ended: none of it is written by a kernel
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, n_warps = blockDim.x >> 5;
     const int heads_all = nh + 2 * c.n_kv_heads;
     const int t = blockIdx.x;
@@ -224,6 +229,7 @@ __global__ void qk_prepare_vec_kernel(const TA* qkv, int n_parts, long long part
     if (qw) load_vec<float, E>(qw + lane * E, gq);
     if (kw) load_vec<float, E>(kw + lane * E, gk);
     const bool upper = lane >= 16;
+    pdl_wait();
     for (int h = blockIdx.y * n_warps + warp; h < heads_all; h += n_warps * gridDim.y) {
         const bool is_v = h >= nh + c.n_kv_heads, is_k = !is_v && h >= nh;
         if ((is_v || is_k) && !write_kv) continue;
