@@ -158,6 +158,46 @@ def timed_decode(engine, sampler, batch, steps, warmup, rng, real_prefill, promp
     return ms, launches, ctx
 
 
+def decode_timeline(engine, batch, prompt_len, rng):
+    """Where the time of one decode step goes, kernel by kernel, as the step really runs (inside its
+    captured graph, kernels overlapping through dependent launches): for each kernel of the step's
+    last layers and the head, when it began and ended and how much later it ended than the kernel
+    before it (the share of the step's time that is its own).  Timestamps come from CUPTI through
+    torch.profiler; run few layers (--layers 6)."""
+    import torch
+    from torch.profiler import ProfilerActivity, profile
+    V = engine.spec.vocab_size
+    slots = engine.open(batch)
+    fill_cache(engine, slots, prompt_len)
+
+    def one():
+        engine.step(slots, [[int(t)] for t in rng.integers(0, V, size=batch)], None, borrow=True)
+    for _ in range(6):
+        one()
+    torch.cuda.synchronize()
+    with profile(activities=[ProfilerActivity.CUDA]) as prof:
+        for _ in range(3):
+            one()
+        torch.cuda.synchronize()
+    ev = [e for e in prof.events() if e.device_type == torch.autograd.DeviceType.CUDA]
+    ev.sort(key=lambda e: e.time_range.start)
+    last = ev[2 * (len(ev) // 3):]                       # the third step
+    t0 = last[0].time_range.start
+    rows, prev_end = [], None
+    for e in last:
+        s, en = e.time_range.start - t0, e.time_range.end - t0
+        rows.append({"kernel": e.name.split("(")[0].replace("void ", "")[:48], "start_us": round(s, 2),
+                     "end_us": round(en, 2), "own_us": None if prev_end is None else round(en - prev_end, 2)})
+        prev_end = en if prev_end is None else max(prev_end, en)
+    engine.close(slots)
+    engine.check_errors()
+    for r in rows[-24:]:
+        print(json.dumps(r))
+    print(json.dumps({"only": "timeline", "batch": batch, "layers": len(engine.spec.layers),
+                      "kernels_a_step": len(last), "step_us": round(prev_end, 2)}))
+    return 0
+
+
 def sampler_params(sampler, params, device):
     """Records of greedy sampling for ``len(params)`` rows, on the device."""
     import numpy as np
@@ -206,6 +246,9 @@ def run_ours(args):
     rng = np.random.default_rng(0)
     engine.warm_up()
     print(f"[bench] model ready in {time.time() - t0:.1f} s", file=sys.stderr, flush=True)
+
+    if args.only == "timeline":
+        return decode_timeline(engine, args.batch, args.prompt, rng)
 
     if args.only == "decode":
         ms, launches, ctx = timed_decode(engine, sampler, args.batch, args.steps, args.warmup, rng,
@@ -388,8 +431,9 @@ def main():
     ap.add_argument("--warmup", type=int, default=4)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--layers", type=int, default=0, help="fewer layers than the configuration (named in config)")
-    ap.add_argument("--only", default="all", choices=["all", "prefill", "decode"],
-                    help="a part of the run only (for profiling); the JSON line then holds that part")
+    ap.add_argument("--only", default="all", choices=["all", "prefill", "decode", "timeline"],
+                    help="a part of the run only (for profiling); the JSON line then holds that part. "
+                         "timeline: every kernel of a decode step with its begin and end inside the graph")
     ap.add_argument("--batch", type=int, default=BATCH, help="sequences of the decode step")
     ap.add_argument("--fast-fill", action="store_true", help="do not run the prompts; mark the cache as filled")
     ap.add_argument("--prompt", type=int, default=PROMPT, help="positions each sequence holds before the timed steps")

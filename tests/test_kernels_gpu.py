@@ -471,6 +471,69 @@ def test_attn_decode_tma(cfg, slices):
     assert err <= 2 ** -7, (cfg, slices, err)
 
 
+@pytest.mark.parametrize("cfg", [dict(nh=8, nkv=2, hd=128, window=0, norm=True, rot=True),
+                                 dict(nh=8, nkv=1, hd=64, window=0, norm=True, rot=True),
+                                 dict(nh=2, nkv=2, hd=256, window=0, norm=False, rot=True),
+                                 dict(nh=6, nkv=2, hd=64, window=50, norm=True, rot=False),
+                                 dict(nh=32, nkv=2, hd=128, window=0, norm=True, rot=True)])
+@pytest.mark.parametrize("slices", [None, 1, 3])
+@pytest.mark.parametrize("owner", [True, False])
+def test_attn_decode_from_the_projection_slices(cfg, slices, owner):
+    """The decode kernel that sums the slices of the fused projection, prepares q and the new key and
+    writes the cache itself gives, bit for bit, what qk_prepare followed by the decode kernel gives:
+    the output and the cache.  Without ownership of the cache it writes nothing and reads what is there."""
+    from ultima_b200.kernels import attn_tc
+    from ultima_b200.engine import Runtime
+    ops = _ops()
+    rt = Runtime(DEV, torch.bfloat16)
+    nh, nkv, hd, window = cfg["nh"], cfg["nkv"], cfg["hd"], cfg["window"]
+    befores = [0, 63, 64, 300, 700]
+    n = len(befores)
+    lens = [b + 1 for b in befores]
+    ring_pages = 12
+    kc, vc, table, _ = _paged(n, lens, nkv, hd, torch.bfloat16, ring_pages, seed=hd + 21)
+    g = torch.Generator().manual_seed(hd + 22)
+    P, W = 3, (nh + 2 * nkv) * hd
+    parts = (torch.randn(P, n, W, generator=g) * 0.6).to(DEV)
+    qw = (1 + 0.1 * torch.randn(hd, generator=g)).to(DEV) if cfg["norm"] else None
+    kw = (1 + 0.1 * torch.randn(hd, generator=g)).to(DEV) if cfg["norm"] else None
+    cos = sin = None
+    if cfg["rot"]:
+        ang = torch.rand(800, hd // 2, generator=g) * 6.28
+        cos, sin = torch.cos(ang).to(DEV), torch.sin(ang).to(DEV)
+    b = _B()
+    b.seq_start = torch.arange(n + 1, dtype=torch.int32, device=DEV)
+    b.seq_before = torch.tensor(befores, dtype=torch.int32, device=DEV)
+    b.n_seqs, b.max_new, b.max_after = n, 1, max(lens)
+    tok_pos = b.seq_before.clone()
+    tok_seq = torch.arange(n, dtype=torch.int32, device=DEV)
+    eps = 1e-5
+    # the two kernels
+    kv_a = _KV(kc.clone(), vc.clone(), table, ring_pages * 64, window or None)
+    kv_a.owner = owner
+    q = torch.empty(n, nh * hd, dtype=torch.bfloat16, device=DEV)
+    ops.qk_prepare(parts, qw, kw, cos, sin, tok_pos, tok_seq, kv_a.k, kv_a.v, table, kv_a.ring, 64, nh, nkv, hd, eps,
+                   write_kv=owner, q_out=q)
+    out_a = torch.full((n, nh * hd), float("nan"), dtype=torch.bfloat16, device=DEV)
+    attn_tc.attention(q, kv_a, out_a, b, nh, nkv, hd, 1 / math.sqrt(hd), rt, slices=slices, kernel="tma")
+    # the one kernel
+    kv_b = _KV(kc.clone(), vc.clone(), table, ring_pages * 64, window or None)
+    kv_b.owner = owner
+    out_b = torch.full((n, nh * hd), float("nan"), dtype=torch.bfloat16, device=DEV)
+    assert attn_tc.decode_from_qkv(parts, qw, kw, cos, sin, eps, kv_b, out_b, b, nh, nkv, hd, 1 / math.sqrt(hd), rt,
+                                   slices=slices, force=True)
+    torch.cuda.synchronize()
+    rt.check_status()
+    assert torch.isfinite(out_b).all()
+    assert torch.equal(out_a, out_b), (cfg, slices, owner, (out_a.float() - out_b.float()).abs().max().item())
+    same = lambda x, y: torch.equal(x.view(torch.int16), y.view(torch.int16))       # NaN-filled spare rows too
+    assert same(kv_a.k, kv_b.k) and same(kv_a.v, kv_b.v)
+    if not owner:
+        assert same(kv_b.k, kc) and same(kv_b.v, vc)
+    else:
+        assert not same(kv_b.k, kc)
+
+
 def test_gemm_tc_partial_products_and_their_consumers():
     """K cut into slices written side by side; qk_prepare and silu_mul add the slices up."""
     gemm_tc, rt = _tc()

@@ -503,11 +503,82 @@ __device__ __forceinline__ void weighted_values_swz(float (*o)[4], const float (
     }
 }
 
+// With ``qkv`` set the kernel also does what qk_prepare does for a step of one token a sequence: a
+// CTA sums the partial results of the fused projection for its own query heads, norms and rotates
+// them straight into shared memory, and the CTA that reads the page of the new position does the
+// same for the new key (and copies the new value), writes both into the cache for later steps and
+// puts them into its own copy of the page.  q never goes through global memory, and the kernel
+// between the projection and the attention is gone.
+struct FusedQKV {
+    const float* qkv;            // [n_parts][tokens, (nh + 2 nkv) * HD] float32; null: q is read from a.q
+    int n_parts; long long part_stride;
+    const float* qw; const float* kw;        // [HD] norm weights or null
+    const float* cs; const float* sn;        // [max_pos, HD / 2] or null
+    float eps;
+    bf16* kcache; bf16* vcache;              // where the new key and value go; null: the cache is another layer's
+};
+
 struct TmaDecodeParams {
     AttnParams a;
     const int* table; int pages_per_seq, ring, nkv;
     int* error;
+    FusedQKV f;
 };
+
+constexpr bool FUSABLE = HD == 64 || HD == 128 || HD == 256;
+constexpr int FE = FUSABLE ? HD / 32 : 2;       // elements of a head a lane holds, neighbours; the lower 16
+                                                // lanes the first half of the head, the upper 16 the second
+
+// The sums of the partial results of NSRC heads of the fused projection's row, a lane's FE elements
+// of each: four parts of every head are in flight before the first add, and they are added in
+// their order.
+template <int NSRC>
+__device__ __forceinline__ void fused_sums(const FusedQKV& f, const float* const* src, int lane, float (*v)[FE]) {
+    for (int p0 = 0; p0 < f.n_parts; p0 += 4) {
+        float part[NSRC][4][FE];
+#pragma unroll
+        for (int s = 0; s < NSRC; ++s) {
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                if (p0 + u < f.n_parts) load_vec<float, FE>(src[s] + (long long)(p0 + u) * f.part_stride + lane * FE, part[s][u]);
+                else {
+#pragma unroll
+                    for (int i = 0; i < FE; ++i) part[s][u][i] = 0.f;
+                }
+            }
+        }
+#pragma unroll
+        for (int s = 0; s < NSRC; ++s) {
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+#pragma unroll
+                for (int i = 0; i < FE; ++i) v[s][i] = (p0 == 0 && u == 0) ? part[s][u][i] : v[s][i] + part[s][u][i];
+            }
+        }
+    }
+}
+
+// Norm with ``w`` (or not) and rotation by (co, si) (or not) of one head held FE elements a lane.
+__device__ __forceinline__ void fused_finish(const FusedQKV& f, const float* w, bool rotate, const float* co,
+                                             const float* si, int lane, float* v) {
+    if (w) {
+        float ss = 0.f;
+#pragma unroll
+        for (int i = 0; i < FE; ++i) ss += v[i] * v[i];
+        ss = warp_sum(ss);
+        const float inv = 1.0f / sqrtf(ss / (float)HD + f.eps);
+#pragma unroll
+        for (int i = 0; i < FE; ++i) v[i] = v[i] * w[i] * inv;
+    }
+    if (rotate) {
+        const bool upper = lane >= 16;
+#pragma unroll
+        for (int i = 0; i < FE; ++i) {
+            const float other = __shfl_xor_sync(0xffffffffu, v[i], 16);
+            v[i] = upper ? other * si[i] + v[i] * co[i] : v[i] * co[i] - other * si[i];
+        }
+    }
+}
 
 __global__ void __launch_bounds__(TMA_THREADS)
 attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v, TmaDecodeParams tp) {
@@ -562,13 +633,72 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
         prefetch_tmap(&map_k); prefetch_tmap(&map_v);
         while (early < n_tiles && early < TSTAGES && t_lo + early < t_last) { load_tile(early); ++early; }
     }
+    // the new key and value, held by the warp that reads their row of the page (fused mode only)
+    const FusedQKV& f = tp.f;
+    const bool fused = FUSABLE && f.qkv != nullptr;
+    const bool has_new = fused && f.kcache != nullptr && n_tiles > 0 && t_hi == t_last;
+    const int new_row = pos % KT;
+    float new_k[FE], new_v[FE];
+    float co[FE], si[FE], gq[FE], gk[FE];
+    if (fused && warp < 4) {
+        // the tables and the norm weights are written by no kernel: fetched before the wait
+        if (f.cs) {
+            const int j0 = (lane & 15) * FE;
+            load_vec<float, FE>(f.cs + (long long)pos * (HD / 2) + j0, co);
+            load_vec<float, FE>(f.sn + (long long)pos * (HD / 2) + j0, si);
+        }
+        if (f.qw) load_vec<float, FE>(f.qw + lane * FE, gq);
+        if (f.kw) load_vec<float, FE>(f.kw + lane * FE, gk);
+    }
     pdl_wait();
-    constexpr int CH = HD / 8;
-    for (int i = tid; i < 16 * CH; i += TMA_THREADS) {
-        const int r = i / CH, ch = i % CH;
-        uint4 v = make_uint4(0, 0, 0, 0);
-        if (r < G) v = *reinterpret_cast<const uint4*>(p.q + (long long)row * p.q_stride + (long long)(kvh * G + r) * HD + ch * 8);
-        *reinterpret_cast<uint4*>(Qs + r * LDS + ch * 8) = v;
+    if (fused) {
+        if (warp < 4) {
+            const int heads_all = p.nh + 2 * tp.nkv;
+            const float* trow = f.qkv + (long long)row * heads_all * HD;
+            const bool mine = has_new && warp == new_row / 16;
+            // this warp's first query head, and the new key and value if they are this warp's: one round of loads
+            float first[3][FE];
+            {
+                const float* src[3] = {trow + (long long)(kvh * G + min(warp, G - 1)) * HD,
+                                       trow + (long long)(p.nh + kvh) * HD, trow + (long long)(p.nh + tp.nkv + kvh) * HD};
+                if (mine) fused_sums<3>(f, src, lane, first);
+                else fused_sums<1>(f, src, lane, first);
+            }
+            for (int r = warp; r < 16; r += 4) {
+                float v[FE];
+                if (r < G) {
+                    if (r == warp) {
+#pragma unroll
+                        for (int i = 0; i < FE; ++i) v[i] = first[0][i];
+                    } else {
+                        const float* src[1] = {trow + (long long)(kvh * G + r) * HD};
+                        fused_sums<1>(f, src, lane, &v);
+                    }
+                    fused_finish(f, f.qw ? gq : nullptr, f.cs != nullptr, co, si, lane, v);
+                } else {
+#pragma unroll
+                    for (int i = 0; i < FE; ++i) v[i] = 0.f;
+                }
+                store_vec<bf16, FE>(Qs + r * LDS + lane * FE, v);
+            }
+            if (mine) {
+#pragma unroll
+                for (int i = 0; i < FE; ++i) { new_k[i] = first[1][i]; new_v[i] = first[2][i]; }
+                fused_finish(f, f.kw ? gk : nullptr, f.cs != nullptr, co, si, lane, new_k);
+                const PagedKV c{tp.table, tp.pages_per_seq, tp.ring, KT, tp.nkv, HD};
+                const long long at = paged_offset(c, seq, pos, kvh) + lane * FE;
+                store_vec<bf16, FE>(f.kcache + at, new_k);
+                store_vec<bf16, FE>(f.vcache + at, new_v);
+            }
+        }
+    } else {
+        constexpr int CH = HD / 8;
+        for (int i = tid; i < 16 * CH; i += TMA_THREADS) {
+            const int r = i / CH, ch = i % CH;
+            uint4 v = make_uint4(0, 0, 0, 0);
+            if (r < G) v = *reinterpret_cast<const uint4*>(p.q + (long long)row * p.q_stride + (long long)(kvh * G + r) * HD + ch * 8);
+            *reinterpret_cast<uint4*>(Qs + r * LDS + ch * 8) = v;
+        }
     }
     __syncthreads();
 
@@ -600,6 +730,13 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
             if (!mbar_wait(&full[s], (uint32_t)((j / TSTAGES) & 1), err)) break;
             const uint32_t k_base = smem_u32(ring + s * 2 * PAGE_BYTES), v_base = k_base + PAGE_BYTES;
             const int base = (t_lo + j) * KT;
+            if (has_new && t_lo + j == t_last && warp == new_row / 16) {
+                // the page came from the cache as it was before this step: the new key and value go in here
+                uint8_t* pg = ring + s * 2 * PAGE_BYTES;
+                store_vec<bf16, FE>(reinterpret_cast<bf16*>(pg + swz(new_row, lane * FE)), new_k);
+                store_vec<bf16, FE>(reinterpret_cast<bf16*>(pg + PAGE_BYTES + swz(new_row, lane * FE)), new_v);
+                __syncwarp();
+            }
             if (base + KT - 1 > pos) {
                 // this warp's rows of V past the sequence's end: zeros instead of what the page held before
                 for (int i = lane; i < 16 * NBLK * 8; i += 32) {
@@ -675,14 +812,16 @@ UB_API int ub_attn_map_kv(void* out_map, const void* cache, long long n_pages, i
 UB_API int ub_attn_decode_tma_stages() { return TSTAGES; }
 
 // one new token for every sequence, group <= 16; K and V through their tensor maps
-UB_API int ub_attn_decode_tma(const void* map_k, const void* map_v, const void* q, long long q_stride, void* out,
-                              long long o_stride, const int* seq_start, const int* seq_before, const int* table,
-                              int pages_per_seq, int ring, int page, int n_seqs, int nh, int nkv, int window,
-                              float scale, int n_slices, float* part_o, float* part_ml, int* error, cudaStream_t st) {
+static int decode_tma_launch(const void* map_k, const void* map_v, const void* q, long long q_stride, void* out,
+                             long long o_stride, const int* seq_start, const int* seq_before, const int* table,
+                             int pages_per_seq, int ring, int page, int n_seqs, int nh, int nkv, int window,
+                             float scale, int n_slices, float* part_o, float* part_ml, int* error, const FusedQKV& f,
+                             cudaStream_t st) {
     if (n_seqs <= 0) return 0;
     if (page != KT || ring % page != 0 || nh % nkv != 0 || (q_stride % 8) != 0 || (o_stride % 2) != 0) return UB_ERR_ARG;
     if (((uintptr_t)q & 15) || ((uintptr_t)out & 3) || n_seqs > 65535 || nkv > 65535 || nh / nkv > 16) return UB_ERR_ARG;
     TmaDecodeParams tp;
+    tp.f = f;
     AttnParams& p = tp.a;
     p.q = (const bf16*)q; p.q_stride = q_stride; p.out = (bf16*)out; p.o_stride = o_stride;
     p.kc = nullptr; p.vc = nullptr; p.seq_start = seq_start; p.seq_before = seq_before;
@@ -706,6 +845,34 @@ UB_API int ub_attn_decode_tma(const void* map_k, const void* map_v, const void* 
         if (e != cudaSuccess) return (int)e;
     }
     return 0;
+}
+
+UB_API int ub_attn_decode_tma(const void* map_k, const void* map_v, const void* q, long long q_stride, void* out,
+                              long long o_stride, const int* seq_start, const int* seq_before, const int* table,
+                              int pages_per_seq, int ring, int page, int n_seqs, int nh, int nkv, int window,
+                              float scale, int n_slices, float* part_o, float* part_ml, int* error, cudaStream_t st) {
+    FusedQKV f{};
+    return decode_tma_launch(map_k, map_v, q, q_stride, out, o_stride, seq_start, seq_before, table, pages_per_seq,
+                             ring, page, n_seqs, nh, nkv, window, scale, n_slices, part_o, part_ml, error, f, st);
+}
+
+// The same from the fused projection's result instead of q: qkv [n_parts][tokens, (nh + 2 nkv) * HD]
+// float32, its parts part_stride elements apart and summed here; qw, kw [HD] norm weights (null: no
+// norm); cs, sn [max_pos, HD / 2] (null: no rotation); kcache, vcache: where the new key and value
+// are written (null: this layer reads a cache that another layer has written).  Head sizes 64, 128, 256.
+UB_API int ub_attn_decode_tma_qkv(const void* map_k, const void* map_v, const float* qkv, int n_parts,
+                                  long long part_stride, const float* qw, const float* kw, const float* cs,
+                                  const float* sn, float eps, void* kcache, void* vcache, void* out, long long o_stride,
+                                  const int* seq_start, const int* seq_before, const int* table, int pages_per_seq,
+                                  int ring, int page, int n_seqs, int nh, int nkv, int window, float scale,
+                                  int n_slices, float* part_o, float* part_ml, int* error, cudaStream_t st) {
+    if (!FUSABLE) return UB_ERR_UNSUPPORTED;
+    if (!qkv || n_parts < 1 || (part_stride % 4) != 0 || (!kcache) != (!vcache) || (!cs) != (!sn)) return UB_ERR_ARG;
+    if ((((uintptr_t)qkv | (uintptr_t)qw | (uintptr_t)kw | (uintptr_t)cs | (uintptr_t)sn | (uintptr_t)kcache |
+          (uintptr_t)vcache) & 15) != 0) return UB_ERR_ARG;
+    FusedQKV f{qkv, n_parts, part_stride, qw, kw, cs, sn, eps, (bf16*)kcache, (bf16*)vcache};
+    return decode_tma_launch(map_k, map_v, nullptr, 0, out, o_stride, seq_start, seq_before, table, pages_per_seq,
+                             ring, page, n_seqs, nh, nkv, window, scale, n_slices, part_o, part_ml, error, f, st);
 }
 #endif   // HEAD_DIM % 64 == 0
 

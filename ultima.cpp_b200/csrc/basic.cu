@@ -28,11 +28,40 @@ __global__ void embed_kernel(const TT* __restrict__ table, const int* __restrict
         x[(long long)t * width + i] = ok ? to_f32<TT>(row[i]) : 0.f;
 }
 
+// The same, eight values a thread and step: rows that begin on 16-byte boundaries.
+template <typename TT>
+__global__ void embed_vec_kernel(const TT* __restrict__ table, const int* __restrict__ ids,
+                                 float* __restrict__ x, int width, int vocab, int* status) {
+    pdl_trigger();
+    pdl_wait();
+    const int t = blockIdx.x;
+    const int id = ids[t];
+    const bool ok = id >= 0 && id < vocab;
+    if (!ok && threadIdx.x == 0) atomicExch(status, 1);
+    const TT* row = table + (long long)(ok ? id : 0) * width;
+    for (int i = threadIdx.x * 8; i < width; i += blockDim.x * 8) {
+        float v[8];
+        load_vec<TT, 8>(row + i, v);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) v[j] = ok ? v[j] : 0.f;
+        store_vec<float, 8>(x + (long long)t * width + i, v);
+    }
+}
+
 UB_API int ub_embed(const void* table, int table_dtype, const int* ids, float* x, int n_tokens,
                     int width, int vocab, int* status, cudaStream_t st) {
     if (n_tokens <= 0) return 0;
-    const int threads = width >= 1024 ? 256 : 128;
     cudaError_t e;
+    if (width % 8 == 0 && (((uintptr_t)table | (uintptr_t)x) & 15) == 0 && (table_dtype == UB_F32 || table_dtype == UB_BF16)) {
+        int vt = 32;
+        while (vt < 256 && vt * 16 < width) vt <<= 1;
+        if (table_dtype == UB_F32)
+            e = ub_launch_dependent(embed_vec_kernel<float>, dim3(n_tokens), dim3(vt), 0, st, (const float*)table, ids, x, width, vocab, status);
+        else
+            e = ub_launch_dependent(embed_vec_kernel<__nv_bfloat16>, dim3(n_tokens), dim3(vt), 0, st, (const __nv_bfloat16*)table, ids, x, width, vocab, status);
+        return (int)e;
+    }
+    const int threads = width >= 1024 ? 256 : 128;
     if (table_dtype == UB_F32)
         e = ub_launch_dependent(embed_kernel<float>, dim3(n_tokens), dim3(threads), 0, st, (const float*)table, ids, x, width, vocab, status);
     else if (table_dtype == UB_BF16)

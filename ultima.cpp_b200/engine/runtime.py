@@ -121,6 +121,21 @@ class Runtime:
         return out
 
     # ---- attention ----------------------------------------------------------------------
+    def attention_from_qkv(self, qkv_parts, q_norm, k_norm, cos, sin, eps, kv, out, batch, n_heads, n_kv_heads,
+                           head_dim, scale) -> bool:
+        """Attention of a step of one token a sequence, straight from the float32 partial results of
+        the fused q/k/v projection: one kernel sums them, prepares q and the new key, writes the new
+        key and value and attends.  False when no kernel takes the case; the caller then prepares
+        q and the cache itself and calls ``attention``."""
+        if not (self.use_tensor_cores and qkv_parts is not None and batch.max_new == 1):
+            return False
+        from ..kernels import attn_tc
+        done = attn_tc.decode_from_qkv(qkv_parts, q_norm, k_norm, cos, sin, eps, kv, out, batch, n_heads,
+                                       n_kv_heads, head_dim, scale, self)
+        if done:
+            self.launches += 1
+        return done
+
     def attention(self, q, kv, out, batch, n_heads, n_kv_heads, head_dim, scale):
         self.launches += 1
         if self.use_tensor_cores and q.dtype == torch.bfloat16:

@@ -40,6 +40,11 @@ def lib(head_dim: int):
                                              c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                                              c_float, c_int, c_void_p, c_void_p, c_void_p, c_void_p]
             L.ub_attn_decode_tma.restype = c_int
+            L.ub_attn_decode_tma_qkv.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_longlong, c_void_p, c_void_p,
+                                                 c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_void_p, c_longlong,
+                                                 c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
+                                                 c_int, c_float, c_int, c_void_p, c_void_p, c_void_p, c_void_p]
+            L.ub_attn_decode_tma_qkv.restype = c_int
         _libs[head_dim] = L
     return L
 
@@ -129,6 +134,51 @@ def decode_slices(n_seqs: int, n_kv_heads: int, longest: int, window, per_sm: in
     want = -(-per_sm * N_SMS // ctas)
     n = max(1, min(want, tiles, SLICE_CAP))
     return 1 << (n.bit_length() - 1)            # a power of two: few distinct captured graphs
+
+
+FUSE_QKV = _os.environ.get("ULTIMA_ATTN_FUSE_QKV", "1") != "0"
+
+
+def decode_from_qkv(qkv, q_norm, k_norm, cos, sin, eps, kv, out, batch, n_heads, n_kv_heads, head_dim, scale, rt,
+                    slices: int | None = None, force: bool = False) -> bool:
+    """A step of one token a sequence, straight from the fused projection's float32 partial results
+    ``qkv`` [parts, T, (heads + 2 kv heads) * head size]: the attention kernel sums them, norms and
+    rotates its own query heads and the new key, and writes the new key and value into the cache
+    (when this layer owns it).  False: the case is not this kernel's (the caller prepares q and
+    calls ``attention``)."""
+    if not (FUSE_QKV or force) or not (USE_TMA_DECODE or force):
+        return False
+    group = n_heads // n_kv_heads
+    if not (batch.max_new == 1 and group <= 16 and head_dim in (64, 128, 256) and qkv.dim() == 3
+            and qkv.dtype == torch.float32 and qkv.is_contiguous() and kv.k.dtype == torch.bfloat16
+            and kv.k.is_contiguous() and kv.v.is_contiguous() and kv.page == 64
+            and out.dtype == torch.bfloat16 and out.stride(1) == 1 and qkv.stride(0) % 4 == 0
+            and qkv.shape[2] == (n_heads + 2 * n_kv_heads) * head_dim):
+        return False
+    if USE_TCGEN05_DECODE and not force:
+        return False
+    for t in (q_norm, k_norm, cos, sin):
+        if t is not None and not (t.dtype == torch.float32 and t.is_contiguous() and t.data_ptr() % 16 == 0):
+            return False
+    L = lib(head_dim)
+    n_slices = slices or decode_slices(batch.n_seqs, n_kv_heads, batch.max_after, kv.window)
+    part_o = part_ml = None
+    if n_slices > 1:
+        part_o = rt.arena.alloc((batch.n_seqs, n_heads, n_slices, head_dim), torch.float32)
+        part_ml = rt.arena.alloc((batch.n_seqs, n_heads, n_slices, 2), torch.float32)
+    mk = _tc_map(("kvd", kv.k.data_ptr(), kv.k.shape[0], n_kv_heads, head_dim),
+                 lambda a: L.ub_attn_map_kv(a, kv.k.data_ptr(), kv.k.shape[0], n_kv_heads))
+    mv = _tc_map(("kvd", kv.v.data_ptr(), kv.v.shape[0], n_kv_heads, head_dim),
+                 lambda a: L.ub_attn_map_kv(a, kv.v.data_ptr(), kv.v.shape[0], n_kv_heads))
+    own = bool(kv.owner)
+    rc = L.ub_attn_decode_tma_qkv(mk, mv, _ptr(qkv), qkv.shape[0], qkv.stride(0), _ptr(q_norm), _ptr(k_norm),
+                                  _ptr(cos), _ptr(sin), float(eps), _ptr(kv.k) if own else None,
+                                  _ptr(kv.v) if own else None, _ptr(out), out.stride(0), _ptr(batch.seq_start),
+                                  _ptr(batch.seq_before), _ptr(kv.table), kv.table.shape[1], kv.ring, kv.page,
+                                  batch.n_seqs, n_heads, n_kv_heads, int(kv.window or 0), float(scale), n_slices,
+                                  _ptr(part_o), _ptr(part_ml), _ptr(rt.status[1:2]), _stream())
+    _check(rc, "attn_decode_tma_qkv")
+    return True
 
 
 def attention(q, kv, out, batch, n_heads, n_kv_heads, head_dim, scale, rt, slices: int | None = None,

@@ -69,8 +69,14 @@ class Attention(Mixer):
         cos = sin = None
         if self.position is not None:
             cos, sin = self.position.cos, self.position.sin
+        o = rt.arena.alloc((T, self.q_width), rt.dtype)
         parts = rt.matmul_parts(h, self.wqkv)        # few tokens: K in slices, summed by the next kernel
         if parts is not None:
+            # one token a sequence: the attention kernel can take the slices as they are
+            if rt.attention_from_qkv(parts, self.q_norm, self.k_norm, cos, sin, self.eps, kv, o, batch,
+                                     self.nh, self.nkv, self.hd, self.scale):
+                rt.matmul(o, self.wo, residual, ops.EPI_ADD)
+                return
             qkv = parts
             q = rt.arena.alloc((T, self.q_width), rt.dtype)
         else:
@@ -81,6 +87,5 @@ class Attention(Mixer):
         ops.qk_prepare(qkv, self.q_norm, self.k_norm, cos, sin, batch.tok_pos, batch.tok_seq,
                        kv.k, kv.v, kv.table, kv.ring, kv.page, self.nh, self.nkv, self.hd, self.eps,
                        write_kv=kv.owner, q_out=q)
-        o = rt.arena.alloc((T, self.q_width), rt.dtype)
         rt.attention(q, kv, o, batch, self.nh, self.nkv, self.hd, self.scale)
         rt.matmul(o, self.wo, residual, ops.EPI_ADD)
