@@ -566,7 +566,7 @@ __device__ __forceinline__ void fused_finish(const FusedQKV& f, const float* w, 
 #pragma unroll
         for (int i = 0; i < FE; ++i) ss += v[i] * v[i];
         ss = warp_sum(ss);
-        const float inv = 1.0f / sqrtf(ss / (float)HD + f.eps);
+        const float inv = inv_rms(ss, (float)HD, f.eps);
 #pragma unroll
         for (int i = 0; i < FE; ++i) v[i] = v[i] * w[i] * inv;
     }

@@ -84,7 +84,7 @@ __global__ void rmsnorm_kernel(const float* __restrict__ x, const int* __restric
     float ss = 0.f;
     for (int i = threadIdx.x; i < width; i += blockDim.x) { const float v = xr[i]; ss += v * v; }
     ss = block_sum(ss, red);
-    const float inv = 1.0f / sqrtf(ss / (float)width + eps);
+    const float inv = inv_rms(ss, (float)width, eps);
     for (int i = threadIdx.x; i < width; i += blockDim.x)
         out[(long long)r * width + i] = from_f32<TO>(xr[i] * w[i] * inv);
 }
@@ -115,7 +115,7 @@ __global__ void rmsnorm_vec_kernel(const float* __restrict__ x, const int* __res
         if (i < nv) { v[u] = xr[i]; ss += v[u].x * v[u].x + v[u].y * v[u].y + v[u].z * v[u].z + v[u].w * v[u].w; }
     }
     ss = block_sum(ss, red);
-    const float inv = 1.0f / sqrtf(ss / (float)width + eps);
+    const float inv = inv_rms(ss, (float)width, eps);
 #pragma unroll
     for (int u = 0; u < 4; ++u) {
         const int i = threadIdx.x + u * blockDim.x;
@@ -208,7 +208,7 @@ __global__ void qk_prepare_kernel(const TA* qkv, int n_parts, long long part_str
         }
     }
     ss = warp_sum(ss);
-    const float inv = w ? 1.0f / sqrtf(ss / (float)hd + eps) : 1.0f;
+    const float inv = w ? inv_rms(ss, (float)hd, eps) : 1.0f;
     TC* dst = is_k ? kcache + paged_offset(c, seq, pos, h - nh) : nullptr;
     TQ* qdst = q_out + (long long)t * q_out_stride + (long long)h * hd;
 #pragma unroll
@@ -232,7 +232,7 @@ __global__ void qk_prepare_kernel(const TA* qkv, int n_parts, long long part_str
 // lower 16 lanes the first half of the head and the upper 16 the second, so the partner of a
 // rotation pair sits 16 lanes away and every access is one aligned vector.
 template <typename TA, typename TQ, typename TC, int E>
-__global__ void qk_prepare_vec_kernel(const TA* qkv, int n_parts, long long part_stride,
+__global__ void __launch_bounds__(256, E <= 4 ? 4 : 2) qk_prepare_vec_kernel(const TA* qkv, int n_parts, long long part_stride,
                                       TQ* q_out, long long q_out_stride, const float* __restrict__ qw,
                                       const float* __restrict__ kw, const float* __restrict__ cs,
                                       const float* __restrict__ sn, const int* __restrict__ tok_pos,
@@ -250,50 +250,73 @@ __global__ void qk_prepare_vec_kernel(const TA* qkv, int n_parts, long long part
     const int pos = tok_pos[t];
     const int seq = tok_seq[t];
     float co[E], si[E], gq[E], gk[E];
-    if (cs) {
-        const int j0 = (lane & 15) * E;                          // index of the pair within the half
-        load_vec<float, E>(cs + (long long)pos * half + j0, co);
-        load_vec<float, E>(sn + (long long)pos * half + j0, si);
-    }
     if (qw) load_vec<float, E>(qw + lane * E, gq);
     if (kw) load_vec<float, E>(kw + lane * E, gk);
     const bool upper = lane >= 16;
+    // where the token's keys and values go: the page is looked up once, a head is then a stride away
+    const int li = pos % c.ring;
+    const long long kv_at = write_kv ? (((long long)c.table[(long long)seq * c.pages_per_seq + li / c.page] * c.n_kv_heads) * c.page
+                                        + (li % c.page)) * hd + lane * E : 0;
+    const long long kv_head_stride = (long long)c.page * hd;
+    const TA* trow = qkv + (long long)t * heads_all * hd + lane * E;
+    TQ* qrow = q_out + (long long)t * q_out_stride + lane * E;
     pdl_wait();
-    for (int h = blockIdx.y * n_warps + warp; h < heads_all; h += n_warps * gridDim.y) {
-        const bool is_v = h >= nh + c.n_kv_heads, is_k = !is_v && h >= nh;
-        if ((is_v || is_k) && !write_kv) continue;
-        const TA* row = qkv + ((long long)t * heads_all + h) * hd + lane * E;
-        float v[E];
-        load_vec<TA, E>(row, v);
-        for (int p = 1; p < n_parts; ++p) {
-            float more[E];
-            load_vec<TA, E>(row + p * part_stride, more);
+    // four of the warp's heads at a time: the loads of all four are in flight before the first is used
+    const int h_step = n_warps * gridDim.y;
+    const int h_first = blockIdx.y * n_warps + warp;
+    for (int h0 = h_first; h0 < heads_all; h0 += 4 * h_step) {
+        float v4[4][E];
 #pragma unroll
-            for (int i = 0; i < E; ++i) v[i] += more[i];
+        for (int u = 0; u < 4; ++u) {
+            const int h = h0 + u * h_step;
+            const bool is_kv = h >= nh;
+            if (h < heads_all && !(is_kv && !write_kv))
+                load_vec<TA, E>(trow + h * hd, v4[u]);
         }
-        if (is_v) {
-            store_vec<TC, E>(vcache + paged_offset(c, seq, pos, h - nh - c.n_kv_heads) + lane * E, v);
-            continue;
+        if (cs && h0 == h_first) {
+            // after the first heads' loads, which do not have to wait for the position as these do
+            const int j0 = (lane & 15) * E;                      // index of the pair within the half
+            load_vec<float, E>(cs + (long long)pos * half + j0, co);
+            load_vec<float, E>(sn + (long long)pos * half + j0, si);
         }
-        if (is_k ? kw != nullptr : qw != nullptr) {
-            float ss = 0.f;
 #pragma unroll
-            for (int i = 0; i < E; ++i) ss += v[i] * v[i];
-            ss = warp_sum(ss);
-            const float inv = 1.0f / sqrtf(ss / (float)hd + eps);
+        for (int u = 0; u < 4; ++u) {
+            const int h = h0 + u * h_step;
+            if (h >= heads_all) break;
+            const bool is_v = h >= nh + c.n_kv_heads, is_k = !is_v && h >= nh;
+            if ((is_v || is_k) && !write_kv) continue;
+            float* v = v4[u];
+            const TA* row = trow + h * hd;
+            for (int p = 1; p < n_parts; ++p) {
+                float more[E];
+                load_vec<TA, E>(row + p * part_stride, more);
 #pragma unroll
-            for (int i = 0; i < E; ++i) v[i] = v[i] * (is_k ? gk[i] : gq[i]) * inv;
-        }
-        if (cs) {
-#pragma unroll
-            for (int i = 0; i < E; ++i) {
-                const float other = __shfl_xor_sync(0xffffffffu, v[i], 16);
-                // lower lanes hold a (partner b): a c - b s; upper lanes hold b (partner a): a s + b c
-                v[i] = upper ? other * si[i] + v[i] * co[i] : v[i] * co[i] - other * si[i];
+                for (int i = 0; i < E; ++i) v[i] += more[i];
             }
+            if (is_v) {
+                store_vec<TC, E>(vcache + kv_at + (h - nh - c.n_kv_heads) * kv_head_stride, v);
+                continue;
+            }
+            if (is_k ? kw != nullptr : qw != nullptr) {
+                float ss = 0.f;
+#pragma unroll
+                for (int i = 0; i < E; ++i) ss += v[i] * v[i];
+                ss = warp_sum(ss);
+                const float inv = inv_rms(ss, (float)hd, eps);
+#pragma unroll
+                for (int i = 0; i < E; ++i) v[i] = v[i] * (is_k ? gk[i] : gq[i]) * inv;
+            }
+            if (cs) {
+#pragma unroll
+                for (int i = 0; i < E; ++i) {
+                    const float other = __shfl_xor_sync(0xffffffffu, v[i], 16);
+                    // lower lanes hold a (partner b): a c - b s; upper lanes hold b (partner a): a s + b c
+                    v[i] = upper ? other * si[i] + v[i] * co[i] : v[i] * co[i] - other * si[i];
+                }
+            }
+            if (is_k) store_vec<TC, E>(kcache + kv_at + (h - nh) * kv_head_stride, v);
+            else store_vec<TQ, E>(qrow + h * hd, v);
         }
-        if (is_k) store_vec<TC, E>(kcache + paged_offset(c, seq, pos, h - nh) + lane * E, v);
-        else store_vec<TQ, E>(q_out + (long long)t * q_out_stride + (long long)h * hd + lane * E, v);
     }
 }
 

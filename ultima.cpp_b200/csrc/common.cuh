@@ -68,14 +68,29 @@ template <typename T, int E>
 __device__ __forceinline__ void store_vec(T* p, const float* v) {
     constexpr int NB = sizeof(T) * E;
     alignas(16) T tmp[E];
+    if constexpr (sizeof(T) == 2 && E % 2 == 0) {
+        // two values a conversion instruction
 #pragma unroll
-    for (int i = 0; i < E; ++i) tmp[i] = from_f32<T>(v[i]);
+        for (int i = 0; i < E; i += 2)
+            *reinterpret_cast<__nv_bfloat162*>(&tmp[i]) = __floats2bfloat162_rn(v[i], v[i + 1]);
+    } else {
+#pragma unroll
+        for (int i = 0; i < E; ++i) tmp[i] = from_f32<T>(v[i]);
+    }
     if constexpr (NB == 4) *reinterpret_cast<uint32_t*>(p) = *reinterpret_cast<const uint32_t*>(tmp);
     else if constexpr (NB == 8) *reinterpret_cast<uint2*>(p) = *reinterpret_cast<const uint2*>(tmp);
     else {
 #pragma unroll
         for (int i = 0; i < NB / 16; ++i) reinterpret_cast<uint4*>(p)[i] = reinterpret_cast<const uint4*>(tmp)[i];
     }
+}
+
+// 1 / sqrt(sum of squares / n + eps) of the norms: the hardware's reciprocal square root refined by
+// one Newton step, which leaves it within an ulp or two of the division by the square root.
+__device__ __forceinline__ float inv_rms(float sum_sq, float n, float eps) {
+    const float x = sum_sq / n + eps;
+    const float y = rsqrtf(x);
+    return y * fmaf(-0.5f * x * y, y, 1.5f);
 }
 
 __device__ __forceinline__ float warp_sum(float v) {
