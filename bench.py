@@ -116,13 +116,12 @@ def prefill_flops(cfg, T):
 def fill_cache(engine, slots, n_tokens):
     """Put ``n_tokens`` positions of random keys and values into each slot without running the
     model (what they hold does not change a decode step's time)."""
-    from ultima_b200.kernels import ops
     for s in slots:
         engine.cache.reserve(s, n_tokens)
         engine.cache.commit(s, n_tokens)
 
 
-def timed_decode(engine, sampler, batch, steps, warmup, rng, real_prefill, prompt_len=PROMPT):
+def timed_decode(engine, sampler, batch, steps, warmup, rng, real_prefill, prompt_len=PROMPT, spread=None):
     import torch
     from ultima_b200.sampling import SamplingParams
     V = engine.spec.vocab_size
@@ -154,6 +153,18 @@ def timed_decode(engine, sampler, batch, steps, warmup, rng, real_prefill, promp
     ms = e0.elapsed_time(e1)
     launches = engine.rt.launches - l0 + steps
     ctx = engine.length(slots[0])
+    if spread is not None:
+        # how even the steps are: a few more of them, each between two events of its own
+        n = min(32, steps, toks.shape[0])
+        evs = [torch.cuda.Event(enable_timing=True) for _ in range(n + 1)]
+        evs[0].record()
+        for i in range(n):
+            one(i)
+            evs[i + 1].record()
+        torch.cuda.synchronize()
+        each = sorted(evs[i].elapsed_time(evs[i + 1]) for i in range(n))
+        spread.update({"p10": round(each[n // 10], 4), "median": round(each[n // 2], 4),
+                       "p90": round(each[(9 * n) // 10], 4), "steps": n})
     engine.close(slots)
     return ms, launches, ctx
 
@@ -288,7 +299,9 @@ def run_ours(args):
 
     clocks = ClockSampler()
     clocks.start()
-    ms, launches, ctx = timed_decode(engine, sampler, BATCH, args.steps, args.warmup, rng, real_prefill=True)
+    spread = {}
+    ms, launches, ctx = timed_decode(engine, sampler, BATCH, args.steps, args.warmup, rng, real_prefill=True,
+                                     spread=spread)
     clk = clocks.stop()
     value = BATCH * args.steps / ms * 1e3
     wbytes = weight_bytes(cfg)
@@ -332,7 +345,7 @@ def run_ours(args):
         "e2e": e2e, "gpu_launches": int(launches), "clocks": clk, "prefill": prefill,
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
                      "frac": round(achieved / pk["hbm_gbs"], 4)},
-        "points": points, "impl": "ours",
+        "points": points, "step_ms": spread, "impl": "ours",
     }
     print(json.dumps(out), flush=True)
     return 0

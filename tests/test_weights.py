@@ -144,3 +144,31 @@ def test_sharded_folder_is_read_through_its_index(tmp_path):
         json.dump({"metadata": {}, "weight_map": weight_map}, fh)
     got = load_weights(d, u.model_spec_for(cfg).weight_specs(), torch.float32)
     assert all(torch.equal(got[n], tensors[n]) for n in names)
+
+
+def test_command_line_reports_on_folders_without_a_gpu(tmp_path, capsys):
+    """archinfo, scan and inspect read configuration and file headers only."""
+    import copy
+    import json as _json
+    from conftest import TINY_A, TINY_B
+    from ultima_b200.cli import main
+    good, bad = tmp_path / "zoo" / "good", tmp_path / "zoo" / "bad"
+    u.write_random_model(str(good), u.config_from_dict(copy.deepcopy(TINY_A)), seed=1)
+    u.write_random_model(str(bad), u.config_from_dict(copy.deepcopy(TINY_B)), seed=2)
+    cfg = _json.loads((bad / "config.json").read_text())
+    cfg["intermediate_size"] += 64                       # the files no longer fit the configuration
+    (bad / "config.json").write_text(_json.dumps(cfg))
+    assert main(["archinfo", str(good)]) == 0
+    out = capsys.readouterr().out
+    assert "model.layers.0.self_attn.q_proj.weight" in out and "all" in out and "tensors present" in out
+    assert main(["archinfo", str(bad)]) == 1
+    assert "wrong shape" in capsys.readouterr().out
+    assert main(["scan", str(tmp_path / "zoo")]) == 0
+    out = capsys.readouterr().out
+    lines = [l for l in out.splitlines() if l.strip()]
+    assert len(lines) == 2
+    assert any(l.startswith("runnable") and "good" in l for l in lines)
+    assert any(l.startswith("NOT runnable") and "bad" in l for l in lines)
+    assert main(["inspect", str(good), "q_norm"]) == 0
+    out = capsys.readouterr().out
+    assert "q_norm.weight" in out and "k_norm" not in out and "tensors shown" in out

@@ -5,7 +5,10 @@ request's tokens: ``--prompt "1,2,3"``; several prompts are separated by ``;`` a
 
   ultima --version | --help
   ultima archs                               list known architectures and their status
-  ultima archinfo <model_dir>                configuration and tensors the model asks for
+  ultima archinfo <model_dir>                configuration, the tensors the model asks for, and whether
+                                             the folder's files hold them (names, shapes, types)
+  ultima scan <dir>                          every model folder below <dir>: runnable or why not
+  ultima inspect <model_dir|file> [filter]   what the safetensors files hold: name, type, shape
   ultima random <model_dir> --config C.json [--seed N] [--dtype bfloat16|float32]
                                              write config.json and model.safetensors
   ultima run <model_dir> [--prompt IDS] [--n-predict N] [--n-ctx N] [--temp X] [--seed N]
@@ -51,6 +54,89 @@ def cmd_archinfo(argv) -> int:
         total += n
         print(f"{s.name:56s} {list(s.shape)}")
     print(f"{total} parameters; runs: {[r.layer for r in spec.runs]}")
+    # do the folder's files hold these tensors?  (headers only; the reference's archinfo resolves
+    # every tensor slot the same way, apps/ultima-cli/main.cpp:378-459)
+    import os
+    from .weights import WeightError, check_weights
+    if os.path.isfile(os.path.join(argv[0], "model.safetensors")) or \
+            os.path.isfile(os.path.join(argv[0], "model.safetensors.index.json")):
+        optional = ("lm_head.weight",) if spec.head.get("tied") else ()
+        try:
+            found = check_weights(argv[0], spec.weight_specs(), optional)
+            kinds = sorted({dt for dt, _ in found.values()})
+            print(f"weights: all {len(found)} tensors present with the right shapes (stored as {', '.join(kinds)})")
+        except WeightError as e:
+            print(str(e))
+            return 1
+    else:
+        print("weights: no model.safetensors in this folder")
+    return 0
+
+
+def _runnable(model_dir: str):
+    """(True, summary) or (False, reason) for one folder with a config.json."""
+    from . import ConfigError, config_from_dir, model_spec_for
+    from .weights import SafetensorsError, WeightError, check_weights
+    try:
+        cfg = config_from_dir(model_dir)
+        spec = model_spec_for(cfg)
+        optional = ("lm_head.weight",) if spec.head.get("tied") else ()
+        found = check_weights(model_dir, spec.weight_specs(), optional)
+    except (ConfigError, WeightError, SafetensorsError, OSError, ValueError) as e:
+        return False, str(e).splitlines()[0] if str(e) else type(e).__name__
+    n = 0
+    for _, shape in found.values():
+        k = 1
+        for d in shape:
+            k *= d
+        n += k
+    return True, f"{type(cfg).__name__.replace('Config', '')}, {len(spec.layers)} layers, {n / 1e6:.1f} M parameters"
+
+
+def cmd_scan(argv) -> int:
+    """Every folder below the given one that holds a config.json: runnable by this library, or the
+    first line of why not (the reference's ``scan`` reports the same for a folder of GGUF files,
+    apps/ultima-cli/main.cpp:466-550)."""
+    import os
+    if not argv:
+        print("ultima scan: missing folder", file=sys.stderr)
+        return 2
+    hits = 0
+    for root, dirs, files in os.walk(argv[0]):
+        dirs.sort()
+        if "config.json" in files:
+            hits += 1
+            ok, what = _runnable(root)
+            print(f"{'runnable ' if ok else 'NOT runnable'}  {root}: {what}")
+    if not hits:
+        print(f"no model folder (config.json) below '{argv[0]}'")
+    return 0
+
+
+def cmd_inspect(argv) -> int:
+    """Names, types and shapes in a model folder's safetensors files, optionally only names that
+    contain ``filter`` (the reference's ``--inspect <model> [filter]`` dumps its file's metadata
+    and tensor table, apps/ultima-cli/main.cpp:154-244)."""
+    import os
+    from .weights import read_safetensors_header
+    from .weights.loader import _shard_files
+    if not argv:
+        print("ultima inspect: missing model folder or file", file=sys.stderr)
+        return 2
+    paths = [argv[0]] if os.path.isfile(argv[0]) else _shard_files(argv[0])
+    needle = argv[1] if len(argv) > 1 else ""
+    shown = total = 0
+    for path in paths:
+        header, start, size = read_safetensors_header(path)
+        print(f"{path}: {len(header)} tensors, header {start} bytes, file {size} bytes")
+        for name in sorted(header, key=lambda n: header[n]["data_offsets"][0]):
+            total += 1
+            if needle and needle not in name:
+                continue
+            e = header[name]
+            shown += 1
+            print(f"  {name:56s} {e['dtype']:5s} {list(e['shape'])}")
+    print(f"{shown} of {total} tensors shown")
     return 0
 
 
@@ -141,6 +227,10 @@ def main(argv=None) -> int:
             return cmd_archs()
         if cmd == "archinfo":
             return cmd_archinfo(rest)
+        if cmd == "scan":
+            return cmd_scan(rest)
+        if cmd in ("inspect", "--inspect"):
+            return cmd_inspect(rest)
         if cmd == "random":
             return cmd_random(rest)
         if cmd == "run":

@@ -46,6 +46,49 @@ def _shard_files(model_dir: str) -> list[str]:
     raise WeightError(f"no model.safetensors (or model.safetensors.index.json) in '{model_dir}'")
 
 
+def _fit_error(model_dir, want: dict, where: dict, info, optional: tuple):
+    """The one WeightError that lists everything that does not fit, or None."""
+    missing = [n for n in want if n not in where]
+    unexpected = sorted(n for n in where if n not in want and n not in optional)
+    wrong_shape, wrong_dtype = [], []
+    for n, s in want.items():
+        if n not in where:
+            continue
+        dt, shape = info(n)
+        if tuple(shape) != tuple(s.shape):
+            wrong_shape.append((n, tuple(s.shape), tuple(shape)))
+        if (s.kind == "table") != (dt in _INTS):
+            wrong_dtype.append((n, "integer" if s.kind == "table" else "floating", dt))
+    if not (missing or unexpected or wrong_shape or wrong_dtype):
+        return None
+    lines = [f"weights in '{model_dir}' do not fit the model:"]
+    if missing:
+        lines.append(f"  missing tensors ({len(missing)}): " + ", ".join(missing))
+    if unexpected:
+        lines.append(f"  unexpected tensors ({len(unexpected)}): " + ", ".join(unexpected))
+    for n, exp, got in wrong_shape:
+        lines.append(f"  wrong shape: '{n}' expected {list(exp)}, got {list(got)}")
+    for n, exp, got in wrong_dtype:
+        lines.append(f"  wrong dtype: '{n}' expected a {exp} type, got {got}")
+    return WeightError("\n".join(lines), missing, unexpected, wrong_shape, wrong_dtype)
+
+
+def check_weights(model_dir: str, specs: list[WeightSpec], optional: tuple = ()) -> dict:
+    """Reads the headers only and raises the same WeightError as ``load_weights`` would; returns
+    name -> (file dtype name, shape) of the model's tensors when everything fits."""
+    from .safetensors_io import read_safetensors_header
+    found = {}
+    for path in _shard_files(model_dir):
+        header, _, _ = read_safetensors_header(path)
+        for n, e in header.items():
+            found[n] = (e["dtype"], tuple(int(x) for x in e["shape"]))
+    want = {s.name: s for s in specs}
+    err = _fit_error(model_dir, want, found, lambda n: found[n], optional)
+    if err is not None:
+        raise err
+    return {n: found[n] for n in want}
+
+
 def load_weights(model_dir: str, specs: list[WeightSpec], run_dtype: torch.dtype,
                  device: str | torch.device = "cpu", optional: tuple = ()) -> dict:
     """name -> tensor on ``device``.  ``optional`` names may be present and are then ignored
@@ -57,28 +100,9 @@ def load_weights(model_dir: str, specs: list[WeightSpec], run_dtype: torch.dtype
             for n in f.names():
                 where[n] = f
         want = {s.name: s for s in specs}
-        missing = [n for n in want if n not in where]
-        unexpected = sorted(n for n in where if n not in want and n not in optional)
-        wrong_shape, wrong_dtype = [], []
-        for n, s in want.items():
-            if n not in where:
-                continue
-            dt, shape = where[n].info(n)
-            if tuple(shape) != tuple(s.shape):
-                wrong_shape.append((n, tuple(s.shape), tuple(shape)))
-            if (s.kind == "table") != (dt in _INTS):
-                wrong_dtype.append((n, "integer" if s.kind == "table" else "floating", dt))
-        if missing or unexpected or wrong_shape or wrong_dtype:
-            lines = [f"weights in '{model_dir}' do not fit the model:"]
-            if missing:
-                lines.append(f"  missing tensors ({len(missing)}): " + ", ".join(missing))
-            if unexpected:
-                lines.append(f"  unexpected tensors ({len(unexpected)}): " + ", ".join(unexpected))
-            for n, exp, got in wrong_shape:
-                lines.append(f"  wrong shape: '{n}' expected {list(exp)}, got {list(got)}")
-            for n, exp, got in wrong_dtype:
-                lines.append(f"  wrong dtype: '{n}' expected a {exp} type, got {got}")
-            raise WeightError("\n".join(lines), missing, unexpected, wrong_shape, wrong_dtype)
+        err = _fit_error(model_dir, want, where, lambda n: where[n].info(n), optional)
+        if err is not None:
+            raise err
         out = {}
         for n, s in want.items():
             dt, _ = where[n].info(n)
