@@ -137,3 +137,20 @@ def test_sampling_params_defaults_follow_the_reference():
     assert s.history_window() == 512
     with pytest.raises(ValueError):
         SamplingParams(top_k=-1).validate()
+
+
+def test_penalties_look_back_on_the_prompt_and_then_on_what_was_generated():
+    """The reference pushes the prompt into its sampler's window before the first draw
+    (apps/ultima-cli/main.cpp:664, src/server/http_server.cpp:163)."""
+    import ultima_b200.engine.generate as G
+    eng = FakeEngine()
+    seen_by_sampler = []
+
+    def sample(rows, params, streams, counters, recents):
+        seen_by_sampler.append([list(r) for r in recents])
+        return [50 + c for c in counters]
+    with_history = SamplingParams(rep_penalty=1.3, repeat_last_n=8)
+    plain = SamplingParams()
+    generate(eng, sample, [[1, 2, 3], [4]], [with_history, plain], 3, ())
+    assert [s[0] for s in seen_by_sampler] == [[1, 2, 3], [1, 2, 3, 50], [1, 2, 3, 50, 51]]
+    assert all(s[1] == [] for s in seen_by_sampler)          # no history kept where nothing reads it

@@ -146,3 +146,51 @@ def test_penalties_and_bias_change_the_greedy_choice():
     for p, rec in ((rep, [10, 10, 5]), (fp, [10, 10]), (dry, [10, 10, 10, 7])):
         want, _ = host_ladder(x[0].numpy(), p, rec)
         assert s.sample(x.to(DEV), [p], [1], [len(rec)], [rec]) == [want]
+
+
+@pytest.mark.parametrize("case", ["ties", "far_cut", "deep_top_p", "top_p_after_top_k", "wide_vocab"])
+def test_cuts_on_rows_that_leave_the_fast_search(case):
+    """Rows on which the three-pass search for the cut gives up (long runs of equal values, a cut
+    further than 64 units below the maximum) or must be exact (a cumulative mass right at the
+    boundary, top-p narrowing what top-k kept): the kept set is still the host's."""
+    from ultima_b200.sampling import SamplingParams
+    g = torch.Generator().manual_seed(21)
+    if case == "ties":
+        V = 6000
+        logits = torch.zeros(1, V)
+        logits[0, ::3] = 1.0                                   # 2,000 equal maxima: top-k keeps them all
+        p = SamplingParams(temperature=1.0, top_k=5)
+    elif case == "far_cut":
+        V = 4000
+        logits = torch.randn(1, V, generator=g) * 60           # the 500th largest lies far below the maximum
+        p = SamplingParams(temperature=1.0, top_k=500)
+    elif case == "deep_top_p":
+        V = 9001
+        logits = torch.randn(1, V, generator=g) * 0.05         # nearly flat: top-p keeps almost everything
+        p = SamplingParams(temperature=1.0, top_p=0.97)
+    elif case == "top_p_after_top_k":
+        V = 3000
+        logits = torch.randn(1, V, generator=g) * 2
+        p = SamplingParams(temperature=1.0, top_k=64, top_p=0.5)
+    else:
+        V = 151936
+        logits = torch.randn(1, V, generator=g) * 3
+        p = SamplingParams(temperature=0.6, top_k=50, top_p=0.9, min_p=0.02)
+    s = _sampler(V)
+    pr, _ = host_ladder(logits[0].numpy(), p, [])
+    kept = np.nonzero(pr)[0]
+    n = 600
+    ids = np.array(s.sample(logits.repeat(n, 1).to(DEV), [p] * n, [3] * n, list(range(n))))
+    assert set(ids.tolist()) <= set(kept.tolist()), (case, sorted(set(ids.tolist()) - set(kept.tolist()))[:10])
+    if case == "ties":
+        assert len(kept) == 2000 and len(set(ids.tolist())) > 250          # spread over the tied maxima
+    if case == "far_cut":
+        assert len(kept) == 500
+    if case == "deep_top_p":
+        # the draws follow the kept distribution: low and high halves of the kept set by index
+        # carry about the mass the host gives them
+        half = kept[len(kept) // 2]
+        host_low = pr[:half].sum()
+        assert abs((ids < half).mean() - host_low) < 0.07
+    if len(kept) <= 12:
+        assert set(ids.tolist()) == set(kept.tolist())

@@ -44,15 +44,218 @@ __device__ __forceinline__ int count_if_first(const int* recent, int start, int 
 
 constexpr int ST = 1024;
 
+// Every element of x[0, V) once, as f(index, value): four neighbouring elements a load where the
+// row allows it, several loads in flight.  A thread meets its indices in rising order.
+template <typename F>
+__device__ __forceinline__ void visit(const float* __restrict__ x, int V, int tid, F f) {
+    const int head = min(V, (int)(((16u - (unsigned)((uintptr_t)x & 15u)) & 15u) >> 2));
+    if (tid < head) f(tid, x[tid]);
+    const float4* x4 = reinterpret_cast<const float4*>(x + head);
+    const int n4 = (V - head) >> 2;
+#pragma unroll 4
+    for (int i = tid; i < n4; i += ST) {
+        const float4 v = x4[i];
+        const int b = head + 4 * i;
+        f(b, v.x); f(b + 1, v.y); f(b + 2, v.z); f(b + 3, v.w);
+    }
+    const int t = head + 4 * n4 + tid;
+    if (t < V) f(t, x[t]);
+}
+
+// ---------------------------------------------------------------------------------------
+// Where to cut: the largest key t such that the kept elements with key >= t weigh at least
+// ``need`` (weight 1 each for top-k, exp(x - max) for top-p, the latter as a 64-bit fixed-point
+// integer so that a sum does not depend on the order of its terms).  Instead of 32 passes over
+// the row (one a bit of the key) it takes three: a histogram of 1024 buckets over the 64 logit
+// units below the maximum, a histogram of 1024 parts of the bucket that holds the cut, then the
+// elements of that part (a handful) are copied to shared memory and ranked there.  The histograms
+// only say where to look (counts are exact; masses are float sums in arrival order); the pass that
+// copies the elements also sums, exactly, what lies above them, and the ranking is exact.  A row
+// that does not fit (the cut lies further than 64 units below the maximum, more than LIST elements
+// share the last part, or the float sums pointed one part off) takes the bit-by-bit search, which
+// answers the same question with the same integers, so both ways give the same cut.
+// ---------------------------------------------------------------------------------------
+constexpr int NB = 1024;
+constexpr int LIST = 2048;
+constexpr float BUCKET_SCALE = (float)NB / 64.0f;
+constexpr float FIXED_ONE = 1099511627776.0f;              // 2^40
+typedef unsigned long long u64;
+
+struct SelectSmem {
+    union { float f[NB]; unsigned u[NB]; } hist;
+    union { float f[32]; unsigned u[32]; } warp_tot;
+    u64 red64[33];
+    float list_v[LIST];
+    u64 list_w[LIST];
+    float found_above_f;
+    unsigned found_above_u;
+    int found_bucket, count;
+    unsigned best;
+};
+
+template <bool MASS>
+__device__ __forceinline__ u64 weight_of(float v, float m) {
+    if (!MASS) return 1ull;
+    const float d = __fsub_rn(v, m);
+    return d < -28.0f ? 0ull : (u64)__fmul_rn(expf(d), FIXED_ONE);       // below that the product is under one anyway
+}
+// bucket (0: at the maximum) and part of the bucket of a value; both fall as the value rises
+__device__ __forceinline__ void place_of(float v, float m, int& bucket, int& part) {
+    // single operations, never fused with what comes before: every pass must place a value alike
+    const float d = __fmul_rn(__fsub_rn(m, v), BUCKET_SCALE);
+    if (!(d < (float)(NB - 1))) { bucket = NB - 1; part = NB - 1; return; }
+    bucket = d > 0.f ? (int)d : 0;
+    const float f = __fmul_rn(__fsub_rn(d, (float)bucket), (float)NB);
+    part = f > 0.f ? min(NB - 1, (int)f) : 0;
+}
+
+__device__ __forceinline__ u64 block_sum_u64(u64 v, u64* red, int tid) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    __syncthreads();
+    if ((tid & 31) == 0) red[tid >> 5] = v;
+    __syncthreads();
+    if (tid == 0) {
+        u64 t = 0;
+        for (int w = 0; w < ST / 32; ++w) t += red[w];
+        red[32] = t;
+    }
+    __syncthreads();
+    return red[32];
+}
+
+__device__ __forceinline__ void note_above(SelectSmem& sm, float v) { sm.found_above_f = v; }
+__device__ __forceinline__ void note_above(SelectSmem& sm, unsigned v) { sm.found_above_u = v; }
+
+// The first bucket b with hist[0] + ... + hist[b] >= need (thread b holds hist[b]); its index and
+// the sum before it go to shared memory.  found_bucket stays -1 when the whole sum is too small.
+template <typename T>
+__device__ __forceinline__ void first_reaching(SelectSmem& sm, T* hist, T* warp_tot, T need, int tid) {
+    const int lane = tid & 31, warp = tid >> 5;
+    const T own = hist[tid];
+    T incl = own;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const T up = __shfl_up_sync(0xffffffffu, incl, o);
+        if (lane >= o) incl += up;
+    }
+    if (lane == 31) warp_tot[warp] = incl;
+    if (tid == 0) sm.found_bucket = -1;
+    __syncthreads();
+    T before = 0;
+    for (int w = 0; w < warp; ++w) before += warp_tot[w];
+    incl += before;
+    if (incl >= need && incl - own < need) {
+        sm.found_bucket = tid;
+        note_above(sm, (T)(incl - own));
+    }
+    __syncthreads();
+}
+
+template <bool MASS>
+__device__ bool select_cut(const float* x, float sc, int V, float m, unsigned old_cut, u64 need, SelectSmem& sm,
+                           int tid, unsigned& cut_out) {
+    static_assert(NB == ST, "one thread a bucket");
+    // buckets (what lies further than the last bucket below the maximum is not counted: a cut that far
+    // down is not found here)
+    sm.hist.u[tid] = 0;
+    __syncthreads();
+    visit(x, V, tid, [&](int, float raw) {
+        const float v = __fmul_rn(raw, sc);
+        if (key_of(v) < old_cut) return;
+        int b, part;
+        place_of(v, m, b, part);
+        if (b < NB - 1) {
+            if (MASS) atomicAdd(&sm.hist.f[b], expf(__fsub_rn(v, m)));
+            else atomicAdd(&sm.hist.u[b], 1u);
+        }
+    });
+    __syncthreads();
+    const float need_f = (float)need * (1.0f / FIXED_ONE);
+    if (MASS) first_reaching<float>(sm, sm.hist.f, sm.warp_tot.f, need_f, tid);
+    else first_reaching<unsigned>(sm, sm.hist.u, sm.warp_tot.u, (unsigned)need, tid);
+    const int b1 = sm.found_bucket;
+    const float above1_f = sm.found_above_f;
+    const unsigned above1_u = sm.found_above_u;
+    if (b1 < 0) return false;
+    // parts of that bucket
+    __syncthreads();
+    sm.hist.u[tid] = 0;
+    __syncthreads();
+    visit(x, V, tid, [&](int, float raw) {
+        const float v = __fmul_rn(raw, sc);
+        if (key_of(v) < old_cut) return;
+        int b, part;
+        place_of(v, m, b, part);
+        if (b == b1) {
+            if (MASS) atomicAdd(&sm.hist.f[part], expf(__fsub_rn(v, m)));
+            else atomicAdd(&sm.hist.u[part], 1u);
+        }
+    });
+    __syncthreads();
+    if (MASS) first_reaching<float>(sm, sm.hist.f, sm.warp_tot.f, fmaxf(need_f - above1_f, 1e-30f), tid);
+    else first_reaching<unsigned>(sm, sm.hist.u, sm.warp_tot.u, (unsigned)need - above1_u, tid);
+    const int b2 = sm.found_bucket;
+    if (b2 < 0) return false;
+    // the elements of that part, and the exact weight of everything above it
+    if (tid == 0) { sm.count = 0; sm.best = 0; }
+    __syncthreads();
+    u64 above_l = 0;
+    visit(x, V, tid, [&](int, float raw) {
+        const float v = __fmul_rn(raw, sc);
+        if (key_of(v) < old_cut) return;
+        int b, part;
+        place_of(v, m, b, part);
+        if (b < b1 || (b == b1 && part < b2)) above_l += weight_of<MASS>(v, m);
+        else if (b == b1 && part == b2) {
+            const int at = atomicAdd(&sm.count, 1);
+            if (at < LIST) { sm.list_v[at] = v; sm.list_w[at] = weight_of<MASS>(v, m); }
+        }
+    });
+    const u64 above = block_sum_u64(above_l, sm.red64, tid);
+    const int n = sm.count;
+    if (n > LIST || above >= need) return false;
+    // the element with the largest key whose own weight and that of all larger ones reach the need
+    const u64 left = need - above;
+    for (int e = tid; e < n; e += ST) {
+        const unsigned ke = key_of(sm.list_v[e]);
+        u64 sum = 0;
+        for (int j = 0; j < n; ++j) sum += key_of(sm.list_v[j]) >= ke ? sm.list_w[j] : 0ull;
+        if (sum >= left) atomicMax(&sm.best, ke);
+    }
+    __syncthreads();
+    cut_out = sm.best;
+    return sm.best != 0;
+}
+
+// The same cut, one bit of the key a pass over the row.
+template <bool MASS>
+__device__ unsigned search_cut(const float* x, float sc, int V, float m, unsigned old_cut, u64 need, SelectSmem& sm,
+                               int tid) {
+    unsigned t = 0;
+    for (int bit = 31; bit >= 0; --bit) {
+        const unsigned cand = t | (1u << bit);
+        u64 sum = 0;
+        visit(x, V, tid, [&](int, float raw) {
+            const float v = __fmul_rn(raw, sc);
+            const unsigned k = key_of(v);
+            if (k >= cand && k >= old_cut) sum += weight_of<MASS>(v, m);
+        });
+        if (block_sum_u64(sum, sm.red64, tid) >= need) t = cand;
+    }
+    return t;
+}
+
 __global__ void __launch_bounds__(ST)
 sample_kernel(const float* __restrict__ logits, long long ld, float* __restrict__ work, int V,
               const SampleParams* __restrict__ params, const int* __restrict__ recent_all,
               const int* __restrict__ bias_ids, const float* __restrict__ bias_vals,
               int* __restrict__ out_ids, unsigned long long counter_add) {
     __shared__ float red[33];
-    __shared__ float seg[ST];
+    __shared__ float seg[34];
     __shared__ int best_idx_s[32];
     __shared__ float best_val_s[32];
+    __shared__ SelectSmem sel;
     const int row = blockIdx.x, tid = threadIdx.x;
     const SampleParams p = params[row];
     const float* src = logits + (long long)row * ld;
@@ -60,8 +263,8 @@ sample_kernel(const float* __restrict__ logits, long long ld, float* __restrict_
     const bool greedy = !(p.temperature > 0.f);
     const bool plain = p.n_bias == 0 && p.n_recent == 0;
     const float* x = src;
-    if (!(greedy && plain)) {
-        for (int i = tid; i < V; i += ST) w[i] = src[i];
+    if (!plain) {
+        visit(src, V, tid, [&](int i, float v) { w[i] = v; });
         __syncthreads();
         // 1. bias
         for (int i = tid; i < p.n_bias; i += ST) {
@@ -115,10 +318,9 @@ sample_kernel(const float* __restrict__ logits, long long ld, float* __restrict_
     // maximum and its first index
     float bv = -INFINITY;
     int bi = 0x7fffffff;
-    for (int i = tid; i < V; i += ST) {
-        const float v = x[i];
-        if (v > bv) { bv = v; bi = i; }            // strided: a thread's first hit is its lowest index
-    }
+    visit(x, V, tid, [&](int i, float v) {
+        if (v > bv) { bv = v; bi = i; }            // indices rise: a thread's first hit is its lowest index
+    });
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) {
         const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
@@ -142,80 +344,87 @@ sample_kernel(const float* __restrict__ logits, long long ld, float* __restrict_
     const int imax = best_idx_s[0];
     if (greedy) { if (tid == 0) out_ids[row] = imax == 0x7fffffff ? 0 : imax; return; }
 
-    // 5. temperature (in place); from here on the maximum is vmax / T
-    const float invT = 1.0f / p.temperature;
-    if (p.temperature != 1.0f) {
-        for (int i = tid; i < V; i += ST) w[i] *= invT;
-        __syncthreads();
-    }
-    const float m = p.temperature != 1.0f ? vmax * invT : vmax;
+    // 5. temperature: every later read takes x[i] * sc; the maximum is vmax * sc
+    const float sc = p.temperature != 1.0f ? 1.0f / p.temperature : 1.0f;
+    const float m = vmax * sc;
     unsigned cut = 0;                             // keep keys >= cut
     // 6. top-k: the largest cut that still keeps k elements
     if (p.top_k > 0 && p.top_k < V) {
         unsigned t = 0;
-        for (int bit = 31; bit >= 0; --bit) {
-            const unsigned cand = t | (1u << bit);
-            float cnt = 0.f;
-            for (int i = tid; i < V; i += ST) cnt += key_of(w[i]) >= cand ? 1.f : 0.f;
-            cnt = block_sum(cnt, red);
-            if (cnt >= (float)p.top_k) t = cand;
-        }
+        if (!select_cut<false>(x, sc, V, m, 0u, (u64)p.top_k, sel, tid, t))
+            t = search_cut<false>(x, sc, V, m, 0u, (u64)p.top_k, sel, tid);
         cut = t;
     }
     // 7. top-p: the largest cut whose kept mass reaches p of the mass kept so far
     if (p.top_p < 1.0f && p.top_p > 0.f) {
-        float z = 0.f;
-        for (int i = tid; i < V; i += ST) z += key_of(w[i]) >= cut ? expf(w[i] - m) : 0.f;
-        z = block_sum(z, red);
-        const float need = p.top_p * z;
+        u64 zl = 0;
+        visit(x, V, tid, [&](int, float raw) {
+            const float v = __fmul_rn(raw, sc);
+            zl += key_of(v) >= cut ? weight_of<true>(v, m) : 0ull;
+        });
+        const u64 zi = block_sum_u64(zl, sel.red64, tid);
+        u64 need_i = (u64)((double)p.top_p * (double)zi);
+        if (need_i < 1) need_i = 1;
         unsigned t = cut;
-        for (int bit = 31; bit >= 0; --bit) {
-            if (t & (1u << bit)) continue;
-            const unsigned cand = t | (1u << bit);
-            float mass = 0.f;
-            for (int i = tid; i < V; i += ST) mass += key_of(w[i]) >= cand ? expf(w[i] - m) : 0.f;
-            mass = block_sum(mass, red);
-            if (mass >= need) t = cand;
-        }
-        cut = t;
+        if (!select_cut<true>(x, sc, V, m, cut, need_i, sel, tid, t))
+            t = search_cut<true>(x, sc, V, m, cut, need_i, sel, tid);
+        cut = t > cut ? t : cut;
     }
     // 8. min-p: drop p_i < min_p * p_max, i.e. exp(x_i - m) < min_p
     const float minp = p.min_p > 0.f ? p.min_p : 0.f;
-    // 9. draw: inverse CDF in index order; thread t owns one contiguous stretch
-    const int per = (V + ST - 1) / ST;
-    const int b = tid * per, e = min(V, b + per);
+    // 9. draw: inverse CDF in index order.  Warp w owns the stretch [w * C, (w + 1) * C) and reads it
+    // row by row of 32 neighbours; the warp that holds the target walks its stretch once more.
+    const int lane = tid & 31, warp = tid >> 5;
+    const int C = (((V + 31) / 32 + 31) / 32) * 32;           // a stretch: whole rows
+    const int c0 = warp * C, c1 = min(V, c0 + C);
+    auto kept = [&](int i) -> float {
+        const float v = __fmul_rn(x[i], sc);
+        // what was cut away, and what is too small for a float that is not denormal, needs no exp
+        const float d = __fsub_rn(v, m);
+        if (key_of(v) < cut || d < -87.0f) return 0.f;
+        const float pe = expf(d);
+        return pe >= minp ? pe : 0.f;
+    };
     float local = 0.f;
-    for (int i = b; i < e; ++i) {
-        const float v = w[i];
-        const float pe = expf(v - m);
-        local += (key_of(v) >= cut && pe >= minp) ? pe : 0.f;
-    }
-    seg[tid] = local;
+#pragma unroll 4
+    for (int i = c0 + lane; i < c1; i += 32) local += kept(i);
+    local = warp_sum(local);
+    if (lane == 0) seg[warp] = local;
     __syncthreads();
-    if (tid == 0) {                               // exclusive prefix, in order
+    if (tid == 0) {                               // exclusive prefix over the stretches, in order
         float run = 0.f;
-        for (int i = 0; i < ST; ++i) { const float s = seg[i]; seg[i] = run; run += s; }
-        red[0] = run;
+        for (int i = 0; i < 32; ++i) { const float t = seg[i]; seg[i] = run; run += t; }
+        seg[32] = run;
         const unsigned long long r = mix64s(p.seed ^ mix64s(p.counter + counter_add + 0x632BE59BD9B4E019ull));
         red[1] = (float)(unsigned)(r >> 40) * (1.0f / 16777216.0f);
         best_idx_s[1] = imax;                     // fallback: the maximum
     }
     __syncthreads();
-    const float total = red[0];
+    const float total = seg[32];
     const float target = red[1] * total;
-    const float before = seg[tid];
-    const float after = tid + 1 < ST ? seg[tid + 1] : total;
-    // the owner of the target: before <= target < after (the last non-empty stretch takes the end)
-    if (e > b && target >= before && (target < after)) {
+    const float before = seg[warp];
+    const float after = seg[warp + 1];
+    // the owner of the target: before <= target < after (rounding may leave the very end to nobody:
+    // the maximum stands in)
+    if (c1 > c0 && target >= before && target < after) {
         float run = before;
         int pick = -1;
-        for (int i = b; i < e; ++i) {
-            const float v = w[i];
-            const float pe = expf(v - m);
-            const float pr = (key_of(v) >= cut && pe >= minp) ? pe : 0.f;
-            if (pr > 0.f) { run += pr; if (target < run) { pick = i; break; } pick = i; }
+        for (int r0 = c0; r0 < c1; r0 += 32) {
+            const int i = r0 + lane;
+            const float pr = i < c1 ? kept(i) : 0.f;
+            float incl = pr;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const float up = __shfl_up_sync(0xffffffffu, incl, o);
+                if (lane >= o) incl += up;
+            }
+            const unsigned has = __ballot_sync(0xffffffffu, pr > 0.f);
+            const unsigned hit = __ballot_sync(0xffffffffu, pr > 0.f && target < run + incl);
+            if (hit) { pick = r0 + __ffs(hit) - 1; break; }
+            if (has) pick = r0 + 31 - __clz(has);          // the last kept element so far
+            run += __shfl_sync(0xffffffffu, incl, 31);
         }
-        if (pick >= 0) best_idx_s[1] = pick;
+        if (lane == 0 && pick >= 0) best_idx_s[1] = pick;
     }
     __syncthreads();
     if (tid == 0) out_ids[row] = best_idx_s[1];
@@ -234,3 +443,4 @@ UB_API int ub_sample(const float* logits, long long ld, float* work, int n_rows,
     return 0;
 }
 UB_API int ub_sample_params_size() { return (int)sizeof(SampleParams); }
+

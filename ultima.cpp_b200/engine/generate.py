@@ -70,6 +70,10 @@ def run_batch(engine, sample, prompts: list, params: list, n_predict: list, stop
         if len(p) + n_predict[i] > max_context:
             raise ValueError(f"request {i}: prompt of {len(p)} plus {n_predict[i]} new tokens "
                              f"does not fit the context of {max_context}")
+    # what the penalties look back on: the prompt, then what was generated (the reference pushes the
+    # prompt's tokens into its sampler's window before the first draw, apps/ultima-cli/main.cpp:664,
+    # src/server/http_server.cpp:163); built only for requests whose parameters read it
+    seen = [list(p) if params[i].uses_history else [] for i, p in enumerate(prompts)]
     slots = engine.open(n)
     held = set(range(n))
     try:
@@ -88,7 +92,7 @@ def run_batch(engine, sample, prompts: list, params: list, n_predict: list, stop
         first = True
         while live:
             ids = sample(logits, [params[i] for i in live], [streams[i] for i in live],
-                         [len(out[i].tokens) for i in live], [out[i].tokens for i in live])
+                         [len(out[i].tokens) for i in live], [seen[i] for i in live])
             now = time.perf_counter()
             if stats:
                 if first:
@@ -101,6 +105,8 @@ def run_batch(engine, sample, prompts: list, params: list, n_predict: list, stop
             going, feed = [], []
             for i, tok in zip(live, ids):
                 tok = int(tok)
+                if params[i].uses_history:
+                    seen[i].append(tok)
                 if tok in stop:
                     out[i].finish_reason = "stop"
                 elif len(out[i].tokens) + 1 >= n_predict[i]:
