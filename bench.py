@@ -209,6 +209,52 @@ def decode_timeline(engine, batch, prompt_len, rng):
     return 0
 
 
+def sampling_times(batches=(1, 8, 64), vocab=151936, history=256):
+    """Device time of the sampling kernel alone at the 8B vocabulary, for the reference's ladder
+    of options (src/sampler/sampler.cpp:230-277): one JSON line a batch size, microseconds a call.
+    Rows use rings of recent tokens on the device as the generation loop does."""
+    import dataclasses
+    import numpy as np
+    import torch
+    from ultima_b200.engine import Runtime
+    from ultima_b200.kernels import ops
+    from ultima_b200.sampling import Sampler, SamplingParams
+    dev = torch.device("cuda:0")
+    rt = Runtime(dev, torch.bfloat16)
+    server = SamplingParams.server_defaults()
+    modes = [("greedy", SamplingParams()), ("temperature", SamplingParams(temperature=0.8)),
+             ("top_k 40", SamplingParams(temperature=0.8, top_k=40)),
+             ("top_p 0.9", SamplingParams(temperature=0.8, top_p=0.9)),
+             ("min_p 0.05", SamplingParams(temperature=0.8, min_p=0.05)),
+             ("greedy + repetition penalty", SamplingParams(rep_penalty=1.1, repeat_last_n=64)),
+             ("server defaults without penalties", dataclasses.replace(server, rep_penalty=1.0, dry_multiplier=0.0)),
+             ("server defaults", server)]
+    rng = np.random.default_rng(0)
+    for B in batches:
+        logits = torch.randn(B, vocab, device=dev) * 3
+        row = {"only": "sample", "batch": B, "vocab": vocab, "unit": "us a call, kernel only"}
+        for name, sp in modes:
+            smp = Sampler(dev, vocab, rt)
+            hs = [rng.integers(0, vocab, size=history).tolist() for _ in range(B)]
+            for step in range(3):                    # as the loop does: the drawn token joins the history
+                ids = smp.sample(logits, [sp] * B, list(range(B)), [step] * B, hs)
+                for h, t in zip(hs, ids):
+                    h.append(t)
+            _, _, _, rec_dev, bid, bval, _ = smp._cache
+            out = torch.empty(B, dtype=torch.int32, device=dev)
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize()
+            e0.record()
+            for i in range(20):
+                ops.sample(logits, smp._work, rec_dev, smp._dummy_i, bid if bid is not None else smp._dummy_i,
+                           bval if bval is not None else smp._dummy_f, out, 3 + i, smp._hist, smp._hist_len)
+            e1.record()
+            torch.cuda.synchronize()
+            row[name] = round(e0.elapsed_time(e1) / 20 * 1e3, 1)
+        print(json.dumps(row))
+    return 0
+
+
 def sampler_params(sampler, params, device):
     """Records of greedy sampling for ``len(params)`` rows, on the device."""
     import numpy as np
@@ -444,9 +490,10 @@ def main():
     ap.add_argument("--warmup", type=int, default=4)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--layers", type=int, default=0, help="fewer layers than the configuration (named in config)")
-    ap.add_argument("--only", default="all", choices=["all", "prefill", "decode", "timeline"],
+    ap.add_argument("--only", default="all", choices=["all", "prefill", "decode", "timeline", "sample"],
                     help="a part of the run only (for profiling); the JSON line then holds that part. "
-                         "timeline: every kernel of a decode step with its begin and end inside the graph")
+                         "timeline: every kernel of a decode step with its begin and end inside the graph; "
+                         "sample: the sampling kernel alone, option by option")
     ap.add_argument("--batch", type=int, default=BATCH, help="sequences of the decode step")
     ap.add_argument("--fast-fill", action="store_true", help="do not run the prompts; mark the cache as filled")
     ap.add_argument("--prompt", type=int, default=PROMPT, help="positions each sequence holds before the timed steps")
@@ -462,6 +509,8 @@ def main():
     args.steps_given = args.steps is not None
     if args.steps is None:
         args.steps = 64
+    if args.only == "sample":
+        return sampling_times()
     if args.config != "8b":
         return run_other(args)
     return run_ours(args)

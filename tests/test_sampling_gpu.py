@@ -194,3 +194,35 @@ def test_cuts_on_rows_that_leave_the_fast_search(case):
         assert abs((ids < half).mean() - host_low) < 0.07
     if len(kept) <= 12:
         assert set(ids.tolist()) == set(kept.tolist())
+
+
+def test_history_kept_on_the_device_follows_what_the_caller_holds():
+    """The rings of recent tokens on the device give the same choices as sending the history with
+    every call: a sequence that goes on (the kernel appends what it samples), a history that was
+    edited behind the sampler's back, a new sequence under an old stream number, a long history
+    that wraps the ring."""
+    from ultima_b200.sampling import SamplingParams
+    V = 400
+    g = torch.Generator().manual_seed(3)
+    logits = (torch.randn(3, V, generator=g) * 0.3).to(DEV)
+    p = SamplingParams(rep_penalty=1.5, repeat_last_n=48, frequency_penalty=0.2, presence_penalty=0.1)
+    s = _sampler(V)
+
+    def fresh_choice(rows, hists):
+        """What a sampler that has never seen these streams chooses."""
+        return _sampler(V).sample(logits[rows], [p] * len(rows), [100 + r for r in rows], [0] * len(rows),
+                                  [list(h) for h in hists])
+    hists = [[1, 2, 3], [4], list(range(200, 330))]            # the third is longer than the ring
+    streams = [11, 12, 13]
+    for step in range(70):                                     # greedy with penalties never repeats for long
+        got = s.sample(logits, [p] * 3, streams, [step] * 3, hists)
+        assert got == fresh_choice([0, 1, 2], hists), step
+        for h, t in zip(hists, got):
+            h.append(t)
+    # an edited history of the same length, and a new sequence under an old stream
+    hists[0][-1] = (hists[0][-1] + 1) % V
+    got = s.sample(logits, [p] * 3, streams, [70] * 3, hists)
+    assert got == fresh_choice([0, 1, 2], hists)
+    new = [[7, 7, 7, 8], [9]]
+    got = s.sample(logits[:2], [p] * 2, streams[:2], [0, 0], new)
+    assert got == fresh_choice([0, 1], new)

@@ -33,21 +33,48 @@ __device__ __forceinline__ unsigned long long mix64s(unsigned long long z) {
     return z ^ (z >> 31);
 }
 
+// The recent tokens of a row, oldest first: a stretch of a flat array that the host sent with the
+// call, or the last tokens of a ring that stays on the device and that the kernel itself appends
+// each sampled token to (cap > 0: element j lies at (first + j) mod cap).
+struct Window {
+    const int* base;
+    int first, cap;
+    __device__ __forceinline__ int operator[](int j) const {
+        const int k = first + j;
+        return base[cap > 0 ? k % cap : k];
+    }
+};
+
 // Occurrences of recent[i] inside [start, end), or 0 when an earlier index holds the same id.
-__device__ __forceinline__ int count_if_first(const int* recent, int start, int end, int i) {
+// One loop without branches: every thread of a warp reads the same element at the same time.
+__device__ __forceinline__ int count_if_first(const Window& recent, int start, int end, int i) {
     const int id = recent[i];
-    for (int j = start; j < i; ++j) if (recent[j] == id) return 0;
-    int n = 1;
-    for (int j = i + 1; j < end; ++j) n += recent[j] == id;
-    return n;
+    int n = 0, earlier = 0;
+    if (recent.cap == 0) {
+        const int* r = recent.base + recent.first;
+#pragma unroll 8
+        for (int j = start; j < end; ++j) {
+            const int same = r[j] == id;
+            n += same;
+            earlier |= same & (j < i);
+        }
+    } else {
+        for (int j = start; j < end; ++j) {
+            const int same = recent[j] == id;
+            n += same;
+            earlier |= same & (j < i);
+        }
+    }
+    return earlier ? 0 : n;
 }
 
 constexpr int ST = 1024;
+constexpr int WIN_SMEM = 1024;            // recent tokens of a row that are held in shared memory
 
 // Every element of x[0, V) once, as f(index, value): four neighbouring elements a load where the
 // row allows it, several loads in flight.  A thread meets its indices in rising order.
 template <typename F>
-__device__ __forceinline__ void visit(const float* __restrict__ x, int V, int tid, F f) {
+__device__ __forceinline__ void visit(const float* x, int V, int tid, F f) {
     const int head = min(V, (int)(((16u - (unsigned)((uintptr_t)x & 15u)) & 15u) >> 2));
     if (tid < head) f(tid, x[tid]);
     const float4* x4 = reinterpret_cast<const float4*>(x + head);
@@ -250,18 +277,24 @@ __global__ void __launch_bounds__(ST)
 sample_kernel(const float* __restrict__ logits, long long ld, float* __restrict__ work, int V,
               const SampleParams* __restrict__ params, const int* __restrict__ recent_all,
               const int* __restrict__ bias_ids, const float* __restrict__ bias_vals,
-              int* __restrict__ out_ids, unsigned long long counter_add) {
+              int* __restrict__ out_ids, unsigned long long counter_add, int* __restrict__ hist,
+              int* __restrict__ hist_len, int hist_cap) {
     __shared__ float red[33];
     __shared__ float seg[34];
     __shared__ int best_idx_s[32];
     __shared__ float best_val_s[32];
     __shared__ SelectSmem sel;
+    __shared__ int win_s[WIN_SMEM];
     const int row = blockIdx.x, tid = threadIdx.x;
     const SampleParams p = params[row];
     const float* src = logits + (long long)row * ld;
     float* w = work + (long long)row * V;
     const bool greedy = !(p.temperature > 0.f);
     const bool plain = p.n_bias == 0 && p.n_recent == 0;
+    // n_recent < 0: the row's history is ring number recent_offset on the device
+    const bool ring = p.n_recent < 0 && hist != nullptr && hist_cap > 0;
+    const int n_total = ring ? hist_len[p.recent_offset] : 0;
+    int* my_ring = ring ? hist + (long long)p.recent_offset * hist_cap : nullptr;
     const float* x = src;
     if (!plain) {
         visit(src, V, tid, [&](int i, float v) { w[i] = v; });
@@ -272,8 +305,14 @@ sample_kernel(const float* __restrict__ logits, long long ld, float* __restrict_
             if (id >= 0 && id < V) atomicAdd(&w[id], bias_vals[p.bias_offset + i]);
         }
         __syncthreads();
-        const int* recent = recent_all + p.recent_offset;
-        const int nr = p.n_recent;
+        const int nr = ring ? min(n_total, hist_cap) : max(p.n_recent, 0);
+        Window recent = ring ? Window{my_ring, (n_total - nr) % hist_cap, hist_cap}
+                             : Window{recent_all + p.recent_offset, 0, 0};
+        if (nr <= WIN_SMEM) {                     // the usual case: the window is read from shared memory
+            for (int j = tid; j < nr; j += ST) win_s[j] = recent[j];
+            __syncthreads();
+            recent = Window{win_s, 0, 0};
+        }
         // 2. repetition penalty
         if (p.rep_penalty != 1.0f && p.repeat_last_n > 0 && nr > 0) {
             const int start = max(0, nr - p.repeat_last_n);
@@ -296,7 +335,7 @@ sample_kernel(const float* __restrict__ logits, long long ld, float* __restrict_
                     if (id < 0 || id >= V) continue;
                     const int n = count_if_first(recent, start, nr, i);
                     if (n > p.dry_allowed_len)
-                        w[id] -= p.dry_multiplier * powf(p.dry_base, (float)(n - p.dry_allowed_len));
+                        w[id] -= p.dry_multiplier * exp2f(log2f(p.dry_base) * (float)(n - p.dry_allowed_len));
                 }
             }
             __syncthreads();
@@ -342,7 +381,14 @@ sample_kernel(const float* __restrict__ logits, long long ld, float* __restrict_
     __syncthreads();
     const float vmax = best_val_s[0];
     const int imax = best_idx_s[0];
-    if (greedy) { if (tid == 0) out_ids[row] = imax == 0x7fffffff ? 0 : imax; return; }
+    if (greedy) {
+        if (tid == 0) {
+            const int id = imax == 0x7fffffff ? 0 : imax;
+            out_ids[row] = id;
+            if (ring) { my_ring[n_total % hist_cap] = id; hist_len[p.recent_offset] = n_total + 1; }
+        }
+        return;
+    }
 
     // 5. temperature: every later read takes x[i] * sc; the maximum is vmax * sc
     const float sc = p.temperature != 1.0f ? 1.0f / p.temperature : 1.0f;
@@ -427,20 +473,26 @@ sample_kernel(const float* __restrict__ logits, long long ld, float* __restrict_
         if (lane == 0 && pick >= 0) best_idx_s[1] = pick;
     }
     __syncthreads();
-    if (tid == 0) out_ids[row] = best_idx_s[1];
+    if (tid == 0) {
+        const int id = best_idx_s[1];
+        out_ids[row] = id;
+        if (ring) { my_ring[n_total % hist_cap] = id; hist_len[p.recent_offset] = n_total + 1; }
+    }
 }
 
 // ``counter_add`` is added to every row's counter (a batch whose rows have drawn equally often can
-// keep its records on the device and pass the count here).
+// keep its records on the device and pass the count here).  A row whose record has n_recent < 0
+// takes its recent tokens from ring number recent_offset of ``hist`` ([rings, hist_cap] int32, with
+// ``hist_len`` tokens put into it so far) and appends the token it samples.
 UB_API int ub_sample(const float* logits, long long ld, float* work, int n_rows, int V,
                      const void* params, const int* recent, const int* bias_ids, const float* bias_vals,
-                     int* out_ids, unsigned long long counter_add, cudaStream_t st) {
+                     int* out_ids, unsigned long long counter_add, int* hist, int* hist_len, int hist_cap,
+                     cudaStream_t st) {
     if (n_rows <= 0) return 0;
-    if (V <= 0) return UB_ERR_ARG;
+    if (V <= 0 || hist_cap < 0 || (hist_cap > 0 && (!hist || !hist_len))) return UB_ERR_ARG;
     sample_kernel<<<n_rows, ST, 0, st>>>(logits, ld, work, V, (const SampleParams*)params, recent,
-                                         bias_ids, bias_vals, out_ids, counter_add);
+                                         bias_ids, bias_vals, out_ids, counter_add, hist, hist_len, hist_cap);
     UB_LAUNCH_CHECK();
     return 0;
 }
 UB_API int ub_sample_params_size() { return (int)sizeof(SampleParams); }
-

@@ -78,7 +78,7 @@ def _declare(lib, source: str) -> None:
         },
         "gemm_simt.cu": {"ub_gemm_simt": [P, I, P, P, I, P, I, I, I, I, L, L, L, I, P]},
         "attn_simple.cu": {"ub_attn_simple": [P, L, I, P, P, I, P, L, P, P, P, I, I, I, I, I, I, I, I, F, P]},
-        "sampling.cu": {"ub_sample": [P, L, P, I, I, P, P, P, P, P, U, P], "ub_sample_params_size": []},
+        "sampling.cu": {"ub_sample": [P, L, P, I, I, P, P, P, P, P, U, P, P, I, P], "ub_sample_params_size": []},
     }.get(source, {})
     for name, args in sigs.items():
         fn = getattr(lib, name)
@@ -218,9 +218,12 @@ SAMPLE_DTYPE = np.dtype([
     ("bias_offset", "<i4"), ("seed", "<u8"), ("counter", "<u8")])
 
 
-def sample(logits, work, params_dev, recent, bias_ids, bias_vals, out_ids, counter_add: int = 0):
+def sample(logits, work, params_dev, recent, bias_ids, bias_vals, out_ids, counter_add: int = 0,
+           hist=None, hist_len=None):
     """One token id for each row of float32 ``logits``; ``params_dev`` holds one record of
-    SAMPLE_DTYPE a row (as bytes on the device); ``counter_add`` is added to every row's counter."""
+    SAMPLE_DTYPE a row (as bytes on the device); ``counter_add`` is added to every row's counter.
+    ``hist`` [rings, capacity] int32 and ``hist_len`` [rings] int32: rings of recent tokens that stay on
+    the device; a row whose record has n_recent < 0 reads ring ``recent_offset`` and appends its token."""
     _need_cuda(logits, work, params_dev, out_ids)
     lib = _lib("sampling.cu")
     assert lib.ub_sample_params_size() == SAMPLE_DTYPE.itemsize
@@ -228,6 +231,12 @@ def sample(logits, work, params_dev, recent, bias_ids, bias_vals, out_ids, count
     assert logits.dtype == torch.float32 and logits.stride(1) == 1
     assert work is None or (work.dtype == torch.float32 and work.is_contiguous() and work.numel() >= n * V)
     assert out_ids.dtype == torch.int32 and out_ids.numel() >= n
+    cap = 0
+    if hist is not None:
+        assert hist.dtype == torch.int32 and hist.dim() == 2 and hist.is_contiguous()
+        assert hist_len is not None and hist_len.dtype == torch.int32 and hist_len.numel() >= hist.shape[0]
+        cap = hist.shape[1]
     _check(lib.ub_sample(_ptr(logits), logits.stride(0), _ptr(work), n, V, _ptr(params_dev),
-                         _ptr(recent), _ptr(bias_ids), _ptr(bias_vals), _ptr(out_ids), int(counter_add), _stream()),
+                         _ptr(recent), _ptr(bias_ids), _ptr(bias_vals), _ptr(out_ids), int(counter_add),
+                         _ptr(hist), _ptr(hist_len), cap, _stream()),
            "sample")

@@ -11,7 +11,7 @@ from __future__ import annotations
 from dataclasses import dataclass, field
 
 
-@dataclass
+@dataclass(frozen=True)
 class SamplingParams:
     temperature: float = 0.0          # <= 0: first maximum after penalties
     top_k: int = 0                    # 0: off
