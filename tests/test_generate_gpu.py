@@ -89,3 +89,33 @@ def test_command_line_run(model_dirs, capsys):
     assert "gen tok" in out.err
     assert main(["run", model_dirs("A", "float32"), "--n-predict", "100", "--n-ctx", "64"]) == 1
     assert main(["run", model_dirs("A", "float32"), "--bogus"]) == 2
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_steps_queued_ahead_of_the_host_change_nothing(model_dirs, dtype):
+    """With a sampler that hands its ids on without the host and an engine that takes them from the
+    device, the loop queues the next step before it has seen this step's ids.  Tokens, finish reasons
+    and what is left in the cache are those of the loop that waits for every step: with stop tokens
+    that cut sequences at different steps, per-request lengths, seeded sampling and penalties."""
+    from ultima_b200 import LLM
+    from ultima_b200.engine.generate import generate
+    from ultima_b200.sampling import SamplingParams
+    llm = LLM(model_dirs("B", dtype), dtype=dtype, n_ctx=256, max_batch=8)
+    assert llm.engine.feeds_from_device
+    prompts = [random_ids(40 + i, n, 1000) for i, n in enumerate((1, 7, 30, 64, 3, 12))]
+    cases = [(SamplingParams(), ()),
+             (SamplingParams(temperature=0.9, top_k=50, rep_penalty=1.3, repeat_last_n=32), ()),
+             (SamplingParams(temperature=1.2, top_p=0.95, frequency_penalty=0.3), None)]
+    for sp, stop in cases:
+        n_predict = [24, 9, 24, 17, 1, 24]
+        waits = lambda *a: llm.sampler.sample(*a)          # a plain function: the loop cannot look ahead
+        ref = generate(llm.engine, waits, prompts, sp, n_predict, stop or (), seed=5, max_batch=8)
+        if stop is None:                                   # stop on tokens that really come up, early and late
+            stop = (ref[0].tokens[5], ref[2].tokens[11], ref[5].tokens[20])
+            ref = generate(llm.engine, waits, prompts, sp, n_predict, stop, seed=5, max_batch=8)
+            assert any(g.finish_reason == "stop" for g in ref)
+        got = generate(llm.engine, llm.sampler.sample, prompts, sp, n_predict, stop, seed=5, max_batch=8)
+        assert [g.tokens for g in got] == [g.tokens for g in ref]
+        assert [g.finish_reason for g in got] == [g.finish_reason for g in ref]
+        assert llm.engine.cache.pages_held() == 0
+        llm.engine.check_errors()

@@ -144,9 +144,12 @@ class DecodeRecord:
                                seq_before=v[4], seq_slot=v[5], want_rows=v[6], tables=tables, max_new=1,
                                max_after=0, host={"n_ints": self.total})
 
-    def update(self, slots, ids, before, tables_np) -> StepBatch:
+    def update(self, slots, ids, before, tables_np, ids_dev=None) -> StepBatch:
+        """``ids_dev`` (int32 on the device, one a sequence) instead of ``ids``: the token ids are copied
+        from there on the device, and the host's copy leaves that part of the record alone."""
         h, o, B = self.host, self.offs, self.B
-        h[o[0]:o[0] + B] = ids
+        if ids_dev is None:
+            h[o[0]:o[0] + B] = ids
         h[o[1]:o[1] + B] = before
         h[o[4]:o[4] + B] = before
         h[o[5]:o[5] + B] = slots
@@ -154,7 +157,11 @@ class DecodeRecord:
             h[o[7 + i]:o[7 + i] + t.size] = t.reshape(-1)
         idx, pinned = self.ring.take(self.total)
         pinned.numpy()[:self.total] = h
-        self.static.copy_(pinned[:self.total], non_blocking=True)
+        if ids_dev is None:
+            self.static.copy_(pinned[:self.total], non_blocking=True)
+        else:
+            self.static[o[1]:].copy_(pinned[o[1]:self.total], non_blocking=True)
+            self.static[:B].copy_(ids_dev[:B], non_blocking=True)
         self.ring.copied(idx)
         b = self.batch
         b.max_after = int(max(before)) + 1

@@ -274,7 +274,45 @@ class Engine:
                 raise StepError(str(e)) from e
         return self._pass(slots, tokens, before, list(range(B)))
 
-    def _pass(self, slots, new_tokens, before, want_rows) -> torch.Tensor:
+    @property
+    def feeds_from_device(self) -> bool:
+        """Whether ``step_fed`` is there: decode steps are replayed graphs that read a record on the device."""
+        return bool(self.use_graphs)
+
+    def step_fed(self, slots, ids_dev: torch.Tensor) -> torch.Tensor:
+        """The common decode step with the token ids already on the device (int32, one a slot, for
+        instance where the sampler has just put them): the step can be queued before the host has
+        seen the ids, so the device never waits for the host between two steps.  An id outside the
+        vocabulary raises the status flag that ``check_errors`` reports.  The logits returned are
+        the graph's own buffer: they hold until the next step with as many sequences."""
+        if not self.feeds_from_device:
+            raise StepError("step_fed: this engine does not replay captured decode steps")
+        B = len(slots)
+        if len(set(slots)) != B:
+            raise StepError("step: a slot is named twice")
+        if ids_dev.dtype != torch.int32 or ids_dev.device != self.device or ids_dev.numel() < B:
+            raise StepError("step_fed: token ids must be int32 on the engine's device, one a slot")
+        before, after = [], {}
+        for s in slots:
+            self.cache.slots.check(s)
+            n = self.cache.slots.length[s]
+            if n + 1 > self.max_context:
+                raise StepError(f"step: slot {s} would reach {n + 1} positions; the limit is {self.max_context}")
+            before.append(n)
+            if n % 64 == 0:
+                after[s] = n + 1
+        if after:
+            try:
+                self.cache.can_hold(after)
+            except CacheError as e:
+                raise StepError(str(e)) from e
+        self._borrow = True
+        try:
+            return self._pass(slots, [[0]] * B, before, list(range(B)), ids_dev=ids_dev)
+        finally:
+            self._borrow = False
+
+    def _pass(self, slots, new_tokens, before, want_rows, ids_dev=None) -> torch.Tensor:
         """One pass through the layers: reserve pages, lay the batch out, run, commit."""
         for s, t, b in zip(slots, new_tokens, before):
             self.cache.reserve(s, b + len(t))
@@ -282,7 +320,7 @@ class Engine:
         tables = self.cache.tables(slots)
         decode = self.use_graphs and all(len(t) == 1 for t in new_tokens) and list(want_rows) == list(range(B))
         if decode:
-            logits = self._decode_pass(slots, new_tokens, before, want_rows, tables)
+            logits = self._decode_pass(slots, new_tokens, before, want_rows, tables, ids_dev)
         else:
             batch = build_step_batch(slots, new_tokens, before, want_rows, tables, self.device, self._ring)
             self.last_h2d_bytes = batch.host["n_ints"] * 4
@@ -300,7 +338,7 @@ class Engine:
             key.append(attn_tc.decode_slices(B, g.need.n_kv_heads, longest, g.need.window))
         return tuple(key)
 
-    def _decode_pass(self, slots, new_tokens, before, want_rows, tables) -> torch.Tensor:
+    def _decode_pass(self, slots, new_tokens, before, want_rows, tables, ids_dev=None) -> torch.Tensor:
         B = len(slots)
         longest = max(before) + 1
         key = self._decode_key(B, longest)
@@ -308,7 +346,7 @@ class Engine:
         entry = self._graphs.get(key)
         if entry is None:
             record = DecodeRecord(B, [t.shape[1] for t in tables], self.device, self._ring)
-            batch = record.update(slots, ids, before, tables)
+            batch = record.update(slots, ids, before, tables, ids_dev)
             self.model.forward(batch, self.cache)              # warm: libraries, tensor maps, scratch
             torch.cuda.synchronize(self.device)
             graph = torch.cuda.CUDAGraph()
@@ -319,7 +357,7 @@ class Engine:
             self.rt.launches = l0
             self._graphs[key] = entry
         graph, record, logits, n_launch = entry
-        record.update(slots, ids, before, tables)
+        record.update(slots, ids, before, tables, ids_dev)
         self.last_h2d_bytes = record.total * 4
         graph.replay()
         self.rt.launches += n_launch

@@ -86,13 +86,34 @@ def run_batch(engine, sample, prompts: list, params: list, n_predict: list, stop
             return out
         t0 = time.perf_counter()
         borrow = {"borrow": True} if getattr(engine, "use_graphs", False) else {}
+        # A sampler that can hand its token ids on without the host (begin / wait) and an engine that
+        # can take them from the device (step_fed) let the next step be queued before this step's ids
+        # have reached the host: the device then never waits for the host between two steps.
+        owner = getattr(sample, "__self__", None)
+        begin = getattr(sample, "begin", None) or getattr(owner, "begin", None)
+        ahead = begin is not None and getattr(engine, "feeds_from_device", False)
         logits = engine.step([slots[i] for i in live], [prompts[i] for i in live], None)
         if stats:
             stats.prompt_tokens += sum(len(prompts[i]) for i in live)
+
+        def draw(rows_logits, rows, continuing=False):
+            args = (rows_logits, [params[i] for i in rows], [streams[i] for i in rows],
+                    [len(out[i].tokens) for i in rows], [seen[i] for i in rows])
+            if begin is None:
+                ids = sample(*args)
+                return lambda: ids
+            return begin(*args, continuing=continuing).wait
+
         first = True
+        pending = draw(logits, live)
         while live:
-            ids = sample(logits, [params[i] for i in live], [streams[i] for i in live],
-                         [len(out[i].tokens) for i in live], [seen[i] for i in live])
+            # queue the next step now if every sequence goes on unless it draws a stop token
+            next_logits = None
+            if ahead and all(len(out[i].tokens) + 1 < n_predict[i] for i in live):
+                ids_dev = getattr(getattr(pending, "__self__", None), "ids_dev", None)
+                if ids_dev is not None:
+                    next_logits = engine.step_fed([slots[i] for i in live], ids_dev)
+            ids = pending()
             now = time.perf_counter()
             if stats:
                 if first:
@@ -102,8 +123,8 @@ def run_batch(engine, sample, prompts: list, params: list, n_predict: list, stop
                 stats.steps += 1
             first = False
             t0 = now
-            going, feed = [], []
-            for i, tok in zip(live, ids):
+            going, feed, rows = [], [], []
+            for r, (i, tok) in enumerate(zip(live, ids)):
                 tok = int(tok)
                 if params[i].uses_history:
                     seen[i].append(tok)
@@ -116,13 +137,20 @@ def run_batch(engine, sample, prompts: list, params: list, n_predict: list, stop
                     out[i].tokens.append(tok)
                     going.append(i)
                     feed.append([tok])
+                    rows.append(r)
                     continue
                 engine.close([slots[i]])            # a sequence that ends gives its slot back
                 held.discard(i)
+            same = going == live
             live = going
             if not live:
                 break
-            logits = engine.step([slots[i] for i in live], feed, None, **borrow)
+            if next_logits is not None:
+                # the step has run for all that were alive; those that stopped are dropped from its rows
+                pending = draw(next_logits if same else next_logits[rows], live, continuing=same)
+            else:
+                logits = engine.step([slots[i] for i in live], feed, None, **borrow)
+                pending = draw(logits, live)
         return out
     finally:
         if stats:

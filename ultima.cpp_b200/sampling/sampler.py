@@ -56,8 +56,12 @@ class Sampler:
         self._dummy_f = torch.zeros(1, dtype=torch.float32, device=self.device)
         self._hist = None          # [RINGS, capacity] int32
         self._hist_len = None      # [RINGS] int32: tokens put into each ring so far
-        self._ring_of: dict = {}   # stream -> (ring, length of the history the ring mirrors)
+        self._ring_of: dict = {}   # (stream, row of that stream) -> (ring, length of the history it mirrors, last token)
         self._free_rings: list = []
+        self._last = None          # rows of the call before: (identity, rings, keys)
+        self._landing = [None, None]   # pinned host buffers the ids are copied into, used in turn
+        self._turn = 0
+        self._keys = []
 
     # ---- rings of recent tokens ------------------------------------------------------------
     def _ensure_rings(self, window: int) -> None:
@@ -154,14 +158,30 @@ class Sampler:
         """logits: float32 [n, vocab] on the device; params[i], streams[i] (from stream_seed),
         counters[i] (tokens drawn so far), recents[i] (the sequence's tokens so far: what penalties
         look back on) for row i."""
+        return self.begin(logits, params, streams, counters, recents).wait()
+
+    def begin(self, logits: torch.Tensor, params: list, streams: list, counters: list,
+              recents: list | None = None, continuing: bool = False) -> "Pending":
+        """The same without waiting: the kernel is launched, the ids start on their way to the host,
+        and ``wait()`` of what is returned gives them.  ``ids_dev`` of it holds them on the device
+        (until the next call) for a step that is queued before the host has seen them.
+        ``continuing``: these are the rows of the call before, one token later; the rings of recent
+        tokens are taken as the kernel left them and ``recents`` is not looked at."""
         n = logits.shape[0]
-        if n == 0:
-            return []
         if n > self._out.numel() - 4:
             raise ValueError(f"at most {self._out.numel() - 4} rows a call")
+        if n == 0:
+            return Pending(self, 0, None, None, (), ())
         dev = self.device
         uses = any(p.history_window() > 0 for p in params)
-        rings = tuple(self._rings_for(params, streams, recents, counters)) if uses else (-1,) * n
+        if continuing:
+            if self._last is None or self._last[0] != (tuple(map(id, params)), tuple(streams)):
+                raise ValueError("continuing: not the rows of the call before")
+            rings, keys = self._last[1], self._last[2]
+        else:
+            rings = tuple(self._rings_for(params, streams, recents, counters)) if uses else (-1,) * n
+            keys = tuple(self._keys) if uses else ()
+        self._last = ((tuple(map(id, params)), tuple(streams)), rings, keys)
         base, plain, greedy, base_dev, bid_dev, bval_dev, _ = self._records(params, streams, rings)
         if all(c == counters[0] for c in counters):
             # rows that have drawn equally often: the records stay, the count is an argument
@@ -179,13 +199,37 @@ class Sampler:
         ops.sample(logits, work, params_dev, self._dummy_i, bid_dev if bid_dev is not None else self._dummy_i,
                    bval_dev if bval_dev is not None else self._dummy_f, out, counter_add,
                    self._hist if uses else None, self._hist_len if uses else None)
-        host = self._out[:4 + n].cpu().tolist()          # the status flags travel with the ids
-        if self.rt is not None and any(host[:4]):
-            self.rt.check_status()
+        # the status flags travel with the ids; two landing places, so that a call may begin before
+        # the one before it has been waited for
+        self._turn ^= 1
+        if self._landing[self._turn] is None:
+            self._landing[self._turn] = torch.empty(self._out.numel(), dtype=torch.int32, pin_memory=True)
+        pin = self._landing[self._turn]
+        pin[:4 + n].copy_(self._out[:4 + n], non_blocking=True)
+        done = torch.cuda.Event()
+        done.record()
+        return Pending(self, n, pin, done, rings if uses else (), keys)
+
+
+class Pending:
+    """Token ids on their way from the device."""
+
+    def __init__(self, sampler, n, pin, done, rings, keys):
+        self.sampler, self.n, self.pin, self.done, self.rings, self.keys = sampler, n, pin, done, rings, keys
+        self.ids_dev = sampler._out[4:4 + n] if n else None
+
+    def wait(self) -> list[int]:
+        if self.n == 0:
+            return []
+        self.done.synchronize()
+        host = self.pin[:4 + self.n].tolist()
+        smp = self.sampler
+        if smp.rt is not None and any(host[:4]):
+            smp.rt.check_status()
         ids = host[4:]
-        if uses:               # what each ring now holds: the history given plus the token just drawn
-            for i, g in enumerate(rings):
-                if g >= 0:
-                    ring, length, _ = self._ring_of[self._keys[i]]
-                    self._ring_of[self._keys[i]] = (ring, length + 1, ids[i])
+        for i, g in enumerate(self.rings):     # what each ring now holds: its history plus the token just drawn
+            if g >= 0:
+                known = smp._ring_of.get(self.keys[i])
+                if known is not None and known[0] == g:
+                    smp._ring_of[self.keys[i]] = (g, known[1] + 1, ids[i])
         return ids
