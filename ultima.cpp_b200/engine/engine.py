@@ -51,7 +51,7 @@ class Engine:
     def __init__(self, spec: ModelSpec, tensors: dict, dtype="bfloat16", max_tokens: int = 4096,
                  max_seqs: int | None = None, max_step_tokens: int = 4096, device="cuda:0",
                  max_context: int | None = None, poison_cache: bool = False, runtime=None,
-                 use_graphs: bool = True):
+                 use_graphs: bool = True, with_sampler: bool = True):
         self.spec = spec
         self.dtype = _dtype_of(dtype)
         self.device = torch.device(device)
@@ -62,7 +62,7 @@ class Engine:
         torch.cuda.set_device(self.device)
         self.rt = runtime or Runtime(self.device, self.dtype)
         from ..kernels import build as _build, catalog as _catalog
-        _build.prebuild(_catalog.targets_for_model(spec, self.dtype))     # nvcc runs side by side
+        _build.prebuild(_catalog.targets_for_model(spec, self.dtype, sampler=with_sampler))     # nvcc runs side by side
         self.model = Model(spec, tensors, self.rt)
         self.max_tokens = int(max_tokens)
         self.max_context = int(min(max_context or spec.max_positions, spec.max_positions))

@@ -78,7 +78,7 @@ def main(argv=None) -> int:
     print(f"[trace_run] loading {args.model} ({args.dtype})", file=sys.stderr, flush=True)
     from .engine import Engine
     engine = Engine.from_dir(args.model, dtype=args.dtype, max_tokens=args.max_tokens,
-                             max_step_tokens=args.max_step_tokens, device=args.device)
+                             max_step_tokens=args.max_step_tokens, device=args.device, with_sampler=False)
     engine.warm_up()
     print("[trace_run] ready", file=sys.stderr, flush=True)
     replay(engine, sys.stdin, args.out, say)

@@ -16,13 +16,23 @@ def all_targets() -> list:
             + [("attn_tcgen05.cu", (f"HEAD_DIM={hd}",)) for hd in TC_HEAD_DIMS])
 
 
-def targets_for_model(spec, dtype) -> list:
-    """What one model needs: the plain libraries and, on the bfloat16 path, the attention
-    library of each head size its mixers use."""
+def targets_for_model(spec, dtype, sampler: bool = True) -> list:
+    """What one model needs: on the float32 path the CUDA-core product and the float32 attention; on
+    the bfloat16 path the tcgen05 product (the CUDA-core one stands in for shapes it refuses) and the
+    attention library of each head size the model's mixers use.  ``sampler``: the sampling kernel
+    too (a replay of given tokens samples nothing)."""
     import torch
-    out = list(PLAIN)
+    out = [("basic.cu", ()), ("gemm_simt.cu", ())]
+    dims = sorted({L.mixer.get("head_dim") for L in spec.layers if L.mixer.get("head_dim")})
     if dtype == torch.bfloat16:
-        dims = sorted({L.mixer.get("head_dim") for L in spec.layers if L.mixer.get("head_dim")})
-        out += [("attn_mma.cu", (f"HEAD_DIM={hd}",)) for hd in dims if hd % 16 == 0 and hd <= 256]
-        out += [("attn_tcgen05.cu", (f"HEAD_DIM={hd}",)) for hd in dims if hd in TC_HEAD_DIMS]
+        out.append(("gemm_tcgen05.cu", ()))
+        fits = [hd for hd in dims if hd % 16 == 0 and 16 <= hd <= 256]
+        out += [("attn_mma.cu", (f"HEAD_DIM={hd}",)) for hd in fits]
+        out += [("attn_tcgen05.cu", (f"HEAD_DIM={hd}",)) for hd in fits if hd in TC_HEAD_DIMS]
+        if len(fits) != len(dims):
+            out.append(("attn_simple.cu", ()))
+    else:
+        out.append(("attn_simple.cu", ()))
+    if sampler:
+        out.append(("sampling.cu", ()))
     return out
