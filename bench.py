@@ -423,6 +423,7 @@ def run_other(args):
                     max_tokens=sum(per_seq), max_seqs=B, max_step_tokens=4096, max_context=CONTEXT)
     sampler = Sampler(dev, cfg.vocab_size, engine.rt)
     engine.warm_up()
+    print(f"[bench] {args.config}: model ready", file=sys.stderr, flush=True)
     slots = engine.open(B)
     prompts = [rng.integers(0, cfg.vocab_size, size=n).tolist() for n in lens]
     engine.step([slots[0]], [prompts[0][:64]], [[]])            # warm the prompt kernels
@@ -436,6 +437,7 @@ def run_other(args):
     e1.record()
     torch.cuda.synchronize()
     pre_ms = e0.elapsed_time(e1)
+    print(f"[bench] {args.config}: {sum(lens)} prompt tokens in {pre_ms:.1f} ms", file=sys.stderr, flush=True)
     toks = rng.integers(0, cfg.vocab_size, size=(args.warmup + steps, B))
     prm = sampler_params(sampler, [None] * B, dev)
     out_ids = torch.empty(B, dtype=torch.int32, device=dev)
@@ -453,6 +455,7 @@ def run_other(args):
     torch.cuda.synchronize()
     ms = e0.elapsed_time(e1)
     clk = clocks.stop()
+    print(f"[bench] {args.config}: {steps} decode steps in {ms:.1f} ms", file=sys.stderr, flush=True)
     engine.check_errors()
     mean_ctx = sum(lens) / B + args.warmup + steps / 2
     step_bytes = weight_bytes(cfg) + B * mean_ctx * kv_bytes_per_token(cfg, 2)
@@ -498,7 +501,13 @@ def main():
     ap.add_argument("--fast-fill", action="store_true", help="do not run the prompts; mark the cache as filled")
     ap.add_argument("--prompt", type=int, default=PROMPT, help="positions each sequence holds before the timed steps")
     ap.add_argument("--prefill-tokens", type=int, default=PREFILL_TOKENS, help="tokens of the timed prompt")
+    ap.add_argument("--watchdog", type=int, default=1500,
+                    help="seconds after which a run that has not ended dumps its stack and exits (0: never)")
     args = ap.parse_args()
+    if args.watchdog > 0:
+        # a run that stops making progress ends with a message instead of holding its GPU
+        import faulthandler
+        faulthandler.dump_traceback_later(args.watchdog, exit=True)
     if args.impl == "reference":
         return run_reference(args)
     if args.gpus != 1:

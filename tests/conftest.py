@@ -14,6 +14,15 @@ for p in (ROOT, os.path.dirname(os.path.abspath(__file__))):
 
 def pytest_configure(config):
     config.addinivalue_line("markers", "gpu: needs a CUDA device (B200)")
+    # all tests together take a few minutes; a session that has not ended after 25 dumps every
+    # thread's stack and exits, so a kernel that stopped making progress cannot hold a GPU for hours
+    import faulthandler
+    faulthandler.dump_traceback_later(1500, exit=True)
+
+
+def pytest_unconfigure(config):
+    import faulthandler
+    faulthandler.cancel_dump_traceback_later()
 
 
 # Three tiny configurations that differ in every size and option: layers, width, heads and

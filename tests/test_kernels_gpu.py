@@ -597,13 +597,21 @@ def test_gemm_tc_interleaved_gate_product(shape):
     assert rel_err(out, gt / (1 + torch.exp(-gt)) * up) <= 2 ** -8, shape
 
 
+@pytest.mark.parametrize("pairs", [False, True])
 @pytest.mark.parametrize("case", [("store", 2500, 1024, 1200), ("add", 2500, 512, 2100), ("add", 5000, 128, 1100), ("gate_il", 1700, 256, 1280),
-                                  ("gate_two", 1100, 320, 1300), ("store_f32", 700, 128, 5000)])
-def test_gemm_tc_many_tiles_a_cta(case):
-    """More tiles than SMs: CTAs stay and walk over tiles with two accumulators in turn."""
+                                  ("gate_two", 1100, 320, 1300), ("store_f32", 700, 128, 5000),
+                                  ("store", 2600, 192, 2100), ("gate_il", 2100, 128, 2560), ("store_f32", 1300, 64, 3300),
+                                  ("add", 2049, 4096, 4096)])
+def test_gemm_tc_many_tiles_a_cta(case, pairs, monkeypatch):
+    """More tiles than SMs: CTAs stay and walk over tiles with two accumulators in turn; with
+    ``pairs`` two CTAs share a tile of 256 weight rows by 256 tokens where there are enough tiles
+    (the last six cases but one), else the same kernel as without."""
     gemm_tc, rt = _tc()
     ops = _ops()
     kind, T, K, N = case
+    monkeypatch.setattr(gemm_tc, "USE_PAIRS", pairs)
+    if pairs and case[1:] in ((2600, 192, 2100), (2100, 128, 2560), (1300, 64, 3300), (2049, 4096, 4096), (5000, 128, 1100)):
+        assert gemm_tc.pairs(T, N, 1, ops.EPI_STORE)
     g = torch.Generator().manual_seed(T)
     a = torch.randn(T, K, generator=g).to(torch.bfloat16).to(DEV)
     w = (torch.randn(N, K, generator=g) * 0.05).to(torch.bfloat16).to(DEV)

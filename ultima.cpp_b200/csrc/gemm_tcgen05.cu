@@ -256,13 +256,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
 struct Pieces {
     int nkb, tile, tile_end, step;
     long long u, u_end;
-    __device__ Pieces(int n_tiles, int nkb_, int share_tail) : nkb(nkb_) {
-        step = gridDim.x;
-        tile = blockIdx.x;
+    // ``me`` of ``workers`` (CTAs, or pairs of CTAs) that share the tiles out
+    __device__ Pieces(int n_tiles, int nkb_, int share_tail, int me, int workers) : nkb(nkb_) {
+        step = workers;
+        tile = me;
         tile_end = share_tail ? (n_tiles / step) * step : n_tiles;       // tiles of the full rounds
         const long long units = (long long)(n_tiles - tile_end) * nkb;
-        u = (long long)tile_end * nkb + units * blockIdx.x / gridDim.x;
-        u_end = (long long)tile_end * nkb + units * (blockIdx.x + 1) / gridDim.x;
+        u = (long long)tile_end * nkb + units * me / workers;
+        u_end = (long long)tile_end * nkb + units * (me + 1) / workers;
     }
     __device__ bool next(int& t, int& kb0, int& kb1) {
         if (tile < tile_end) {
@@ -337,7 +338,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const __gri
             pdl_wait();
             long long it = 0;                            // stages filled so far, over all tiles
             bool ok = true;
-            Pieces pieces(n_tiles, nkb, p.share_tail);
+            Pieces pieces(n_tiles, nkb, p.share_tail, blockIdx.x, gridDim.x);
             int tile, kb0, kb1;
             while (ok && pieces.next(tile, kb0, kb1)) {
                 const int n0 = (tile / tiles_t) * BM, t0 = (tile % tiles_t) * BN;
@@ -366,7 +367,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const __gri
             constexpr uint32_t idesc = make_idesc(BN);
             long long it = 0;
             bool ok = true;
-            Pieces pieces(n_tiles, nkb, p.share_tail);
+            Pieces pieces(n_tiles, nkb, p.share_tail, blockIdx.x, gridDim.x);
             int tile, kb0, kb1;
             for (int i = 0; ok && pieces.next(tile, kb0, kb1); ++i) {
                 const int buf = i & 1;
@@ -400,7 +401,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const __gri
         const int q = warp & 3;
         pdl_wait();
         bool ok = true;
-        Pieces pieces(n_tiles, nkb, p.share_tail);
+        Pieces pieces(n_tiles, nkb, p.share_tail, blockIdx.x, gridDim.x);
         int tile, kb0, kb1;
         for (int i = 0; ok && pieces.next(tile, kb0, kb1); ++i) {
             const int buf = i & 1;
@@ -418,6 +419,153 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const __gri
     if (warp == 1) {
         tc_fence_after();
         tmem_dealloc(tmem_base, S::TMEM_COLS);
+    }
+    if (threadIdx.x == 0 && *err) atomicExch(p.error, 1);
+}
+
+// ---------------------------------------------------------------------------------------
+// The same again with two CTAs (two SMs) on one tile of 256 weight rows x 256 tokens
+// (tcgen05 cta_group::2).  Each CTA loads its own 128 weight rows and its own 128 of the tokens;
+// the leader's MMAs read both CTAs' shared memory, so a CTA moves 32 KB a k block where the
+// one-CTA kernel moves 48 KB for the same arithmetic, and six stages fit instead of four.  Each
+// CTA's tensor memory receives its own 128 weight rows of the result and its own epilogue warps
+// write them out; the tile sharing of the adding epilogue is the same, by pairs.
+// ---------------------------------------------------------------------------------------
+template <int EPI>
+struct SmemPair {
+    static constexpr int BNC = 128;                      // tokens a CTA loads
+    static constexpr int A_BYTES = BM * BK * 2;
+    static constexpr int B_BYTES = BNC * BK * 2;
+    static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+    static constexpr int STAGES = (196 * 1024) / STAGE_BYTES;
+    static constexpr int XCH_BYTES = EPI == EPI_SWIGLU_IL ? 64 * 16 * 4 : 0;
+    static constexpr int TOTAL = STAGES * STAGE_BYTES + 1024 + 256 + XCH_BYTES;
+    static constexpr int ACC_COLS = 2 * BNC;             // the pair's tokens
+    static constexpr int TMEM_COLS = 512;                // two accumulators
+};
+
+template <int EPI, typename TO>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_a, GemmParams p) {
+    static_assert(EPI != EPI_SWIGLU, "one accumulator a tile");
+    using S = SmemPair<EPI>;
+    constexpr int BN2 = 2 * S::BNC, BM2 = 2 * BM;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint64_t* full = (uint64_t*)(smem + S::STAGES * S::STAGE_BYTES);     // the leader's are used
+    uint64_t* empty = full + S::STAGES;
+    uint64_t* acc_full = empty + S::STAGES;            // [2]
+    uint64_t* acc_empty = acc_full + 2;                // [2], the leader's are used
+    uint32_t* tmem_slot = (uint32_t*)(acc_empty + 2);
+    volatile int* err = (volatile int*)(tmem_slot + 1);
+    float* xch = (float*)(smem + S::STAGES * S::STAGE_BYTES + 256);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int rank = (int)cluster_cta_rank();
+    const bool leader = rank == 0;
+    const int pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
+    const int tiles_w = (p.N + BM2 - 1) / BM2, tiles_t = (p.T + BN2 - 1) / BN2;
+    const int n_tiles = tiles_w * tiles_t;
+    const int nkb = (p.K + BK - 1) / BK;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < S::STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+        for (int b = 0; b < 2; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], 8); }   // 4 warps of each CTA
+        *err = 0;
+        fence_barrier_init();
+    }
+    if (warp == 1) { tmem_alloc_pair(tmem_slot, S::TMEM_COLS); tmem_relinquish_pair(); }
+    if (warp == 0 && lane == 0) { prefetch_tmap(&map_w); prefetch_tmap(&map_a); }
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync_all();                                  // the other CTA's barriers exist before anything lands on them
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+    // No part in dependent launches: this kernel is launched the ordinary way and lets no kernel
+    // start before it has ended (pairs of SMs are handed out whole, and with kernels that start
+    // early in the mix the device was seen to stop making progress).
+
+    if (warp == 0) {
+        if (lane == 0) {
+            long long it = 0;
+            bool ok = true;
+            Pieces pieces(n_tiles, nkb, p.share_tail, pair, n_pairs);
+            int tile, kb0, kb1;
+            while (ok && pieces.next(tile, kb0, kb1)) {
+                const int n0 = (tile / tiles_t) * BM2 + rank * BM, t0 = (tile % tiles_t) * BN2 + rank * S::BNC;
+                for (int kb = kb0; kb < kb1; ++kb, ++it) {
+                    const int s = (int)(it % S::STAGES);
+                    const uint32_t ph = (uint32_t)((it / S::STAGES) & 1);
+                    ok = mbar_wait(&empty[s], ph ^ 1, err);
+                    if (!ok) break;
+                    uint8_t* st = smem + s * S::STAGE_BYTES;
+                    if (leader) mbar_expect_tx(&full[s], 2 * S::STAGE_BYTES);      // both CTAs' copies
+                    tma_load_2d_pair(st, &map_w, &full[s], kb * BK, n0);
+                    tma_load_2d_pair(st + S::A_BYTES, &map_a, &full[s], kb * BK, t0);
+                }
+            }
+            if (*err && leader) {
+                for (long long j = it > S::STAGES ? it - S::STAGES : 0; j < it; ++j) {
+                    const long long tstart = clock64();
+                    while (!mbar_try_wait(&full[j % S::STAGES], (uint32_t)((j / S::STAGES) & 1)))
+                        if (clock64() - tstart > WAIT_LIMIT_CYCLES / 8) break;
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0 && leader) {
+            constexpr uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN2 >> 3) << 17) | ((uint32_t)(BM2 >> 4) << 24);
+            long long it = 0;
+            bool ok = true;
+            Pieces pieces(n_tiles, nkb, p.share_tail, pair, n_pairs);
+            int tile, kb0, kb1;
+            for (int i = 0; ok && pieces.next(tile, kb0, kb1); ++i) {
+                const int buf = i & 1;
+                ok = mbar_wait(&acc_empty[buf], (uint32_t)(((i >> 1) & 1) ^ 1), err);   // both epilogues have read it
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t acc = tmem_base + buf * S::ACC_COLS;
+                for (int kb = kb0; kb < kb1; ++kb, ++it) {
+                    const int s = (int)(it % S::STAGES);
+                    const uint32_t ph = (uint32_t)((it / S::STAGES) & 1);
+                    ok = mbar_wait(&full[s], ph, err);
+                    if (!ok) break;
+                    tc_fence_after();
+                    const uint32_t a_addr = smem_u32(smem + s * S::STAGE_BYTES);
+                    const uint64_t da = make_desc(a_addr), db = make_desc(a_addr + S::A_BYTES);
+#pragma unroll
+                    for (int k = 0; k < BK / UMMA_K; ++k) {
+                        const uint64_t koff = (uint64_t)((k * UMMA_K * 2) >> 4);
+                        tc_mma_bf16_pair(acc, da + koff, db + koff, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
+                    }
+                    tc_commit_pair(&empty[s]);           // frees the stage in both CTAs
+                }
+                if (ok) tc_commit_pair(&acc_full[buf]);  // wakes both epilogues
+            }
+        }
+    } else {
+        const int q = warp & 3;
+        bool ok = true;
+        Pieces pieces(n_tiles, nkb, p.share_tail, pair, n_pairs);
+        int tile, kb0, kb1;
+        for (int i = 0; ok && pieces.next(tile, kb0, kb1); ++i) {
+            const int buf = i & 1;
+            ok = mbar_wait(&acc_full[buf], (uint32_t)((i >> 1) & 1), err);
+            if (!ok) break;
+            tc_fence_after();
+            epilogue_tile<BN2, EPI, TO>(p, tmem_base + buf * S::ACC_COLS, q, lane, (tile / tiles_t) * 2 + rank,
+                                        (tile % tiles_t) * BN2, 0, xch);
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_leader(&acc_empty[buf]);
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync_all();                                  // neither CTA's tensor or shared memory goes while the other may touch it
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc_pair(tmem_base, S::TMEM_COLS);
     }
     if (threadIdx.x == 0 && *err) atomicExch(p.error, 1);
 }
@@ -560,4 +708,52 @@ UB_API int ub_gemm_tc(const void* map_w, const void* map_w2, const void* map_a, 
         case 256: return launch_bn<256>(mw, mw2, ma, p, epi, o_dtype, splits, st);
     }
     return UB_ERR_ARG;
+}
+
+// The two-CTA kernel: many tokens (T > 128), K whole.  map_w: boxes of 128 weight rows; map_a: boxes
+// of 128 tokens.  Epilogues: store, add (float32 out), interleaved gate product.
+template <int EPI, typename TO>
+static int launch_pair(const CUtensorMap* mw, const CUtensorMap* ma, GemmParams p, cudaStream_t st) {
+    using S = SmemPair<EPI>;
+    auto kern = gemm_tc_pair_kernel<EPI, TO>;
+    static bool attr_done = false;
+    if (!attr_done) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL);
+        if (e != cudaSuccess) return (int)e;
+        attr_done = true;
+    }
+    const int n_pairs = sm_count() / 2;
+    const int tiles = ((p.N + 2 * BM - 1) / (2 * BM)) * ((p.T + 255) / 256);
+    p.share_tail = (EPI == EPI_ADD && g_share_tail && tiles % n_pairs != 0 && tiles > n_pairs) ? 1 : 0;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(2 * (tiles < n_pairs ? tiles : n_pairs));
+    cfg.blockDim = dim3(NUM_THREADS);
+    cfg.dynamicSmemBytes = S::TOTAL;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;                  // not a programmatic dependent of the kernel before it
+    cudaError_t e = cudaLaunchKernelEx(&cfg, kern, *mw, *ma, p);
+    return e == cudaSuccess ? 0 : (int)e;
+}
+
+UB_API int ub_gemm_tc_pair(const void* map_w, const void* map_a, void* out, int o_dtype, long long ldo, int T, int N,
+                           int K, int epi, int* error, cudaStream_t st) {
+    if (T <= 0 || N <= 0) return 0;
+    if (K <= 0) return UB_ERR_ARG;
+    if (epi == EPI_SWIGLU_IL && (N % 128) != 0) return UB_ERR_ARG;
+    GemmParams p;
+    p.out = out; p.ldo = ldo; p.split_stride = 0;
+    p.T = T; p.N = N; p.K = K;
+    p.kb_per_split = (K + BK - 1) / BK;
+    p.atomic = 0; p.share_tail = 0; p.error = error;
+    const CUtensorMap* mw = (const CUtensorMap*)map_w;
+    const CUtensorMap* ma = (const CUtensorMap*)map_a;
+    if (epi == EPI_STORE && o_dtype == UB_BF16) return launch_pair<EPI_STORE, __nv_bfloat16>(mw, ma, p, st);
+    if (epi == EPI_STORE && o_dtype == UB_F32) return launch_pair<EPI_STORE, float>(mw, ma, p, st);
+    if (epi == EPI_ADD && o_dtype == UB_F32) return launch_pair<EPI_ADD, float>(mw, ma, p, st);
+    if (epi == EPI_SWIGLU_IL && o_dtype == UB_BF16) return launch_pair<EPI_SWIGLU_IL, __nv_bfloat16>(mw, ma, p, st);
+    return UB_ERR_UNSUPPORTED;
 }

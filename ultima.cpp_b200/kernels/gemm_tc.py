@@ -4,6 +4,7 @@ and kept)."""
 from __future__ import annotations
 
 import ctypes
+import os
 from ctypes import c_int, c_longlong, c_void_p
 
 import torch
@@ -26,6 +27,9 @@ def lib():
         L.ub_gemm_tc.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_longlong, c_longlong,
                                  c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p]
         L.ub_gemm_tc.restype = c_int
+        L.ub_gemm_tc_pair.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_longlong, c_int, c_int, c_int, c_int,
+                                      c_void_p, c_void_p]
+        L.ub_gemm_tc_pair.restype = c_int
         L.ub_gemm_tc_set_pdl.argtypes = [c_int]
         L.ub_gemm_tc_set_pdl.restype = None
         import os
@@ -111,6 +115,17 @@ def k_splits(T: int, N: int, K: int, bn: int, epilogue: int) -> int:
     return -(-nkb // per)
 
 
+USE_PAIRS = os.environ.get("ULTIMA_GEMM_PAIRS", "1") != "0"
+
+
+def pairs(T: int, N: int, splits: int, epilogue: int) -> bool:
+    """Whether the product runs on pairs of CTAs (tiles of 256 weight rows by 256 tokens): many
+    tokens, K whole, and at least one tile for every pair of SMs."""
+    if not USE_PAIRS or splits != 1 or epilogue == EPI_SWIGLU or T <= 128:
+        return False
+    return -(-N // 256) * -(-T // 256) >= N_SMS // 2
+
+
 def gemm(a, w, out, epilogue, w2, rt, splits: int | None = None, bn: int | None = None):
     """out: [T, N]; for EPI_SWIGLU_IL [T, N / 2]; for EPI_STORE with ``splits`` > 1 a float32
     [splits, T, N] whose sum over the first axis is the product."""
@@ -128,6 +143,10 @@ def gemm(a, w, out, epilogue, w2, rt, splits: int | None = None, bn: int | None 
         assert s == 1 or epilogue == EPI_ADD
         ldo = out.stride(0)
     L = lib()
+    if pairs(T, N, s, epilogue) and out.dim() == 2:
+        rc = L.ub_gemm_tc_pair(_tmap(w, 128), _tmap(a, 128), _ptr(out), BF16 if out.dtype == torch.bfloat16 else F32,
+                               out.stride(0), T, N, K, epilogue, _ptr(rt.status[1:2]), _stream())
+        return _check(rc, "gemm_tc_pair")
     mw = _tmap(w, 128)
     mw2 = _tmap(w2, 128) if w2 is not None else 0
     ma = _tmap(a, bn)
