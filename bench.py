@@ -209,6 +209,40 @@ def decode_timeline(engine, batch, prompt_len, rng):
     return 0
 
 
+def prefill_timeline(engine, tokens, rng):
+    """The same for one prompt of ``tokens`` tokens: the kernels of its last layers with begin, end and
+    own share (run few layers: --layers 4)."""
+    import torch
+    from torch.profiler import ProfilerActivity, profile
+    prompt = rng.integers(0, engine.spec.vocab_size, size=tokens).tolist()
+
+    def one():
+        s = engine.open(1)
+        engine.step(s, [prompt], None)
+        engine.close(s)
+    for _ in range(3):
+        one()
+    torch.cuda.synchronize()
+    with profile(activities=[ProfilerActivity.CUDA]) as prof:
+        one()
+        torch.cuda.synchronize()
+    ev = [e for e in prof.events() if e.device_type == torch.autograd.DeviceType.CUDA]
+    ev.sort(key=lambda e: e.time_range.start)
+    t0 = ev[0].time_range.start
+    rows, prev_end = [], None
+    for e in ev:
+        s, en = e.time_range.start - t0, e.time_range.end - t0
+        rows.append({"kernel": e.name.split("(")[0].replace("void ", "")[:48], "start_us": round(s, 2),
+                     "end_us": round(en, 2), "own_us": None if prev_end is None else round(en - prev_end, 2)})
+        prev_end = en if prev_end is None else max(prev_end, en)
+    engine.check_errors()
+    for r in rows[-20:]:
+        print(json.dumps(r))
+    print(json.dumps({"only": "timeline-prefill", "tokens": tokens, "layers": len(engine.spec.layers),
+                      "kernels": len(ev), "prompt_us": round(prev_end, 2)}))
+    return 0
+
+
 def sampling_times(batches=(1, 8, 64), vocab=151936, history=256):
     """Device time of the sampling kernel alone at the 8B vocabulary, for the reference's ladder
     of options (src/sampler/sampler.cpp:230-277): one JSON line a batch size, microseconds a call.
@@ -306,6 +340,8 @@ def run_ours(args):
 
     if args.only == "timeline":
         return decode_timeline(engine, args.batch, args.prompt, rng)
+    if args.only == "timeline-prefill":
+        return prefill_timeline(engine, args.prefill_tokens, rng)
 
     if args.only == "decode":
         ms, launches, ctx = timed_decode(engine, sampler, args.batch, args.steps, args.warmup, rng,
@@ -493,9 +529,10 @@ def main():
     ap.add_argument("--warmup", type=int, default=4)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--layers", type=int, default=0, help="fewer layers than the configuration (named in config)")
-    ap.add_argument("--only", default="all", choices=["all", "prefill", "decode", "timeline", "sample"],
+    ap.add_argument("--only", default="all", choices=["all", "prefill", "decode", "timeline", "timeline-prefill", "sample"],
                     help="a part of the run only (for profiling); the JSON line then holds that part. "
-                         "timeline: every kernel of a decode step with its begin and end inside the graph; "
+                         "timeline: every kernel of a decode step with its begin and end inside the graph "
+                         "(timeline-prefill: of a prompt); "
                          "sample: the sampling kernel alone, option by option")
     ap.add_argument("--batch", type=int, default=BATCH, help="sequences of the decode step")
     ap.add_argument("--fast-fill", action="store_true", help="do not run the prompts; mark the cache as filled")
