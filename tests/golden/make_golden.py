@@ -88,7 +88,9 @@ def run(exe: str, name: str, bdir: str):
 
 
 if __name__ == "__main__":
-    ref = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) < 2:
+        sys.exit("usage: make_golden.py <checkout of tattooinmtl/Ultima.cpp> [build folder]")
+    ref = sys.argv[1]
     bdir = sys.argv[2] if len(sys.argv) > 2 else os.path.join(tempfile.gettempdir(), "ultima_golden_build")
     exe = build(ref, bdir)
     for name in ("A", "B"):

@@ -7,9 +7,9 @@
 // :220-228, :261-263; else logits / T, :101-106), top-k (:109-121), top-p (:146-164), min-p
 // (:167-176), softmax and one draw (:178-182).
 //
-// Two rules are this library's own.  Cuts are made by value, found by a bit-wise search
-// instead of a sort, so elements equal to the cut value are all kept (the reference keeps an
-// arbitrary k of them).  The draw is the inverse CDF in index order at u = hash(seed, counter),
+// Two rules are this library's own.  Cuts are made by value, found by bucket histograms
+// instead of a sort (see "Where to cut" below), so elements equal to the cut value are all kept
+// (the reference keeps an arbitrary k of them).  The draw is the inverse CDF in index order at u = hash(seed, counter),
 // one stream for each sequence, so a sequence's tokens do not depend on its batch (the
 // reference draws from a std::mt19937_64 it owns for one sequence).
 #include "common.cuh"
