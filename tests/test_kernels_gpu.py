@@ -225,6 +225,58 @@ def test_qk_prepare_norm_rotation_and_cache_write(cfg, dtype):
     assert float(kc2.abs().sum()) == 0 and float(vc2.abs().sum()) == 0
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("cfg", [dict(nh=4, nkv=2, hd=128, norm=True, rot=True), dict(nh=5, nkv=1, hd=64, norm=True, rot=True),
+                                 dict(nh=2, nkv=1, hd=256, norm=False, rot=True), dict(nh=3, nkv=3, hd=128, norm=True, rot=False),
+                                 dict(nh=3, nkv=1, hd=80, norm=True, rot=True)])
+def test_qk_prepare_for_prompts(cfg, dtype):
+    """Hundreds of tokens of two sequences (a block a token, its warps walking over the heads),
+    with and without norm and rotation, q written to a matrix of its own."""
+    ops = _ops()
+    nh, nkv, hd = cfg["nh"], cfg["nkv"], cfg["hd"]
+    half, eps, theta = hd // 2, 1e-5, 1e4
+    lens = [190, 141]
+    toks = [(s, p) for s, n in enumerate(lens) for p in range(n)]
+    T = len(toks)
+    g = torch.Generator().manual_seed(hd + nh)
+    qkv = torch.randn(T, (nh + 2 * nkv) * hd, generator=g).to(dtype)
+    qw = (1 + 0.1 * torch.randn(hd, generator=g)) if cfg["norm"] else None
+    kw = (1 + 0.1 * torch.randn(hd, generator=g)) if cfg["norm"] else None
+    inv = 1.0 / theta ** (2.0 * torch.arange(half, dtype=torch.float64) / hd)
+    ang = torch.arange(256, dtype=torch.float64)[:, None] * inv[None]
+    cos = torch.cos(ang).float().to(DEV) if cfg["rot"] else None
+    sin = torch.sin(ang).float().to(DEV) if cfg["rot"] else None
+    n_pages = 9
+    table = torch.tensor([[5, 1, 8], [0, 7, 3]], dtype=torch.int32)
+    kc = torch.zeros(n_pages, nkv, 64, hd, dtype=dtype, device=DEV)
+    vc = torch.zeros(n_pages, nkv, 64, hd, dtype=dtype, device=DEV)
+    q_out = torch.full((T, nh * hd), float("nan"), dtype=dtype, device=DEV)
+    ops.qk_prepare(qkv.to(DEV), None if qw is None else qw.to(DEV), None if kw is None else kw.to(DEV), cos, sin,
+                   torch.tensor([p for _, p in toks], dtype=torch.int32, device=DEV),
+                   torch.tensor([s for s, _ in toks], dtype=torch.int32, device=DEV),
+                   kc, vc, table.to(DEV), 3 * 64, 64, nh, nkv, hd, eps, q_out=q_out)
+
+    def prep(x, w, p):          # x [T, heads, hd] float64, p [T]
+        if w is not None:
+            x = x * w.double() / torch.sqrt((x * x).mean(-1, keepdim=True) + eps)
+        if not cfg["rot"]:
+            return x
+        a, b = x[..., :half], x[..., half:]
+        c, s = torch.cos(ang[p])[:, None], torch.sin(ang[p])[:, None]
+        return torch.cat([a * c - b * s, a * s + b * c], -1)
+    pos = torch.tensor([p for _, p in toks])
+    rows = qkv.double()
+    tol = 1e-5 if dtype == torch.float32 else 2 ** -7
+    q_ref = prep(rows[:, :nh * hd].view(T, nh, hd), qw, pos)
+    k_ref = prep(rows[:, nh * hd:(nh + nkv) * hd].view(T, nkv, hd), kw, pos)
+    v_ref = rows[:, (nh + nkv) * hd:].view(T, nkv, hd)
+    assert rel_err(q_out.view(T, nh, hd), q_ref) <= tol
+    for t, (s, p) in enumerate(toks):
+        pg = int(table[s, p // 64])
+        assert rel_err(kc[pg, :, p % 64], k_ref[t]) <= tol, (t, s, p)
+        assert rel_err(vc[pg, :, p % 64], v_ref[t]) <= (0 if dtype == torch.float32 else tol)
+
+
 def test_silu_mul_convert_add_fill():
     ops = _ops()
     g = torch.Generator().manual_seed(9)
