@@ -52,7 +52,13 @@ TINY_E = dict(architectures=["Qwen3ForCausalLM"], model_type="qwen3", vocab_size
               intermediate_size=448, num_hidden_layers=2, num_attention_heads=3, num_key_value_heads=1,
               head_dim=128, rms_norm_eps=1e-5, rope_theta=1000000.0, max_position_embeddings=512,
               tie_word_embeddings=False, hidden_act="silu")
-TINY = {"A": TINY_A, "B": TINY_B, "C": TINY_C, "D": TINY_D, "E": TINY_E}
+# and one whose sizes fit none of the tensor-core kernels: rows of 100 values (not a multiple of 8),
+# a head size that is no multiple of 16, an inner size and a vocabulary that are odd
+TINY_F = dict(architectures=["Qwen3ForCausalLM"], model_type="qwen3", vocab_size=257, hidden_size=100,
+              intermediate_size=131, num_hidden_layers=2, num_attention_heads=5, num_key_value_heads=5,
+              head_dim=24, rms_norm_eps=2e-6, rope_theta=50000.0, max_position_embeddings=256,
+              tie_word_embeddings=False, hidden_act="silu")
+TINY = {"A": TINY_A, "B": TINY_B, "C": TINY_C, "D": TINY_D, "E": TINY_E, "F": TINY_F}
 
 
 def make_model_dir(tmp, name: str, dtype: str, seed: int = 7) -> str:

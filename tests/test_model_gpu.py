@@ -188,3 +188,25 @@ def test_weights_stored_in_32_bit_stay_32_bit_on_the_bfloat16_path(model_dirs, p
         rows.append(eng.step(s, [[ids[t]]], [[0]]).cpu().numpy())
     eng.close(s)
     _check(np.concatenate(rows), P.forward(cfg, w, ids), "bfloat16", name, "float32 weights on the bfloat16 path")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_sizes_that_fit_no_tensor_core_kernel(model_dirs, plain_models, dtype):
+    """Rows of 100 values, 5 heads of size 24, an inner size of 131, a vocabulary of 257: on the
+    bfloat16 path every product goes to the CUDA-core kernel and attention to the float32-accumulating
+    kernel, and the logits are still the plain implementation's: whole, and the end one by one."""
+    eng = _engine(model_dirs, "F", dtype)
+    ids = random_ids(31, 90, 257)
+    ref = _plain_logits(plain_models, "F", ids)
+    s = eng.open(1)
+    got = eng.step(s, [ids], [list(range(90))]).cpu().numpy()
+    eng.close(s)
+    _check(got, ref, dtype, "F", "whole, 90 tokens")
+    s = eng.open(2)
+    rows = [eng.step(s, [ids[:70], ids[:5]], [list(range(70)), []]).cpu().numpy()]
+    for t in range(70, 90):
+        rows.append(eng.step([s[0]], [[ids[t]]], [[0]]).cpu().numpy())
+    eng.close(s)
+    _check(np.concatenate(rows), ref, dtype, "F", "70 tokens, then one by one beside a second sequence")
+    eng.check_errors()
+    assert eng.cache.pages_held() == 0
