@@ -114,6 +114,7 @@ struct SelectSmem {
     u64 red64[33];
     float list_v[LIST];
     u64 list_w[LIST];
+    int list_i[LIST];
     float found_above_f;
     unsigned found_above_u;
     int found_bucket, count;
@@ -401,6 +402,71 @@ sample_kernel(const float* __restrict__ logits, long long ld, float* __restrict_
             t = search_cut<false>(x, sc, V, m, 0u, (u64)p.top_k, sel, tid);
         cut = t;
     }
+    const float minp = p.min_p > 0.f ? p.min_p : 0.f;
+    // What top-k left is usually a few dozen elements: they are copied to shared memory once and
+    // everything that follows (top-p, min-p, the draw) happens there instead of in passes over the row.
+    if (cut != 0) {
+        if (tid == 0) { sel.count = 0; sel.best = 0; }
+        __syncthreads();
+        visit(x, V, tid, [&](int i, float raw) {
+            const float v = __fmul_rn(raw, sc);
+            if (key_of(v) < cut) return;
+            const int at = atomicAdd(&sel.count, 1);
+            if (at < LIST) { sel.list_v[at] = v; sel.list_i[at] = i; }
+        });
+        __syncthreads();
+        const int n = sel.count;
+        if (n <= LIST) {
+            for (int e = tid; e < n; e += ST) sel.list_w[e] = weight_of<true>(sel.list_v[e], m);
+            __syncthreads();
+            unsigned cut2 = cut;
+            if (p.top_p < 1.0f && p.top_p > 0.f) {
+                u64 zl = 0;
+                for (int e = tid; e < n; e += ST) zl += sel.list_w[e];
+                const u64 zi = block_sum_u64(zl, sel.red64, tid);
+                u64 need_i = (u64)((double)p.top_p * (double)zi);
+                if (need_i < 1) need_i = 1;
+                for (int e = tid; e < n; e += ST) {
+                    const unsigned ke = key_of(sel.list_v[e]);
+                    u64 sum = 0;
+                    for (int j = 0; j < n; ++j) sum += key_of(sel.list_v[j]) >= ke ? sel.list_w[j] : 0ull;
+                    if (sum >= need_i) atomicMax(&sel.best, ke);
+                }
+                __syncthreads();
+                if (sel.best > cut2) cut2 = sel.best;
+            }
+            // probabilities of the survivors, then the draw in index order: element e stands at the
+            // number of survivors with a smaller index
+            for (int e = tid; e < n; e += ST) {
+                const float v = sel.list_v[e];
+                const float d = __fsub_rn(v, m);
+                float pe = (key_of(v) < cut2 || d < -87.0f) ? 0.f : expf(d);
+                if (pe < minp) pe = 0.f;
+                int rank = 0;
+                const int ie = sel.list_i[e];
+                for (int j = 0; j < n; ++j) rank += sel.list_i[j] < ie;
+                reinterpret_cast<float*>(sel.list_w)[rank] = pe;               // the weights are no longer needed
+                reinterpret_cast<int*>(sel.list_w)[LIST + rank] = ie;
+            }
+            __syncthreads();
+            if (tid == 0) {
+                const float* pr = reinterpret_cast<const float*>(sel.list_w);
+                const int* id = reinterpret_cast<const int*>(sel.list_w) + LIST;
+                float total = 0.f;
+                for (int j = 0; j < n; ++j) total += pr[j];
+                const unsigned long long r = mix64s(p.seed ^ mix64s(p.counter + counter_add + 0x632BE59BD9B4E019ull));
+                const float target = (float)(unsigned)(r >> 40) * (1.0f / 16777216.0f) * total;
+                float run = 0.f;
+                int pick = imax;
+                for (int j = 0; j < n; ++j) {
+                    if (pr[j] > 0.f) { run += pr[j]; pick = id[j]; if (target < run) break; }
+                }
+                out_ids[row] = pick;
+                if (ring) { my_ring[n_total % hist_cap] = pick; hist_len[p.recent_offset] = n_total + 1; }
+            }
+            return;
+        }
+    }
     // 7. top-p: the largest cut whose kept mass reaches p of the mass kept so far
     if (p.top_p < 1.0f && p.top_p > 0.f) {
         u64 zl = 0;
@@ -416,8 +482,7 @@ sample_kernel(const float* __restrict__ logits, long long ld, float* __restrict_
             t = search_cut<true>(x, sc, V, m, cut, need_i, sel, tid);
         cut = t > cut ? t : cut;
     }
-    // 8. min-p: drop p_i < min_p * p_max, i.e. exp(x_i - m) < min_p
-    const float minp = p.min_p > 0.f ? p.min_p : 0.f;
+    // 8. min-p: drop p_i < min_p * p_max, i.e. exp(x_i - m) < min_p (minp above)
     // 9. draw: inverse CDF in index order.  Warp w owns the stretch [w * C, (w + 1) * C) and reads it
     // row by row of 32 neighbours; the warp that holds the target walks its stretch once more.
     const int lane = tid & 31, warp = tid >> 5;
