@@ -132,6 +132,7 @@ def gemm(a, w, out, epilogue, w2, rt, splits: int | None = None, bn: int | None 
     T, K = a.shape
     N = w.shape[0]
     assert w.shape[1] == K and out.stride(-1) == 1
+    tile_given = bn is not None
     bn = bn or token_tile(T, epilogue)
     s = splits or k_splits(T, N, K, bn, epilogue)
     split_stride = 0
@@ -143,7 +144,7 @@ def gemm(a, w, out, epilogue, w2, rt, splits: int | None = None, bn: int | None 
         assert s == 1 or epilogue == EPI_ADD
         ldo = out.stride(0)
     L = lib()
-    if pairs(T, N, s, epilogue) and out.dim() == 2:
+    if not tile_given and out.dim() == 2 and pairs(T, N, s, epilogue):
         rc = L.ub_gemm_tc_pair(_tmap(w, 128), _tmap(a, 128), _ptr(out), BF16 if out.dtype == torch.bfloat16 else F32,
                                out.stride(0), T, N, K, epilogue, _ptr(rt.status[1:2]), _stream())
         return _check(rc, "gemm_tc_pair")
