@@ -274,6 +274,52 @@ __device__ unsigned search_cut(const float* x, float sc, int V, float m, unsigne
     return t;
 }
 
+// top-k in two passes when what lies at and above the cut's bucket is a handful: the count histogram
+// as above, then every element of those buckets (value and index) is copied to shared memory, where the
+// cut is the k-th largest of them.  The copied elements are what the rest of the ladder works on.
+// False (nothing changed that matters) when the bucket is not found or holds too much.
+__device__ bool topk_collect(const float* x, float sc, int V, float m, int k, SelectSmem& sm, int tid,
+                             unsigned& cut_out, int& n_out) {
+    sm.hist.u[tid] = 0;
+    __syncthreads();
+    visit(x, V, tid, [&](int, float raw) {
+        const float v = __fmul_rn(raw, sc);
+        int b, part;
+        place_of(v, m, b, part);
+        if (b < NB - 1) atomicAdd(&sm.hist.u[b], 1u);
+    });
+    __syncthreads();
+    first_reaching<unsigned>(sm, sm.hist.u, sm.warp_tot.u, (unsigned)k, tid);
+    const int b1 = sm.found_bucket;
+    if (b1 < 0) return false;
+    const unsigned expect = sm.found_above_u + sm.hist.u[b1];
+    if (expect > (unsigned)LIST) return false;
+    if (tid == 0) { sm.count = 0; sm.best = 0; }
+    __syncthreads();
+    visit(x, V, tid, [&](int i, float raw) {
+        const float v = __fmul_rn(raw, sc);
+        int b, part;
+        place_of(v, m, b, part);
+        if (b <= b1) {
+            const int at = atomicAdd(&sm.count, 1);
+            if (at < LIST) { sm.list_v[at] = v; sm.list_i[at] = i; }
+        }
+    });
+    __syncthreads();
+    const int n = sm.count;
+    if (n > LIST || n < k) return false;
+    for (int e = tid; e < n; e += ST) {
+        const unsigned ke = key_of(sm.list_v[e]);
+        int c = 0;
+        for (int j = 0; j < n; ++j) c += key_of(sm.list_v[j]) >= ke;
+        if (c >= k) atomicMax(&sm.best, ke);
+    }
+    __syncthreads();
+    cut_out = sm.best;
+    n_out = n;
+    return sm.best != 0;
+}
+
 __global__ void __launch_bounds__(ST)
 sample_kernel(const float* __restrict__ logits, long long ld, float* __restrict__ work, int V,
               const SampleParams* __restrict__ params, const int* __restrict__ recent_all,
@@ -396,28 +442,39 @@ sample_kernel(const float* __restrict__ logits, long long ld, float* __restrict_
     const float m = vmax * sc;
     unsigned cut = 0;                             // keep keys >= cut
     // 6. top-k: the largest cut that still keeps k elements
+    int n_list = -1;                              // >= 0: what top-k kept (and a few below it) lies in shared memory
     if (p.top_k > 0 && p.top_k < V) {
         unsigned t = 0;
-        if (!select_cut<false>(x, sc, V, m, 0u, (u64)p.top_k, sel, tid, t))
-            t = search_cut<false>(x, sc, V, m, 0u, (u64)p.top_k, sel, tid);
+        if (!topk_collect(x, sc, V, m, p.top_k, sel, tid, t, n_list)) {
+            n_list = -1;
+            __syncthreads();
+            if (!select_cut<false>(x, sc, V, m, 0u, (u64)p.top_k, sel, tid, t))
+                t = search_cut<false>(x, sc, V, m, 0u, (u64)p.top_k, sel, tid);
+        }
         cut = t;
     }
     const float minp = p.min_p > 0.f ? p.min_p : 0.f;
-    // What top-k left is usually a few dozen elements: they are copied to shared memory once and
-    // everything that follows (top-p, min-p, the draw) happens there instead of in passes over the row.
+    // What top-k left is usually a few dozen elements: once they are in shared memory, everything
+    // that follows (top-p, min-p, the draw) happens there instead of in passes over the row.
     if (cut != 0) {
-        if (tid == 0) { sel.count = 0; sel.best = 0; }
-        __syncthreads();
-        visit(x, V, tid, [&](int i, float raw) {
-            const float v = __fmul_rn(raw, sc);
-            if (key_of(v) < cut) return;
-            const int at = atomicAdd(&sel.count, 1);
-            if (at < LIST) { sel.list_v[at] = v; sel.list_i[at] = i; }
-        });
-        __syncthreads();
-        const int n = sel.count;
+        if (n_list < 0) {
+            if (tid == 0) { sel.count = 0; sel.best = 0; }
+            __syncthreads();
+            visit(x, V, tid, [&](int i, float raw) {
+                const float v = __fmul_rn(raw, sc);
+                if (key_of(v) < cut) return;
+                const int at = atomicAdd(&sel.count, 1);
+                if (at < LIST) { sel.list_v[at] = v; sel.list_i[at] = i; }
+            });
+            __syncthreads();
+            n_list = sel.count;
+        }
+        const int n = n_list;
         if (n <= LIST) {
-            for (int e = tid; e < n; e += ST) sel.list_w[e] = weight_of<true>(sel.list_v[e], m);
+            if (tid == 0) sel.best = 0;
+            // elements below the cut (the list may hold some) weigh nothing
+            for (int e = tid; e < n; e += ST)
+                sel.list_w[e] = key_of(sel.list_v[e]) >= cut ? weight_of<true>(sel.list_v[e], m) : 0ull;
             __syncthreads();
             unsigned cut2 = cut;
             if (p.top_p < 1.0f && p.top_p > 0.f) {
