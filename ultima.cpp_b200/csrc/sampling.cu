@@ -104,6 +104,7 @@ __device__ __forceinline__ void visit(const float* x, int V, int tid, F f) {
 // ---------------------------------------------------------------------------------------
 constexpr int NB = 1024;
 constexpr int LIST = 2048;
+constexpr int SMALL = 512;             // survivors that the rest of the ladder handles in shared memory (ranked pair by pair)
 constexpr float BUCKET_SCALE = (float)NB / 64.0f;
 constexpr float FIXED_ONE = 1099511627776.0f;              // 2^40
 typedef unsigned long long u64;
@@ -181,6 +182,10 @@ __device__ __forceinline__ void first_reaching(SelectSmem& sm, T* hist, T* warp_
 }
 
 template <bool MASS>
+__device__ bool select_in_bucket(const float* x, float sc, int V, float m, unsigned old_cut, u64 need, SelectSmem& sm,
+                                 int tid, int b1, float above1_f, unsigned above1_u, unsigned& cut_out);
+
+template <bool MASS>
 __device__ bool select_cut(const float* x, float sc, int V, float m, unsigned old_cut, u64 need, SelectSmem& sm,
                            int tid, unsigned& cut_out) {
     static_assert(NB == ST, "one thread a bucket");
@@ -203,9 +208,16 @@ __device__ bool select_cut(const float* x, float sc, int V, float m, unsigned ol
     if (MASS) first_reaching<float>(sm, sm.hist.f, sm.warp_tot.f, need_f, tid);
     else first_reaching<unsigned>(sm, sm.hist.u, sm.warp_tot.u, (unsigned)need, tid);
     const int b1 = sm.found_bucket;
-    const float above1_f = sm.found_above_f;
-    const unsigned above1_u = sm.found_above_u;
     if (b1 < 0) return false;
+    return select_in_bucket<MASS>(x, sc, V, m, old_cut, need, sm, tid, b1, sm.found_above_f, sm.found_above_u, cut_out);
+}
+
+// The second and third pass of the above, given the bucket b1 that holds the cut and what the
+// histogram summed before it.
+template <bool MASS>
+__device__ bool select_in_bucket(const float* x, float sc, int V, float m, unsigned old_cut, u64 need, SelectSmem& sm,
+                                 int tid, int b1, float above1_f, unsigned above1_u, unsigned& cut_out) {
+    const float need_f = (float)need * (1.0f / FIXED_ONE);
     // parts of that bucket
     __syncthreads();
     sm.hist.u[tid] = 0;
@@ -293,7 +305,7 @@ __device__ bool topk_collect(const float* x, float sc, int V, float m, int k, Se
     const int b1 = sm.found_bucket;
     if (b1 < 0) return false;
     const unsigned expect = sm.found_above_u + sm.hist.u[b1];
-    if (expect > (unsigned)LIST) return false;
+    if (expect > (unsigned)SMALL) return false;
     if (tid == 0) { sm.count = 0; sm.best = 0; }
     __syncthreads();
     visit(x, V, tid, [&](int i, float raw) {
@@ -307,7 +319,7 @@ __device__ bool topk_collect(const float* x, float sc, int V, float m, int k, Se
     });
     __syncthreads();
     const int n = sm.count;
-    if (n > LIST || n < k) return false;
+    if (n > SMALL || n < k) return false;
     for (int e = tid; e < n; e += ST) {
         const unsigned ke = key_of(sm.list_v[e]);
         int c = 0;
@@ -318,6 +330,57 @@ __device__ bool topk_collect(const float* x, float sc, int V, float m, int k, Se
     cut_out = sm.best;
     n_out = n;
     return sm.best != 0;
+}
+
+// top-p, first pass: the kept elements' total mass (exact) and the histogram of masses in one go, then
+// the bucket b1 where the mass reaches the need.  If the buckets down to b1 + 1 (one more for the
+// float sums' sake) hold little enough (a peaked distribution; counted in a pass of its own, no
+// atomics), their elements are copied to shared memory and n_out says how many: the caller finds
+// the cut among them with exact sums and checks that it is there.  Else n_out is -1 and the caller
+// goes on from b1 with the passes over the row.
+__device__ void topp_first(const float* x, float sc, int V, float m, unsigned old_cut, float top_p, SelectSmem& sm,
+                           int tid, u64& z_out, u64& need_out, int& b1_out, int& n_out) {
+    sm.hist.f[tid] = 0.f;
+    __syncthreads();
+    u64 zl = 0;
+    visit(x, V, tid, [&](int, float raw) {
+        const float v = __fmul_rn(raw, sc);
+        if (key_of(v) < old_cut) return;
+        zl += weight_of<true>(v, m);
+        int b, part;
+        place_of(v, m, b, part);
+        if (b < NB - 1) atomicAdd(&sm.hist.f[b], expf(__fsub_rn(v, m)));
+    });
+    const u64 z = block_sum_u64(zl, sm.red64, tid);
+    u64 need = (u64)((double)top_p * (double)z);
+    if (need < 1) need = 1;
+    first_reaching<float>(sm, sm.hist.f, sm.warp_tot.f, (float)need * (1.0f / FIXED_ONE), tid);
+    z_out = z; need_out = need; b1_out = sm.found_bucket; n_out = -1;
+    const int b1 = sm.found_bucket;
+    if (b1 < 0 || b1 + 1 >= NB - 1) return;
+    u64 mine = 0;
+    visit(x, V, tid, [&](int, float raw) {
+        const float v = __fmul_rn(raw, sc);
+        if (key_of(v) < old_cut) return;
+        int b, part;
+        place_of(v, m, b, part);
+        mine += b <= b1 + 1;
+    });
+    if (block_sum_u64(mine, sm.red64, tid) > (u64)SMALL) return;
+    if (tid == 0) { sm.count = 0; sm.best = 0; }
+    __syncthreads();
+    visit(x, V, tid, [&](int i, float raw) {
+        const float v = __fmul_rn(raw, sc);
+        if (key_of(v) < old_cut) return;
+        int b, part;
+        place_of(v, m, b, part);
+        if (b <= b1 + 1) {
+            const int at = atomicAdd(&sm.count, 1);
+            if (at < LIST) { sm.list_v[at] = v; sm.list_i[at] = i; }
+        }
+    });
+    __syncthreads();
+    n_out = sm.count <= SMALL ? sm.count : -1;
 }
 
 __global__ void __launch_bounds__(ST)
@@ -456,7 +519,14 @@ sample_kernel(const float* __restrict__ logits, long long ld, float* __restrict_
     const float minp = p.min_p > 0.f ? p.min_p : 0.f;
     // What top-k left is usually a few dozen elements: once they are in shared memory, everything
     // that follows (top-p, min-p, the draw) happens there instead of in passes over the row.
-    if (cut != 0) {
+    // top-p where top-k has left no list (it is off, or it kept too much): the first pass over the row,
+    // and a list if what top-p keeps is little
+    u64 z_all = 0, need_all = 0;                  // the kept elements' mass and the share of it that top-p asks for
+    int b1_p = -1;
+    const bool p_first = n_list < 0 && p.top_p < 1.0f && p.top_p > 0.f;
+    if (p_first) topp_first(x, sc, V, m, cut, p.top_p, sel, tid, z_all, need_all, b1_p, n_list);
+    __syncthreads();
+    if ((cut != 0 && !p_first) || n_list >= 0) {
         if (n_list < 0) {
             if (tid == 0) { sel.count = 0; sel.best = 0; }
             __syncthreads();
@@ -470,17 +540,19 @@ sample_kernel(const float* __restrict__ logits, long long ld, float* __restrict_
             n_list = sel.count;
         }
         const int n = n_list;
-        if (n <= LIST) {
+        if (n <= SMALL) {
             if (tid == 0) sel.best = 0;
             // elements below the cut (the list may hold some) weigh nothing
             for (int e = tid; e < n; e += ST)
                 sel.list_w[e] = key_of(sel.list_v[e]) >= cut ? weight_of<true>(sel.list_v[e], m) : 0ull;
             __syncthreads();
             unsigned cut2 = cut;
+            bool found = true;
             if (p.top_p < 1.0f && p.top_p > 0.f) {
                 u64 zl = 0;
                 for (int e = tid; e < n; e += ST) zl += sel.list_w[e];
-                const u64 zi = block_sum_u64(zl, sel.red64, tid);
+                u64 zi = block_sum_u64(zl, sel.red64, tid);
+                if (z_all) zi = z_all;
                 u64 need_i = (u64)((double)p.top_p * (double)zi);
                 if (need_i < 1) need_i = 1;
                 for (int e = tid; e < n; e += ST) {
@@ -491,7 +563,10 @@ sample_kernel(const float* __restrict__ logits, long long ld, float* __restrict_
                 }
                 __syncthreads();
                 if (sel.best > cut2) cut2 = sel.best;
+                found = sel.best != 0;            // the cut lies in the list (always, when the list is all that is kept)
             }
+            __syncthreads();
+            if (found) {
             // probabilities of the survivors, then the draw in index order: element e stands at the
             // number of survivors with a smaller index
             for (int e = tid; e < n; e += ST) {
@@ -522,21 +597,18 @@ sample_kernel(const float* __restrict__ logits, long long ld, float* __restrict_
                 if (ring) { my_ring[n_total % hist_cap] = pick; hist_len[p.recent_offset] = n_total + 1; }
             }
             return;
+            }
         }
     }
     // 7. top-p: the largest cut whose kept mass reaches p of the mass kept so far
     if (p.top_p < 1.0f && p.top_p > 0.f) {
-        u64 zl = 0;
-        visit(x, V, tid, [&](int, float raw) {
-            const float v = __fmul_rn(raw, sc);
-            zl += key_of(v) >= cut ? weight_of<true>(v, m) : 0ull;
-        });
-        const u64 zi = block_sum_u64(zl, sel.red64, tid);
-        u64 need_i = (u64)((double)p.top_p * (double)zi);
-        if (need_i < 1) need_i = 1;
+        // the first pass has been made (topp_first): on from its bucket
+        __syncthreads();
         unsigned t = cut;
-        if (!select_cut<true>(x, sc, V, m, cut, need_i, sel, tid, t))
-            t = search_cut<true>(x, sc, V, m, cut, need_i, sel, tid);
+        first_reaching<float>(sel, sel.hist.f, sel.warp_tot.f, (float)need_all * (1.0f / FIXED_ONE), tid);
+        bool ok = b1_p >= 0 && sel.found_bucket == b1_p;
+        if (ok) ok = select_in_bucket<true>(x, sc, V, m, cut, need_all, sel, tid, b1_p, sel.found_above_f, 0u, t);
+        if (!ok) t = search_cut<true>(x, sc, V, m, cut, need_all, sel, tid);
         cut = t > cut ? t : cut;
     }
     // 8. min-p: drop p_i < min_p * p_max, i.e. exp(x_i - m) < min_p (minp above)
@@ -618,3 +690,4 @@ UB_API int ub_sample(const float* logits, long long ld, float* work, int n_rows,
     return 0;
 }
 UB_API int ub_sample_params_size() { return (int)sizeof(SampleParams); }
+
