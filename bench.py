@@ -243,6 +243,49 @@ def prefill_timeline(engine, tokens, rng):
     return 0
 
 
+def attention_times(lengths=(2048, 4096, 8192, 16384), nh=32, nkv=8, hd=128):
+    """Device time of the prompt attention kernel alone (one sequence, causal, Qwen3-8B head counts), one
+    JSON line a prompt length: microseconds a launch and TFLOP/s of the causal half."""
+    import math
+    import torch
+    from ultima_b200.engine import Runtime
+    from ultima_b200.kernels import attn_tc
+    dev = torch.device("cuda:0")
+    rt = Runtime(dev, torch.bfloat16)
+
+    class Box:
+        pass
+    for T in lengths:
+        pages = (T + 63) // 64
+        kv = Box()
+        kv.k = torch.randn(pages, nkv, 64, hd, device=dev).to(torch.bfloat16)
+        kv.v = torch.randn(pages, nkv, 64, hd, device=dev).to(torch.bfloat16)
+        kv.table = torch.arange(pages, dtype=torch.int32, device=dev).view(1, -1)
+        kv.ring, kv.page, kv.window = pages * 64, 64, None
+        q = torch.randn(T, nh * hd, device=dev).to(torch.bfloat16)
+        out = torch.empty(T, nh * hd, dtype=torch.bfloat16, device=dev)
+        b = Box()
+        b.seq_start = torch.tensor([0, T], dtype=torch.int32, device=dev)
+        b.seq_before = torch.tensor([0], dtype=torch.int32, device=dev)
+        b.n_seqs, b.max_new, b.max_after = 1, T, T
+        def run():
+            attn_tc.attention(q, kv, out, b, nh, nkv, hd, 1 / math.sqrt(hd), rt)
+        for _ in range(3):
+            run()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        e0.record()
+        for _ in range(20):
+            run()
+        e1.record()
+        torch.cuda.synchronize()
+        rt.check_status()
+        us = e0.elapsed_time(e1) / 20 * 1e3
+        print(json.dumps({"only": "attention", "tokens": T, "heads": nh, "kv_heads": nkv, "head_dim": hd,
+                          "us": round(us, 1), "tflops_causal": round(4 * nh * hd * (T * (T + 1) / 2) / us / 1e6, 1)}))
+    return 0
+
+
 def sampling_times(batches=(1, 8, 64), vocab=151936, history=256):
     """Device time of the sampling kernel alone at the 8B vocabulary, for the reference's ladder
     of options (src/sampler/sampler.cpp:230-277): one JSON line a batch size, microseconds a call.
@@ -531,11 +574,11 @@ def main():
     ap.add_argument("--warmup", type=int, default=4)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--layers", type=int, default=0, help="fewer layers than the configuration (named in config)")
-    ap.add_argument("--only", default="all", choices=["all", "prefill", "decode", "timeline", "timeline-prefill", "sample"],
+    ap.add_argument("--only", default="all", choices=["all", "prefill", "decode", "timeline", "timeline-prefill", "sample", "attention"],
                     help="a part of the run only (for profiling); the JSON line then holds that part. "
                          "timeline: every kernel of a decode step with its begin and end inside the graph "
                          "(timeline-prefill: of a prompt); "
-                         "sample: the sampling kernel alone, option by option")
+                         "sample: the sampling kernel alone, option by option; attention: the prompt attention alone")
     ap.add_argument("--batch", type=int, default=BATCH, help="sequences of the decode step")
     ap.add_argument("--fast-fill", action="store_true", help="do not run the prompts; mark the cache as filled")
     ap.add_argument("--prompt", type=int, default=PROMPT, help="positions each sequence holds before the timed steps")
@@ -559,6 +602,8 @@ def main():
         args.steps = 64
     if args.only == "sample":
         return sampling_times()
+    if args.only == "attention":
+        return attention_times()
     if args.config != "8b":
         return run_other(args)
     return run_ours(args)
