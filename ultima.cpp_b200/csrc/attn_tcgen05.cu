@@ -65,11 +65,34 @@ __device__ __forceinline__ float ex2(float x) {
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
 }
+// Two float32 in a 64-bit register and the arithmetic on such pairs (one instruction for both), and the
+// maximum of three.
+__device__ __forceinline__ uint64_t pair_of(float a, float b) {
+    uint64_t r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(a), "f"(b));
+    return r;
+}
+__device__ __forceinline__ void halves_of(uint64_t v, float& a, float& b) { asm("mov.b64 {%0, %1}, %2;" : "=f"(a), "=f"(b) : "l"(v)); }
+__device__ __forceinline__ uint64_t fma_pair(uint64_t a, uint64_t b, uint64_t c) {
+    uint64_t d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+    return d;
+}
+__device__ __forceinline__ uint64_t add_pair(uint64_t a, uint64_t b) {
+    uint64_t d;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
+__device__ __forceinline__ float max3(float a, float b, float c) {
+    float d;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
+}
 // V tile as the N-major B operand: rows of 128 bytes are keys, 8 keys a swizzle atom (1024 bytes)
 __device__ __forceinline__ uint64_t make_desc_mn(uint32_t smem_addr) {
     uint64_t d = 0;
     d |= (uint64_t)((smem_addr & 0x3FFFF) >> 4);
-    d |= (uint64_t)((BN * 128) >> 4) << 16;                // next 64 columns (unused: one block an MMA)
+    d |= (uint64_t)((BN * 128) >> 4) << 16;                // next 64 columns
     d |= (uint64_t)(1024 >> 4) << 32;                      // next 8 keys
     d |= (uint64_t)1 << 46;
     d |= (uint64_t)2 << 61;
@@ -134,7 +157,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
             mbar_init(&k_full[s], 1); mbar_init(&k_empty[s], 1);
             mbar_init(&v_full[s], 1); mbar_init(&v_empty[s], 1);
         }
-        for (int b = 0; b < 2; ++b) { mbar_init(&s_full[b], 1); mbar_init(&p_full[b], 128); mbar_init(&pv_done[b], 1); }
+        for (int b = 0; b < 2; ++b) { mbar_init(&s_full[b], 1); mbar_init(&p_full[b], 4); mbar_init(&pv_done[b], 1); }
         *err = 0;
         fence_barrier_init();
     }
@@ -153,24 +176,42 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
                 for (int nb = 0; nb < NB; ++nb)
                     tma_load_3d(q_s + nb * BM * 128, &map_q, q_full, nb * 64, kvh * G, q0 + tok_first);
             }
+            // Keys and values have cursors of their own: a key tile's place is free as soon as its
+            // scores are formed, which is before the product with the values of the tile before it.
             bool ok = true;
             int armed_k = 0, armed_v = 0;
-            for (int j = 0; j < n_tiles && ok; ++j) {
-                const int s = j % KV_STAGES;
-                const uint32_t ph = (uint32_t)((j / KV_STAGES) & 1);
+            long long t_idle = -1;
+            auto row_of = [&](int j) {
                 const int posn = (t_lo + j) * BN;
                 const int page = p.table[(long long)seq * p.pages_per_seq + (posn % p.ring) / BN];
-                const int row = (page * p.nkv + kvh) * BN;
-                ok = mbar_wait(&k_empty[s], ph ^ 1, err);
-                if (!ok) break;
-                mbar_expect_tx(&k_full[s], KV_BYTES);
-                for (int nb = 0; nb < NB; ++nb) tma_load_2d(k_s + s * KV_BYTES + nb * BN * 128, &map_k, &k_full[s], nb * 64, row);
-                armed_k = j + 1;
-                ok = mbar_wait(&v_empty[s], ph ^ 1, err);
-                if (!ok) break;
-                mbar_expect_tx(&v_full[s], KV_BYTES);
-                for (int nb = 0; nb < NB; ++nb) tma_load_2d(v_s + s * KV_BYTES + nb * BN * 128, &map_v, &v_full[s], nb * 64, row);
-                armed_v = j + 1;
+                return (page * p.nkv + kvh) * BN;
+            };
+            while (armed_v < n_tiles && ok) {
+                bool moved = false;
+                if (armed_k < n_tiles) {
+                    const int j = armed_k, s = j % KV_STAGES;
+                    if (mbar_try_wait(&k_empty[s], (uint32_t)(((j / KV_STAGES) & 1) ^ 1))) {
+                        const int row = row_of(j);
+                        mbar_expect_tx(&k_full[s], KV_BYTES);
+                        for (int nb = 0; nb < NB; ++nb) tma_load_2d(k_s + s * KV_BYTES + nb * BN * 128, &map_k, &k_full[s], nb * 64, row);
+                        armed_k = j + 1;
+                        moved = true;
+                    }
+                }
+                if (armed_v < armed_k) {
+                    const int j = armed_v, s = j % KV_STAGES;
+                    if (mbar_try_wait(&v_empty[s], (uint32_t)(((j / KV_STAGES) & 1) ^ 1))) {
+                        const int row = row_of(j);
+                        mbar_expect_tx(&v_full[s], KV_BYTES);
+                        for (int nb = 0; nb < NB; ++nb) tma_load_2d(v_s + s * KV_BYTES + nb * BN * 128, &map_v, &v_full[s], nb * 64, row);
+                        armed_v = j + 1;
+                        moved = true;
+                    }
+                }
+                if (moved) { t_idle = -1; continue; }
+                if (*err) { ok = false; break; }
+                if (t_idle < 0) t_idle = clock64();
+                else if (clock64() - t_idle > WAIT_LIMIT_CYCLES) { *err = 1; ok = false; }
             }
             if (*err) {          // let the copies in flight land before the CTA's memory goes away
                 const long long tstart = clock64();
@@ -184,29 +225,34 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
     } else if (warp == 1) {
         // ---------------- MMA ----------------
         if (lane == 0) {
+            // Every descriptor is a constant away from three made once: the address field counts 16-byte
+            // units and shared memory ends far below where it would carry into the next field.
             constexpr uint32_t idesc_qk = idesc_bf16(BM, BN, 0);
-            constexpr uint32_t idesc_pv = idesc_bf16(BM, 64, 1);
-            const uint32_t q_addr = smem_u32(q_s);
+            constexpr uint32_t idesc_pv = idesc_bf16(BM, HD, 1);          // all HD output columns in one MMA
+            const uint64_t q_desc = make_desc(smem_u32(q_s));
+            const uint64_t k_desc = make_desc(smem_u32(k_s));
+            const uint64_t v_desc = make_desc_mn(smem_u32(v_s));
             auto issue_qk = [&](int j) {
                 const int s = j % KV_STAGES;
-                const uint32_t k_addr = smem_u32(k_s + s * KV_BYTES);
+                const uint64_t kd = k_desc + (uint64_t)(s * (KV_BYTES >> 4));
                 const uint32_t acc = tmem_base + (uint32_t)((j & 1) * BN);
 #pragma unroll
                 for (int ks = 0; ks < HD / 16; ++ks) {
-                    const uint64_t da = make_desc(q_addr + (ks / 4) * BM * 128) + (uint64_t)(((ks % 4) * 32) >> 4);
-                    const uint64_t db = make_desc(k_addr + (ks / 4) * BN * 128) + (uint64_t)(((ks % 4) * 32) >> 4);
+                    const uint64_t da = q_desc + (uint64_t)(((ks / 4) * BM * 128 + (ks % 4) * 32) >> 4);
+                    const uint64_t db = kd + (uint64_t)(((ks / 4) * BN * 128 + (ks % 4) * 32) >> 4);
                     tc_mma_bf16(acc, da, db, idesc_qk, ks > 0 ? 1u : 0u);
                 }
                 tc_commit(&s_full[j & 1]);
                 tc_commit(&k_empty[s]);
             };
+            // MMAs run in the order of their issue: the scores of tile j+1 may be queued over the place
+            // of tile j-1's probabilities as soon as the product that reads those has been issued.
             bool ok = n_tiles > 0 ? mbar_wait(q_full, 0, err) : true;
             if (ok && n_tiles > 0) ok = mbar_wait(&k_full[0], 0, err);
             if (ok && n_tiles > 0) { tc_fence_after(); issue_qk(0); }
             for (int j = 0; j < n_tiles && ok; ++j) {
                 if (j + 1 < n_tiles) {
-                    if (j >= 1) ok = mbar_wait(&pv_done[(j + 1) & 1], (uint32_t)(((j - 1) >> 1) & 1), err);   // P of tile j-1 used
-                    if (ok) ok = mbar_wait(&k_full[(j + 1) % KV_STAGES], (uint32_t)(((j + 1) / KV_STAGES) & 1), err);
+                    ok = mbar_wait(&k_full[(j + 1) % KV_STAGES], (uint32_t)(((j + 1) / KV_STAGES) & 1), err);
                     if (!ok) break;
                     tc_fence_after();
                     issue_qk(j + 1);
@@ -215,16 +261,12 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
                 if (ok) ok = mbar_wait(&v_full[j % KV_STAGES], (uint32_t)((j / KV_STAGES) & 1), err);
                 if (!ok) break;
                 tc_fence_after();
-                const uint32_t v_addr = smem_u32(v_s + (j % KV_STAGES) * KV_BYTES);
+                const uint64_t vd = v_desc + (uint64_t)((j % KV_STAGES) * (KV_BYTES >> 4));
                 const uint32_t p_t = tmem_base + (uint32_t)((j & 1) * BN);
 #pragma unroll
-                for (int ks = 0; ks < BN / 16; ++ks) {
-#pragma unroll
-                    for (int nb = 0; nb < NB; ++nb) {
-                        const uint64_t db = make_desc_mn(v_addr + nb * BN * 128 + ks * 16 * 128);
-                        tc_mma_bf16_ts(tmem_base + O_COL + nb * 64, p_t + ks * 8, db, idesc_pv, (j > 0 || ks > 0) ? 1u : 0u);
-                    }
-                }
+                for (int ks = 0; ks < BN / 16; ++ks)
+                    tc_mma_bf16_ts(tmem_base + O_COL, p_t + ks * 8, vd + (uint64_t)((ks * 16 * 128) >> 4), idesc_pv,
+                                   (j > 0 || ks > 0) ? 1u : 0u);
                 tc_commit(&pv_done[j & 1]);
                 tc_commit(&v_empty[j % KV_STAGES]);
             }
@@ -264,21 +306,22 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
             tmem_ld_wait();
             // scores stay raw (q.k); the scale goes into the exponent: p = 2^(s c - m).  A tile that
             // every row of the CTA sees whole needs no mask.
-            float mx = -INFINITY;
             const bool whole = row_ok && base + BN - 1 <= before + tok_first && p.window <= 0 && r < TPB * G;
-            if (__all_sync(0xffffffffu, whole)) {
-#pragma unroll
-                for (int cI = 0; cI < BN; ++cI) mx = fmaxf(mx, __uint_as_float(raw[cI]));
-            } else {
+            if (!__all_sync(0xffffffffu, whole)) {
 #pragma unroll
                 for (int cI = 0; cI < BN; ++cI) {
                     const int kp = base + cI;
                     const bool vis = row_ok && kp <= row_pos && (p.window <= 0 || kp > row_pos - p.window);
-                    const float v = vis ? __uint_as_float(raw[cI]) : -INFINITY;
-                    raw[cI] = __float_as_uint(v);
-                    mx = fmaxf(mx, v);
+                    if (!vis) raw[cI] = __float_as_uint(-INFINITY);
                 }
             }
+            float mxs[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};   // four chains of three-input maxima
+#pragma unroll
+            for (int cI = 0; cI < BN; cI += 8)
+#pragma unroll
+                for (int ch = 0; ch < 4; ++ch)
+                    mxs[ch] = max3(mxs[ch], __uint_as_float(raw[cI + 2 * ch]), __uint_as_float(raw[cI + 2 * ch + 1]));
+            float mx = fmaxf(fmaxf(mxs[0], mxs[1]), fmaxf(mxs[2], mxs[3]));
             mx *= p.c;                                       // c > 0: the maximum in exponent units
             // raise the reference maximum only when it lags by more than RESCALE_STEP (or is not set)
             const bool grow = mx > m_ref + RESCALE_STEP || (m_ref == -INFINITY && mx > -INFINITY);
@@ -305,19 +348,26 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
             }
             const float mb = m_ref == -INFINITY ? 0.f : m_ref;
             uint32_t packed[BN / 2];
-            float sum = 0.f;
+            const uint64_t c2 = pair_of(p.c, p.c), shift2 = pair_of(-mb, -mb);
+            uint64_t sums[2] = {pair_of(0.f, 0.f), pair_of(0.f, 0.f)};
 #pragma unroll
             for (int cI = 0; cI < BN; cI += 2) {
-                const float p0 = ex2(fmaf(__uint_as_float(raw[cI]), p.c, -mb)), p1 = ex2(fmaf(__uint_as_float(raw[cI + 1]), p.c, -mb));
-                sum += p0 + p1;
+                float x0, x1;
+                halves_of(fma_pair(pair_of(__uint_as_float(raw[cI]), __uint_as_float(raw[cI + 1])), c2, shift2), x0, x1);
+                const float p0 = ex2(x0), p1 = ex2(x1);
+                sums[(cI >> 1) & 1] = add_pair(sums[(cI >> 1) & 1], pair_of(p0, p1));
                 __nv_bfloat162 pr = __floats2bfloat162_rn(p0, p1);
                 packed[cI / 2] = *reinterpret_cast<uint32_t*>(&pr);
             }
-            l += sum;
+            float s0, s1, s2, s3;
+            halves_of(sums[0], s0, s1);
+            halves_of(sums[1], s2, s3);
+            l += (s0 + s1) + (s2 + s3);
             tmem_st32(lane_addr + (uint32_t)(b * BN), packed);
             tmem_st_wait();
             tc_fence_before();
-            mbar_arrive(&p_full[b]);
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&p_full[b]);         // one arrival a warp
         }
         if (ok && n_tiles > 0) ok = mbar_wait(&pv_done[(n_tiles - 1) & 1], (uint32_t)(((n_tiles - 1) >> 1) & 1), err);
         if (ok) {
