@@ -444,13 +444,19 @@ def test_attn_mma_prefill(cfg):
                                  dict(nh=32, nkv=2, hd=128, window=0), dict(nh=2, nkv=1, hd=128, window=130),
                                  dict(nh=10, nkv=2, hd=128, window=0), dict(nh=6, nkv=2, hd=64, window=0),
                                  dict(nh=7, nkv=1, hd=64, window=33)])
-def test_attn_tcgen05_prefill(cfg):
-    """The tcgen05 prefill kernel: scores and output in tensor memory."""
+@pytest.mark.parametrize("wide", [0, 2])
+def test_attn_tcgen05_prefill(cfg, wide):
+    """The tcgen05 prefill kernels (128 and 256 rows a CTA): scores and output in tensor memory."""
     from ultima_b200.kernels import attn_tc
     assert attn_tc.tcgen05_fits(cfg["hd"], cfg["nh"], cfg["nkv"])
-    for befores, news in (([0, 0, 0, 0], [1, 17, 64, 200]), ([5, 64, 130, 0], [70, 1, 33, 129]), ([0], [700])):
-        err = _attn_tc_case(cfg["nh"], cfg["nkv"], cfg["hd"], cfg["window"], befores, news, seed=cfg["hd"] + 3)
-        assert err <= 2 ** -7, (cfg, befores, news, err)
+    was = attn_tc.WIDE
+    attn_tc.set_wide(wide)
+    try:
+        for befores, news in (([0, 0, 0, 0], [1, 17, 64, 200]), ([5, 64, 130, 0], [70, 1, 33, 129]), ([0], [700])):
+            err = _attn_tc_case(cfg["nh"], cfg["nkv"], cfg["hd"], cfg["window"], befores, news, seed=cfg["hd"] + 3)
+            assert err <= 2 ** -7, (cfg, befores, news, err)
+    finally:
+        attn_tc.set_wide(was)
 
 
 @pytest.mark.parametrize("cfg", [dict(nh=8, nkv=2, hd=128, window=0), dict(nh=8, nkv=1, hd=64, window=0),
@@ -463,10 +469,13 @@ def test_attn_tcgen05_decode(cfg, slices):
     assert err <= 2 ** -7, (cfg, slices, err)
 
 
-def test_attn_tcgen05_rescales_when_the_maximum_grows():
+@pytest.mark.parametrize("wide", [0, 2])
+def test_attn_tcgen05_rescales_when_the_maximum_grows(wide):
     """Keys whose scores grow along the sequence force the reference maximum up again and again."""
     from ultima_b200.kernels import attn_tc
     from ultima_b200.engine import Runtime
+    was = attn_tc.WIDE
+    attn_tc.set_wide(wide)
     rt = Runtime(DEV, torch.bfloat16)
     nh = nkv = 1
     hd, n = 128, 400
@@ -492,6 +501,7 @@ def test_attn_tcgen05_rescales_when_the_maximum_grows():
     torch.cuda.synchronize()
     rt.check_status()
     kd, vd = kc[:, 0].reshape(-1, hd)[:n].double(), vc[:, 0].reshape(-1, hd)[:n].double()
+    attn_tc.set_wide(was)
     for t in (0, 63, 64, 200, 399):
         s = (kd[:t + 1] @ q[t].double().cpu()) / math.sqrt(hd)
         ref = torch.softmax(s, 0) @ vd[:t + 1]

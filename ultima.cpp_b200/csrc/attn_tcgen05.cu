@@ -14,7 +14,10 @@
 // than 2^8 (then the row's output and sum are rescaled in tensor memory), so most tiles cost no
 // pass over the output.  Rows of V the sequence has not reached are zeroed in shared memory.
 // Warp 0 issues TMA, warp 1 issues MMAs and owns the tensor-memory allocation, warps 2-5 are the
-// softmax.  Every wait has a time limit and raises a flag.
+// softmax.  Every wait has a time limit and raises a flag.  The issuing thread never waits for its
+// own MMAs: they run in the order of their issue, so the scores of tile j+1 are queued right behind
+// the product that reads the buffer they fall into.  Long prompts take a second kernel further
+// down, attn_tc_wide_kernel, with 256 rows (two such tiles of rows) a CTA.
 //
 // The arithmetic restated is the reference's per-token loop (src/model/qwen_block.cpp:94-135):
 // scores q.k * scale over the visible positions (p - window, p], max-shifted softmax, weighted
@@ -418,6 +421,355 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
 }
 
 // ---------------------------------------------------------------------------------------
+// Prompts, 256 rows a CTA: two query tiles of 128 rows share every key and value tile, so a tile is
+// fetched from the L2 and written to shared memory once for both, and five such tiles can be in
+// flight.  One CTA an SM with all of its tensor memory: tile t has its scores in columns
+// [128 t, 128 t + 128) (two buffers) and its output in [256 + 128 t, ...).  Warp 0 issues TMA,
+// warps 1 and 2 issue one tile's MMAs each (MMAs of one thread run in the order of their issue, which
+// is what lets a tile's next scores be queued behind the product that reads the buffer they fall
+// into), warps 4-7 and 8-11 are the two tiles' softmax.  A key tile's place is given back when both
+// issuers have let go of it; an issuer whose rows do not see a tile lets go of it at once.
+constexpr int WIDE_TILES = 2;
+constexpr int WIDE_STAGES = HD == 128 ? 4 : 8;
+constexpr int WIDE_THREADS = 384;
+constexpr int WIDE_TMEM = 512;
+constexpr int WIDE_O_COL = 256;
+constexpr int WIDE_MIN_BLOCKS = 148;         // fewer blocks than SMs: the kernel of 128 rows a CTA spreads the work further
+constexpr int wide_smem_bytes() { return WIDE_TILES * Q_BYTES + 2 * WIDE_STAGES * KV_BYTES + 1024 + 512; }
+
+__global__ void __launch_bounds__(WIDE_THREADS, 1)
+attn_tc_wide_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                    const __grid_constant__ CUtensorMap map_v, TcAttnParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    constexpr int S = WIDE_STAGES;
+    pdl_trigger();
+    pdl_wait();
+    const int per_tile = p.n_seqs * p.nkv;
+    const int seq = (blockIdx.x % per_tile) / p.nkv;
+    const int kvh = blockIdx.x % p.nkv;
+    const int q0 = p.seq_start[seq], q_len = p.seq_start[seq + 1] - q0, before = p.seq_before[seq];
+    const int G = p.group;
+    const int TPB = BM / G;                                // tokens a query tile
+    const int wide_tile = p.n_row_tiles - 1 - blockIdx.x / per_tile;     // longest first
+    const int tok_first = wide_tile * WIDE_TILES * TPB;
+    if (tok_first >= q_len) return;
+
+    uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint8_t* q_s = smem;
+    uint8_t* k_s = q_s + WIDE_TILES * Q_BYTES;
+    uint8_t* v_s = k_s + S * KV_BYTES;
+    uint64_t* bars = (uint64_t*)(v_s + S * KV_BYTES);
+    uint64_t* q_full = bars;                               // [2]
+    uint64_t* k_full = q_full + WIDE_TILES;
+    uint64_t* k_empty = k_full + S;
+    uint64_t* v_full = k_empty + S;
+    uint64_t* v_empty = v_full + S;
+    uint64_t* s_full = v_empty + S;                        // [tile][2]
+    uint64_t* p_full = s_full + 2 * WIDE_TILES;
+    uint64_t* pv_done = p_full + 2 * WIDE_TILES;
+    uint32_t* tmem_slot = (uint32_t*)(pv_done + 2 * WIDE_TILES);
+    volatile int* err = (volatile int*)(tmem_slot + 1);
+    static_assert((WIDE_TILES + 4 * WIDE_STAGES + 6 * WIDE_TILES) * 8 + 8 <= 512, "barriers outgrew their place");
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int last_pos = before + q_len - 1;
+    // what each query tile sees: tiles [lo, hi] of the sequence's keys; the CTA walks their union
+    int lo[WIDE_TILES], hi[WIDE_TILES], tokf[WIDE_TILES];
+    bool has[WIDE_TILES];
+#pragma unroll
+    for (int t = 0; t < WIDE_TILES; ++t) {
+        tokf[t] = tok_first + t * TPB;
+        has[t] = tokf[t] < q_len;
+        const int tokl = min(q_len - 1, tokf[t] + TPB - 1);
+        hi[t] = (before + tokl) / BN;
+        lo[t] = p.window > 0 ? max(0, before + tokf[t] - p.window + 1) / BN : 0;
+    }
+    const int t_lo = lo[0];
+    const int t_hi = has[1] ? hi[1] : hi[0];
+    const int n_union = t_hi - t_lo + 1;
+
+    if (threadIdx.x == 0) {
+        for (int t = 0; t < WIDE_TILES; ++t) mbar_init(&q_full[t], 1);
+        for (int s = 0; s < S; ++s) {
+            mbar_init(&k_full[s], 1); mbar_init(&k_empty[s], WIDE_TILES);
+            mbar_init(&v_full[s], 1); mbar_init(&v_empty[s], WIDE_TILES);
+        }
+        for (int b = 0; b < 2 * WIDE_TILES; ++b) { mbar_init(&s_full[b], 1); mbar_init(&p_full[b], 4); mbar_init(&pv_done[b], 1); }
+        *err = 0;
+        fence_barrier_init();
+    }
+    if (warp == 1) { tmem_alloc(tmem_slot, WIDE_TMEM); tmem_relinquish(); }
+    if (warp == 0 && lane == 0) { prefetch_tmap(&map_q); prefetch_tmap(&map_k); prefetch_tmap(&map_v); }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        // ---------------- TMA ----------------
+        if (lane == 0) {
+#pragma unroll
+            for (int t = 0; t < WIDE_TILES; ++t)
+                if (has[t]) {
+                    mbar_expect_tx(&q_full[t], NB * TPB * G * 128);
+                    for (int nb = 0; nb < NB; ++nb)
+                        tma_load_3d(q_s + t * Q_BYTES + nb * BM * 128, &map_q, &q_full[t], nb * 64, kvh * G, q0 + tokf[t]);
+                }
+            bool ok = true;
+            int armed_k = 0, armed_v = 0;
+            long long t_idle = -1;
+            auto row_of = [&](int j) {
+                const int posn = (t_lo + j) * BN;
+                const int page = p.table[(long long)seq * p.pages_per_seq + (posn % p.ring) / BN];
+                return (page * p.nkv + kvh) * BN;
+            };
+            while (armed_v < n_union && ok) {
+                bool moved = false;
+                if (armed_k < n_union) {
+                    const int j = armed_k, s = j % S;
+                    if (mbar_try_wait(&k_empty[s], (uint32_t)(((j / S) & 1) ^ 1))) {
+                        const int row = row_of(j);
+                        mbar_expect_tx(&k_full[s], KV_BYTES);
+                        for (int nb = 0; nb < NB; ++nb) tma_load_2d(k_s + s * KV_BYTES + nb * BN * 128, &map_k, &k_full[s], nb * 64, row);
+                        armed_k = j + 1;
+                        moved = true;
+                    }
+                }
+                if (armed_v < armed_k) {
+                    const int j = armed_v, s = j % S;
+                    if (mbar_try_wait(&v_empty[s], (uint32_t)(((j / S) & 1) ^ 1))) {
+                        const int row = row_of(j);
+                        mbar_expect_tx(&v_full[s], KV_BYTES);
+                        for (int nb = 0; nb < NB; ++nb) tma_load_2d(v_s + s * KV_BYTES + nb * BN * 128, &map_v, &v_full[s], nb * 64, row);
+                        armed_v = j + 1;
+                        moved = true;
+                    }
+                }
+                if (moved) { t_idle = -1; continue; }
+                if (*err) { ok = false; break; }
+                if (t_idle < 0) t_idle = clock64();
+                else if (clock64() - t_idle > WAIT_LIMIT_CYCLES) { *err = 1; ok = false; }
+            }
+            if (*err) {          // let the copies in flight land before the CTA's memory goes away
+                const long long tstart = clock64();
+                for (int t = 0; t < WIDE_TILES; ++t)
+                    while (has[t] && !mbar_try_wait(&q_full[t], 0)) if (clock64() - tstart > WAIT_LIMIT_CYCLES / 8) break;
+                for (int j = max(0, armed_k - S); j < armed_k; ++j)
+                    while (!mbar_try_wait(&k_full[j % S], (j / S) & 1)) if (clock64() - tstart > WAIT_LIMIT_CYCLES / 4) break;
+                for (int j = max(0, armed_v - S); j < armed_v; ++j)
+                    while (!mbar_try_wait(&v_full[j % S], (j / S) & 1)) if (clock64() - tstart > WAIT_LIMIT_CYCLES / 4) break;
+            }
+        }
+    } else if (warp == 1 || warp == 2) {
+        // ---------------- MMA, one query tile a warp ----------------
+        if (lane == 0) {
+            const int t = warp - 1;
+            const int first = has[t] ? lo[t] - t_lo : 0;
+            const int n_act = has[t] ? hi[t] - lo[t] + 1 : 0;
+            constexpr uint32_t idesc_qk = idesc_bf16(BM, BN, 0);
+            constexpr uint32_t idesc_pv = idesc_bf16(BM, HD, 1);
+            const uint64_t q_desc = make_desc(smem_u32(q_s + t * Q_BYTES));
+            const uint64_t k_desc = make_desc(smem_u32(k_s));
+            const uint64_t v_desc = make_desc_mn(smem_u32(v_s));
+            const uint32_t s_base = tmem_base + (uint32_t)(t * 2 * BN);
+            const uint32_t o_base = tmem_base + (uint32_t)(WIDE_O_COL + t * HD);
+            uint64_t* sf = s_full + 2 * t;
+            uint64_t* pf = p_full + 2 * t;
+            uint64_t* pd = pv_done + 2 * t;
+            bool ok = true;
+            // a tile of keys these rows do not see: wait until it is there (which keeps this thread's
+            // arrivals in step with the loads), then give its place back
+            auto pass_by = [&](int j) {
+                const int s = j % S;
+                const uint32_t ph = (uint32_t)((j / S) & 1);
+                ok = mbar_wait(&k_full[s], ph, err);
+                if (!ok) return;
+                mbar_arrive(&k_empty[s]);
+                ok = mbar_wait(&v_full[s], ph, err);
+                if (!ok) return;
+                mbar_arrive(&v_empty[s]);
+            };
+            auto issue_qk = [&](int i) {                   // i counts this tile's own key tiles
+                const int j = first + i, s = j % S;
+                const uint64_t kd = k_desc + (uint64_t)(s * (KV_BYTES >> 4));
+                const uint32_t acc = s_base + (uint32_t)((i & 1) * BN);
+#pragma unroll
+                for (int ks = 0; ks < HD / 16; ++ks) {
+                    const uint64_t da = q_desc + (uint64_t)(((ks / 4) * BM * 128 + (ks % 4) * 32) >> 4);
+                    const uint64_t db = kd + (uint64_t)(((ks / 4) * BN * 128 + (ks % 4) * 32) >> 4);
+                    tc_mma_bf16(acc, da, db, idesc_qk, ks > 0 ? 1u : 0u);
+                }
+                tc_commit(&sf[i & 1]);
+                tc_commit(&k_empty[s]);
+            };
+            for (int j = 0; j < first && ok; ++j) pass_by(j);
+            if (ok && n_act > 0) ok = mbar_wait(&q_full[t], 0, err);
+            if (ok && n_act > 0) ok = mbar_wait(&k_full[first % S], (uint32_t)((first / S) & 1), err);
+            if (ok && n_act > 0) { tc_fence_after(); issue_qk(0); }
+            for (int i = 0; i < n_act && ok; ++i) {
+                const int j = first + i;
+                if (i + 1 < n_act) {
+                    ok = mbar_wait(&k_full[(j + 1) % S], (uint32_t)(((j + 1) / S) & 1), err);
+                    if (!ok) break;
+                    tc_fence_after();
+                    issue_qk(i + 1);
+                }
+                ok = mbar_wait(&pf[i & 1], (uint32_t)((i >> 1) & 1), err);
+                if (ok) ok = mbar_wait(&v_full[j % S], (uint32_t)((j / S) & 1), err);
+                if (!ok) break;
+                tc_fence_after();
+                const uint64_t vd = v_desc + (uint64_t)((j % S) * (KV_BYTES >> 4));
+                const uint32_t p_t = s_base + (uint32_t)((i & 1) * BN);
+#pragma unroll
+                for (int ks = 0; ks < BN / 16; ++ks)
+                    tc_mma_bf16_ts(o_base, p_t + ks * 8, vd + (uint64_t)((ks * 16 * 128) >> 4), idesc_pv, (i > 0 || ks > 0) ? 1u : 0u);
+                tc_commit(&pd[i & 1]);
+                tc_commit(&v_empty[j % S]);
+            }
+            for (int j = first + n_act; j < n_union && ok; ++j) pass_by(j);
+        }
+    } else if (warp >= 4) {
+        // ---------------- softmax: one thread a row, four warps a query tile ----------------
+        const int t = (warp - 4) >> 2;
+        const int q = warp & 3;
+        const int r = q * 32 + lane;                       // row of the tile = lane of tensor memory
+        const int tok = tokf[t] + r / G, g = r % G;
+        const bool row_ok = has[t] && r < TPB * G && tok < q_len;
+        const int row_pos = before + tok;
+        const int first = has[t] ? lo[t] - t_lo : 0;
+        const int n_act = has[t] ? hi[t] - lo[t] + 1 : 0;
+        const uint32_t lane_addr = tmem_base + ((uint32_t)(q * 32) << 16);
+        const uint32_t s_base = lane_addr + (uint32_t)(t * 2 * BN);
+        const uint32_t o_base = lane_addr + (uint32_t)(WIDE_O_COL + t * HD);
+        uint64_t* sf = s_full + 2 * t;
+        uint64_t* pf = p_full + 2 * t;
+        uint64_t* pd = pv_done + 2 * t;
+        const int st = (warp & 3) * 32 + lane;             // 0..127 among the tile's softmax threads
+        float m_ref = -INFINITY, l = 0.f;
+        bool ok = true;
+        for (int i = 0; i < n_act && ok; ++i) {
+            const int b = i & 1;
+            const int j = first + i;
+            const int base = (t_lo + j) * BN;
+            if (base + BN - 1 > last_pos) {
+                // rows of V past the sequence's end hold whatever the page held before: make them zero
+                // (both query tiles do, before their own products with this tile)
+                ok = mbar_wait(&v_full[j % S], (uint32_t)((j / S) & 1), err);
+                if (!ok) break;
+                const int zfirst = last_pos + 1 - base;    // first row to clear (>= 1: the tile holds a valid key)
+                uint8_t* vt = v_s + (j % S) * KV_BYTES;
+                for (int x = st; x < (BN - zfirst) * NB * 8; x += 128) {
+                    const int row = zfirst + x / (NB * 8), rest = x % (NB * 8);
+                    *reinterpret_cast<uint4*>(vt + (rest / 8) * BN * 128 + row * 128 + (rest % 8) * 16) = make_uint4(0, 0, 0, 0);
+                }
+                fence_proxy_async();
+            }
+            ok = mbar_wait(&sf[b], (uint32_t)((i >> 1) & 1), err);
+            if (!ok) break;
+            tc_fence_after();
+            uint32_t raw[BN];
+            tmem_ld32(s_base + (uint32_t)(b * BN), raw);
+            tmem_ld32(s_base + (uint32_t)(b * BN + 32), raw + 32);
+            tmem_ld_wait();
+            const bool whole = row_ok && base + BN - 1 <= before + tokf[t] && p.window <= 0;
+            if (!__all_sync(0xffffffffu, whole)) {
+#pragma unroll
+                for (int cI = 0; cI < BN; ++cI) {
+                    const int kp = base + cI;
+                    const bool vis = row_ok && kp <= row_pos && (p.window <= 0 || kp > row_pos - p.window);
+                    if (!vis) raw[cI] = __float_as_uint(-INFINITY);
+                }
+            }
+            float mxs[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+            for (int cI = 0; cI < BN; cI += 8)
+#pragma unroll
+                for (int ch = 0; ch < 4; ++ch)
+                    mxs[ch] = max3(mxs[ch], __uint_as_float(raw[cI + 2 * ch]), __uint_as_float(raw[cI + 2 * ch + 1]));
+            float mx = fmaxf(fmaxf(mxs[0], mxs[1]), fmaxf(mxs[2], mxs[3]));
+            mx *= p.c;
+            const bool grow = mx > m_ref + RESCALE_STEP || (m_ref == -INFINITY && mx > -INFINITY);
+            if (__any_sync(0xffffffffu, grow)) {
+                const float m_new = grow ? mx : m_ref;
+                const float f = (m_ref == -INFINITY || !grow) ? (grow ? 0.f : 1.f) : exp2f(m_ref - m_new);
+                if (i > 0) {
+                    ok = mbar_wait(&pd[(i - 1) & 1], (uint32_t)(((i - 1) >> 1) & 1), err);   // O is at rest
+                    if (!ok) break;
+                    tc_fence_after();
+#pragma unroll
+                    for (int cb = 0; cb < HD / 32; ++cb) {
+                        uint32_t oo[32];
+                        tmem_ld32(o_base + (uint32_t)(cb * 32), oo);
+                        tmem_ld_wait();
+#pragma unroll
+                        for (int x = 0; x < 32; ++x) oo[x] = __float_as_uint(__uint_as_float(oo[x]) * f);
+                        tmem_st32(o_base + (uint32_t)(cb * 32), oo);
+                    }
+                    tmem_st_wait();
+                }
+                l *= f;
+                m_ref = m_new;
+            }
+            const float mb = m_ref == -INFINITY ? 0.f : m_ref;
+            uint32_t packed[BN / 2];
+            const uint64_t c2 = pair_of(p.c, p.c), shift2 = pair_of(-mb, -mb);
+            uint64_t sums[2] = {pair_of(0.f, 0.f), pair_of(0.f, 0.f)};
+#pragma unroll
+            for (int cI = 0; cI < BN; cI += 2) {
+                float x0, x1;
+                halves_of(fma_pair(pair_of(__uint_as_float(raw[cI]), __uint_as_float(raw[cI + 1])), c2, shift2), x0, x1);
+                const float p0 = ex2(x0), p1 = ex2(x1);
+                sums[(cI >> 1) & 1] = add_pair(sums[(cI >> 1) & 1], pair_of(p0, p1));
+                __nv_bfloat162 pr = __floats2bfloat162_rn(p0, p1);
+                packed[cI / 2] = *reinterpret_cast<uint32_t*>(&pr);
+            }
+            float s0, s1, s2, s3;
+            halves_of(sums[0], s0, s1);
+            halves_of(sums[1], s2, s3);
+            l += (s0 + s1) + (s2 + s3);
+            tmem_st32(s_base + (uint32_t)(b * BN), packed);
+            tmem_st_wait();
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&pf[b]);
+        }
+        if (ok && n_act > 0) ok = mbar_wait(&pd[(n_act - 1) & 1], (uint32_t)(((n_act - 1) >> 1) & 1), err);
+        if (ok && n_act > 0) {
+            tc_fence_after();
+            const float inv = l > 0.f ? 1.0f / l : 0.f;
+            const int head = kvh * G + g;
+            bf16* dst = p.out + (long long)(q0 + tok) * p.o_stride + (long long)head * HD;
+#pragma unroll
+            for (int cb = 0; cb < HD / 32; ++cb) {
+                uint32_t oo[32];
+                tmem_ld32(o_base + (uint32_t)(cb * 32), oo);
+                tmem_ld_wait();
+                if (row_ok) {
+#pragma unroll
+                    for (int x = 0; x < 32; x += 8) {
+                        uint4 w;
+                        __nv_bfloat162 a0 = __floats2bfloat162_rn(__uint_as_float(oo[x]) * inv, __uint_as_float(oo[x + 1]) * inv);
+                        __nv_bfloat162 a1 = __floats2bfloat162_rn(__uint_as_float(oo[x + 2]) * inv, __uint_as_float(oo[x + 3]) * inv);
+                        __nv_bfloat162 a2 = __floats2bfloat162_rn(__uint_as_float(oo[x + 4]) * inv, __uint_as_float(oo[x + 5]) * inv);
+                        __nv_bfloat162 a3 = __floats2bfloat162_rn(__uint_as_float(oo[x + 6]) * inv, __uint_as_float(oo[x + 7]) * inv);
+                        w.x = *reinterpret_cast<uint32_t*>(&a0); w.y = *reinterpret_cast<uint32_t*>(&a1);
+                        w.z = *reinterpret_cast<uint32_t*>(&a2); w.w = *reinterpret_cast<uint32_t*>(&a3);
+                        *reinterpret_cast<uint4*>(dst + cb * 32 + x) = w;
+                    }
+                }
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, WIDE_TMEM);
+    }
+    if (threadIdx.x == 0 && *err) atomicExch(p.error, 1);
+}
+
+// ---------------------------------------------------------------------------------------
 UB_API int ub_attn_tc_head_dim() { return HD; }
 
 // tensor map of q as [tokens, heads, HD] (row stride q_stride elements), boxes of 64 x group x floor(128/group)
@@ -482,6 +834,21 @@ static int launch_attn(dim3 grid, const void* map_q, const void* map_k, const vo
     return (int)e;
 }
 
+static int g_wide = 1;
+// 1 (the default): prompts take the kernel of 256 rows a CTA when that gives every SM a CTA; 0: never; 2: always
+UB_API void ub_attn_tc_set_wide(int on) { g_wide = on; }
+
+static int launch_wide(unsigned blocks, const void* map_q, const void* map_k, const void* map_v, const TcAttnParams& p, cudaStream_t st) {
+    static bool attr_done = false;
+    if (!attr_done) {
+        cudaError_t e = cudaFuncSetAttribute(attn_tc_wide_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, wide_smem_bytes());
+        if (e != cudaSuccess) return (int)e;
+        attr_done = true;
+    }
+    return (int)ub_launch_dependent(attn_tc_wide_kernel, dim3(blocks), dim3(WIDE_THREADS), (size_t)wide_smem_bytes(), st,
+                                    *(const CUtensorMap*)map_q, *(const CUtensorMap*)map_k, *(const CUtensorMap*)map_v, p);
+}
+
 // mode 0: prompts (any numbers of new tokens); mode 1: one new token a sequence, keys in n_slices slices
 // (part_o: float32 [n_seqs, nh, n_slices, HD], part_ml: [.., 2] when n_slices > 1).
 UB_API int ub_attn_tc(int mode, const void* map_q, const void* map_k, const void* map_v, void* out, long long o_stride,
@@ -503,6 +870,12 @@ UB_API int ub_attn_tc(int mode, const void* map_q, const void* map_k, const void
         p.n_slices = 1;
         const int tpb = BM / group;
         p.n_seqs = n_seqs;
+        const long long wide_tiles = (max_new + WIDE_TILES * tpb - 1) / (WIDE_TILES * tpb);
+        const long long wide_blocks = wide_tiles * n_seqs * nkv;
+        if ((g_wide == 2 || (g_wide == 1 && wide_blocks >= WIDE_MIN_BLOCKS)) && wide_blocks <= 0x7fffffffll) {
+            p.n_row_tiles = (int)wide_tiles;
+            return launch_wide((unsigned)wide_blocks, map_q, map_k, map_v, p, st);
+        }
         p.n_row_tiles = (max_new + tpb - 1) / tpb;
         const long long blocks = (long long)p.n_row_tiles * n_seqs * nkv;
         if (blocks > 0x7fffffffll) return UB_ERR_ARG;

@@ -55,6 +55,9 @@ _tc_maps: dict = {}
 USE_TCGEN05 = _os.environ.get("ULTIMA_ATTN_TCGEN05", "1") != "0"
 USE_TCGEN05_DECODE = _os.environ.get("ULTIMA_ATTN_TCGEN05_DECODE", "0") != "0"
 USE_TMA_DECODE = _os.environ.get("ULTIMA_ATTN_TMA_DECODE", "1") != "0"
+# prompts on the tcgen05 kernel: 1 = 256 rows a CTA when that still gives every SM a CTA, 0 = always 128 rows
+# a CTA, 2 = always 256
+WIDE = int(_os.environ.get("ULTIMA_ATTN_WIDE", "1"))
 
 
 def tc_target(head_dim: int):
@@ -73,8 +76,19 @@ def tc_lib(head_dim: int):
                                  c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p,
                                  c_void_p, c_void_p, c_void_p]
         L.ub_attn_tc.restype = c_int
+        L.ub_attn_tc_set_wide.argtypes = [c_int]
+        L.ub_attn_tc_set_wide.restype = None
+        L.ub_attn_tc_set_wide(WIDE)
         _tc_libs[head_dim] = L
     return L
+
+
+def set_wide(mode: int) -> None:
+    """Choose between the two prompt kernels (see ``WIDE``) in every library loaded so far and later."""
+    global WIDE
+    WIDE = int(mode)
+    for L in _tc_libs.values():
+        L.ub_attn_tc_set_wide(WIDE)
 
 
 def tcgen05_fits(head_dim: int, n_heads: int, n_kv_heads: int) -> bool:
