@@ -121,6 +121,51 @@ def fill_cache(engine, slots, n_tokens):
         engine.cache.commit(s, n_tokens)
 
 
+def measured_peaks():
+    """What this GPU gives a plain device-to-device copy (bytes read + bytes written a second, 4 GiB a
+    buffer) and the library's bfloat16 product (8192^3, a burst of 20 and a loop of about two seconds):
+    the same kind of figures as the denominators in MEASURED_PEAKS.json, for the box a run was taken on.
+    Nothing of the library under test runs here."""
+    import torch
+    dev = torch.device("cuda:0")
+    torch.cuda.set_device(dev)
+    n = 1 << 30
+    a = torch.empty(n, dtype=torch.float32, device=dev).normal_()
+    b = torch.empty_like(a)
+
+    def timed(fn, reps):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(reps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / reps
+
+    for _ in range(3):
+        b.copy_(a)
+    copy_ms = timed(lambda: b.copy_(a), 10)
+    copy_gbs = 2 * a.numel() * 4 / (copy_ms * 1e-3) / 1e9
+    del a, b
+    m = 8192
+    x = torch.randn(m, m, device=dev, dtype=torch.bfloat16)
+    y = torch.randn(m, m, device=dev, dtype=torch.bfloat16)
+    out = torch.empty(m, m, device=dev, dtype=torch.bfloat16)
+    for _ in range(5):
+        torch.matmul(x, y, out=out)
+    burst_ms = timed(lambda: torch.matmul(x, y, out=out), 20)
+    flop = 2.0 * m * m * m
+    reps = max(20, int(2000 / burst_ms))
+    clocks = ClockSampler()
+    clocks.start()
+    loop_ms = timed(lambda: torch.matmul(x, y, out=out), reps)
+    clk = clocks.stop()
+    print(json.dumps({"only": "peaks", "copy_gbs": round(copy_gbs, 1), "bf16_tflops_burst": round(flop / burst_ms / 1e9, 1),
+                      "bf16_tflops_loop": round(flop / loop_ms / 1e9, 1), "loop_reps": reps, "clocks": clk,
+                      "in_use": peaks()}))
+    return 0
+
+
 def timed_decode(engine, sampler, batch, steps, warmup, rng, real_prefill, prompt_len=PROMPT, spread=None):
     import torch
     from ultima_b200.sampling import SamplingParams
@@ -574,11 +619,12 @@ def main():
     ap.add_argument("--warmup", type=int, default=4)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--layers", type=int, default=0, help="fewer layers than the configuration (named in config)")
-    ap.add_argument("--only", default="all", choices=["all", "prefill", "decode", "timeline", "timeline-prefill", "sample", "attention"],
+    ap.add_argument("--only", default="all", choices=["all", "prefill", "decode", "timeline", "timeline-prefill", "sample", "attention", "peaks"],
                     help="a part of the run only (for profiling); the JSON line then holds that part. "
                          "timeline: every kernel of a decode step with its begin and end inside the graph "
                          "(timeline-prefill: of a prompt); "
-                         "sample: the sampling kernel alone, option by option; attention: the prompt attention alone")
+                         "sample: the sampling kernel alone, option by option; attention: the prompt attention alone; "
+                         "peaks: this GPU's copy bandwidth and library bfloat16 product, the denominators' kind")
     ap.add_argument("--batch", type=int, default=BATCH, help="sequences of the decode step")
     ap.add_argument("--fast-fill", action="store_true", help="do not run the prompts; mark the cache as filled")
     ap.add_argument("--prompt", type=int, default=PROMPT, help="positions each sequence holds before the timed steps")
@@ -604,6 +650,8 @@ def main():
         return sampling_times()
     if args.only == "attention":
         return attention_times()
+    if args.only == "peaks":
+        return measured_peaks()
     if args.config != "8b":
         return run_other(args)
     return run_ours(args)
