@@ -166,51 +166,66 @@ def measured_peaks():
     return 0
 
 
-def timed_decode(engine, sampler, batch, steps, warmup, rng, real_prefill, prompt_len=PROMPT, spread=None):
+def prefill_slots(engine, slots, prompt_len, rng):
+    """Run a prompt of ``prompt_len`` random token ids into every slot, one prompt a step (keeps the
+    scratch memory of a step small)."""
+    V = engine.spec.vocab_size
+    for s in slots:
+        engine.step([s], [rng.integers(0, V, size=prompt_len).tolist()], [[]])
+
+
+def timed_decode(engine, sampler, slots, steps, warmup, rng, spread=None):
+    """``steps`` decode steps of the sequences in ``slots`` (already holding their prompts), as
+    generation runs them: the sampler draws from a step's logits (greedy, through ``Sampler``) and
+    leaves the ids on the device, the next step takes them from there (``Engine.step_fed``), the ids
+    also start on their way to the host.  Timed on the device between two events, no host wait
+    inside.  Returns (ms, kernels launched, mean positions a sequence held during the timed steps)."""
     import torch
     from ultima_b200.sampling import SamplingParams
+    from ultima_b200.sampling.sampler import stream_seed
     V = engine.spec.vocab_size
-    slots = engine.open(batch)
-    if real_prefill:
-        prompts = [rng.integers(0, V, size=prompt_len).tolist() for _ in range(batch)]
-        for i in range(batch):             # one prompt a step keeps scratch memory small
-            engine.step([slots[i]], [prompts[i]], [[]])
-    else:
-        fill_cache(engine, slots, prompt_len)
-    toks = rng.integers(0, V, size=(warmup + steps, batch))
-    params = [SamplingParams()] * batch
-    out_ids = torch.empty(batch, dtype=torch.int32, device=engine.device)
-    prm = sampler_params(sampler, params, engine.device)
+    B = len(slots)
+    params = [SamplingParams()] * B
+    streams = [stream_seed(0, i) for i in range(B)]
+    state = {"n": 0, "pend": None, "logits": None}
 
-    def one(i):
-        logits = engine.step(slots, [[int(t)] for t in toks[i]], None, borrow=True)
-        sampler_launch(logits, prm, out_ids)
-    for i in range(warmup):
-        one(i)
+    def one():
+        if state["pend"] is None:
+            logits = engine.step(slots, [[int(t)] for t in rng.integers(0, V, size=B)], None, borrow=True)
+        else:
+            logits = engine.step_fed(slots, state["pend"].ids_dev)
+        state["pend"] = sampler.begin(logits, params, streams, [state["n"]] * B, None, continuing=state["n"] > 0)
+        state["logits"] = logits
+        state["n"] += 1
+    for _ in range(warmup):
+        one()
     torch.cuda.synchronize()
+    ctx0 = engine.length(slots[0])
     l0 = engine.rt.launches
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
-    for i in range(warmup, warmup + steps):
-        one(i)
+    for _ in range(steps):
+        one()
     e1.record()
     torch.cuda.synchronize()
     ms = e0.elapsed_time(e1)
-    launches = engine.rt.launches - l0 + steps
-    ctx = engine.length(slots[0])
+    launches = engine.rt.launches - l0 + steps            # the engine's kernels and one sampling kernel a step
+    ids = state["pend"].wait()
+    if not bool(torch.isfinite(state["logits"]).all()) or min(ids) < 0 or max(ids) >= V:
+        raise RuntimeError("decode step gave logits that are not finite, or a token id outside the vocabulary")
+    ctx = ctx0 + steps / 2
     if spread is not None:
         # how even the steps are: a few more of them, each between two events of its own
-        n = min(32, steps, toks.shape[0])
+        n = min(32, steps)
         evs = [torch.cuda.Event(enable_timing=True) for _ in range(n + 1)]
         evs[0].record()
         for i in range(n):
-            one(i)
+            one()
             evs[i + 1].record()
         torch.cuda.synchronize()
         each = sorted(evs[i].elapsed_time(evs[i + 1]) for i in range(n))
         spread.update({"p10": round(each[n // 10], 4), "median": round(each[n // 2], 4),
                        "p90": round(each[(9 * n) // 10], 4), "steps": n})
-    engine.close(slots)
     return ms, launches, ctx
 
 
@@ -377,23 +392,6 @@ def sampling_times(batches=(1, 8, 64), vocab=151936, history=256):
     return 0
 
 
-def sampler_params(sampler, params, device):
-    """Records of greedy sampling for ``len(params)`` rows, on the device."""
-    import numpy as np
-    import torch
-    from ultima_b200.kernels import ops
-    rec = np.zeros(len(params), dtype=ops.SAMPLE_DTYPE)
-    rec["temperature"] = 0.0
-    rec["rep_penalty"] = 1.0
-    rec["top_p"] = 1.0
-    return torch.from_numpy(rec.view(np.uint8).reshape(-1)).to(device)
-
-
-def sampler_launch(logits, prm, out_ids):
-    from ultima_b200.kernels import ops
-    ops.sample(logits, None, prm, None, None, None, out_ids)
-
-
 def run_ours(args):
     import numpy as np
     import torch
@@ -414,12 +412,21 @@ def run_ours(args):
     spec = u.model_spec_for(cfg)
     t0 = time.time()
     tensors = random_tensors_on_device(spec.weight_specs(), 0, torch.bfloat16, dev)
-    # the cache holds the largest point: 64 sequences of a 2,048-token prompt plus the steps
-    per_seq = -(-(max(args.prompt, PROMPT) + args.warmup + args.steps + 64) // 64) * 64
-    n_seq = max(64, args.batch) if args.only == "all" else args.batch
+    run = args.warmup + args.steps
+    whole = args.only == "all"
+    # the far end of the metric: prompts long enough that three timed runs (batch 64, 8, 1, one after
+    # another on the same sequences) end just below the context of 8,192 positions
+    far_prompt = (CONTEXT - 3 * run - 40) // 64 * 64
+    if whole and far_prompt < PROMPT:
+        raise SystemExit(f"bench.py: --steps {args.steps} leaves no room for the points near {CONTEXT} positions")
+    if whole:
+        n_seq, per_seq = 64, CONTEXT
+    else:
+        n_seq = args.batch
+        per_seq = -(-(max(args.prompt, PROMPT) + run + 64) // 64) * 64
     engine = Engine(spec, tensors, dtype="bfloat16", max_tokens=max(n_seq * per_seq, args.prefill_tokens + 64),
                     max_seqs=n_seq, max_step_tokens=max(PREFILL_TOKENS, min(args.prefill_tokens, 8192)),
-                    max_context=max(CONTEXT, args.prompt + args.steps + args.warmup + 64, args.prefill_tokens))
+                    max_context=max(CONTEXT, args.prompt + run + 64, args.prefill_tokens))
     del tensors
     sampler = Sampler(dev, cfg.vocab_size, engine.rt)
     rng = np.random.default_rng(0)
@@ -431,14 +438,24 @@ def run_ours(args):
     if args.only == "timeline-prefill":
         return prefill_timeline(engine, args.prefill_tokens, rng)
 
+    wbytes = weight_bytes(cfg)
+    kvb = kv_bytes_per_token(cfg, 2)
+
+    def frac_of(batch, ctx, ms_step):
+        return (wbytes + batch * ctx * kvb) / (ms_step * 1e-3) / 1e9 / pk["hbm_gbs"]
+
     if args.only == "decode":
-        ms, launches, ctx = timed_decode(engine, sampler, args.batch, args.steps, args.warmup, rng,
-                                         real_prefill=not args.fast_fill, prompt_len=args.prompt)
+        slots = engine.open(args.batch)
+        if args.fast_fill:
+            fill_cache(engine, slots, args.prompt)
+        else:
+            prefill_slots(engine, slots, args.prompt, rng)
+        ms, launches, ctx = timed_decode(engine, sampler, slots, args.steps, args.warmup, rng)
+        engine.close(slots)
         engine.check_errors()
-        sb = weight_bytes(cfg) + args.batch * (ctx - args.steps / 2) * kv_bytes_per_token(cfg, 2)
         print(json.dumps({"only": "decode", "batch": args.batch, "layers": cfg.num_hidden_layers,
                           "ms_per_step": round(ms / args.steps, 4), "context": int(ctx),
-                          "hbm_frac": round(sb / (ms / args.steps * 1e-3) / 1e9 / pk["hbm_gbs"], 4),
+                          "hbm_frac": round(frac_of(args.batch, ctx, ms / args.steps), 4),
                           "value": round(args.batch * args.steps / ms * 1e3, 1), "gpu_launches": int(launches)}))
         return 0
 
@@ -469,23 +486,39 @@ def run_ours(args):
         print(json.dumps({"only": "prefill", "layers": cfg.num_hidden_layers, **prefill}))
         return 0
 
+    # the headline: batch 8 from 2,048-token prompts
+    slots = engine.open(BATCH)
+    prefill_slots(engine, slots, PROMPT, rng)
     clocks = ClockSampler()
     clocks.start()
     spread = {}
-    ms, launches, ctx = timed_decode(engine, sampler, BATCH, args.steps, args.warmup, rng, real_prefill=True,
-                                     spread=spread)
+    ms, launches, ctx = timed_decode(engine, sampler, slots, args.steps, args.warmup, rng, spread=spread)
     clk = clocks.stop()
+    engine.close(slots)
     value = BATCH * args.steps / ms * 1e3
-    wbytes = weight_bytes(cfg)
-    step_bytes = wbytes + BATCH * (ctx - args.steps / 2) * kv_bytes_per_token(cfg, 2)
-    achieved = step_bytes / (ms / args.steps * 1e-3) / 1e9
+    achieved = (wbytes + BATCH * ctx * kvb) / (ms / args.steps * 1e-3) / 1e9
     print(f"[bench] decode b{BATCH}: {value:.1f} tok/s", file=sys.stderr, flush=True)
 
-    points = {}
-    for b in (1, 64):
-        pm, _, _ = timed_decode(engine, sampler, b, args.steps, args.warmup, rng, real_prefill=False)
-        points[f"decode_b{b}"] = round(b * args.steps / pm * 1e3, 1)
-        print(f"[bench] decode b{b}: {points[f'decode_b{b}']} tok/s", file=sys.stderr, flush=True)
+    # the other points: 64 sequences that have really run their prompts, then 8 and 1 of the same
+    # sequences; first from 2,048-token prompts, then near the end of the context
+    points, point_frac, point_ctx = {}, {}, {}
+    for tag, plen, batches in (("", PROMPT, (64, 1)), ("_ctx8k", far_prompt, (64, 8, 1))):
+        slots = engine.open(64)
+        tp = time.time()
+        prefill_slots(engine, slots, plen, rng)
+        torch.cuda.synchronize()
+        print(f"[bench] 64 prompts of {plen} tokens in {time.time() - tp:.1f} s", file=sys.stderr, flush=True)
+        for b in batches:
+            engine.close(slots[b:])
+            slots = slots[:b]
+            pm, _, pctx = timed_decode(engine, sampler, slots, args.steps, args.warmup, rng)
+            key = f"decode_b{b}{tag}"
+            points[key] = round(b * args.steps / pm * 1e3, 1)
+            point_frac[key] = round(frac_of(b, pctx, pm / args.steps), 4)
+            point_ctx[key] = int(pctx)
+            print(f"[bench] {key}: {points[key]} tok/s at {int(pctx)} positions, {point_frac[key]} of the copy bandwidth",
+                  file=sys.stderr, flush=True)
+        engine.close(slots)
 
     # end to end through the generation loop: host token ids in, sampled ids out, every step
     prompts = [rng.integers(0, cfg.vocab_size, size=PROMPT).tolist() for _ in range(BATCH)]
@@ -497,8 +530,10 @@ def run_ours(args):
     e2e_val = BATCH * (n_new - 1) / stats.decode_s
     h2d = engine.last_h2d_bytes                   # the step's record (ids, positions, page tables); the
     # sampler's records stay on the device while a batch samples with the same parameters
+    dev_ms = sorted(stats.device_step_ms)
     e2e = {"value": round(e2e_val, 1), "unit": "tokens/s", "h2d_bytes_per_step": int(h2d),
-           "d2h_bytes_per_step": 4 * (BATCH + 4)}          # the sampled ids and the kernels' status flags
+           "d2h_bytes_per_step": 4 * (BATCH + 4),          # the sampled ids and the kernels' status flags
+           "device_ms_per_step": round(dev_ms[len(dev_ms) // 2], 4) if dev_ms else None}
 
     engine.check_errors()
     out = {
@@ -517,7 +552,7 @@ def run_ours(args):
         "e2e": e2e, "gpu_launches": int(launches), "clocks": clk, "prefill": prefill,
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
                      "frac": round(achieved / pk["hbm_gbs"], 4)},
-        "points": points, "step_ms": spread, "impl": "ours",
+        "points": points, "points_hbm_frac": point_frac, "points_context": point_ctx, "step_ms": spread, "impl": "ours",
     }
     print(json.dumps(out), flush=True)
     return 0
@@ -564,22 +599,9 @@ def run_other(args):
     torch.cuda.synchronize()
     pre_ms = e0.elapsed_time(e1)
     print(f"[bench] {args.config}: {sum(lens)} prompt tokens in {pre_ms:.1f} ms", file=sys.stderr, flush=True)
-    toks = rng.integers(0, cfg.vocab_size, size=(args.warmup + steps, B))
-    prm = sampler_params(sampler, [None] * B, dev)
-    out_ids = torch.empty(B, dtype=torch.int32, device=dev)
-    def one(i):
-        sampler_launch(engine.step(slots, [[int(t)] for t in toks[i]], None, borrow=True), prm, out_ids)
-    for i in range(args.warmup):
-        one(i)
     clocks = ClockSampler()
     clocks.start()
-    torch.cuda.synchronize()
-    e0.record()
-    for i in range(args.warmup, args.warmup + steps):
-        one(i)
-    e1.record()
-    torch.cuda.synchronize()
-    ms = e0.elapsed_time(e1)
+    ms, _, _ = timed_decode(engine, sampler, slots, steps, args.warmup, rng)
     clk = clocks.stop()
     print(f"[bench] {args.config}: {steps} decode steps in {ms:.1f} ms", file=sys.stderr, flush=True)
     engine.check_errors()

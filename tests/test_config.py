@@ -104,8 +104,10 @@ def test_registry_unknown_and_unsupported_are_two_errors():
 def test_model_description_is_data():
     spec = u.model_spec_for(config_from_dict(TINY_C))
     assert len(spec.layers) == 4 and [r.layer for r in spec.runs] == [0, 1, 2, 3]
-    assert [L.mixer.get("window") for L in spec.layers] == [20, None, 20, None]
-    assert spec.layers[0].mixer.get("head_dim") == 48 and spec.layers[0].feed_forward.get("inner") == 176
+    assert [L.part("mixer").get("window") for L in spec.layers] == [20, None, 20, None]
+    assert spec.layers[0].part("mixer").get("head_dim") == 48 and spec.layers[0].part("feed_forward").get("inner") == 176
+    assert spec.layers[0].roles() == {"mixer_norm": "norm", "mixer": "mixer", "feed_forward_norm": "norm",
+                                      "feed_forward": "feed_forward"}
     names = {s.name: s.shape for s in spec.weight_specs()}
     assert names["model.layers.3.self_attn.q_proj.weight"] == (6 * 48, 80)
     assert names["model.layers.0.self_attn.k_norm.weight"] == (48,)
@@ -128,3 +130,52 @@ def test_stop_tokens_come_from_both_json_files(tmp_path):
         json.dump({"eos_token_id": "x"}, f)
     with pytest.raises(ConfigError, match="eos_token_id"):
         u.config_from_dir(str(tmp_path))
+
+
+def test_an_architecture_enters_the_table_only_with_the_whole_protocol():
+    """What the engine asks of a configuration class and of build_spec is checked at registration."""
+    from dataclasses import dataclass
+    from ultima_b200.config import ArchitectureConfig
+
+    @dataclass(frozen=True)
+    class NoToDict:
+        architecture: str = "ToyLM"
+        max_position_embeddings: int = 8
+        torch_dtype: str = "float32"
+
+        @classmethod
+        def from_dict(cls, d):
+            return cls()
+
+    with pytest.raises(ConfigError, match="lacks to_dict"):
+        register_architecture(ArchitectureEntry("ToyLM", "toy_lm", True, "", NoToDict, lambda c, max_positions=None: None))
+
+    @dataclass(frozen=True)
+    class Whole(NoToDict):
+        def to_dict(self):
+            return {}
+
+    with pytest.raises(ConfigError, match="build_spec must be callable as"):
+        register_architecture(ArchitectureEntry("ToyLM", "toy_lm", True, "", Whole, lambda c: None))
+    assert isinstance(Whole(), ArchitectureConfig) and isinstance(config_from_dict(TINY_A), ArchitectureConfig)
+    with pytest.raises(ConfigError, match="unknown architecture"):
+        find_architecture("ToyLM")                         # neither attempt left anything in the table
+
+
+def test_a_layer_names_its_parts_by_the_roles_of_its_arrangement():
+    from ultima_b200.parts import layer, part
+    norm = part("rms", width=8, eps=1e-6)
+    ffn = part("gated_silu", width=8, inner=16)
+    att = part("attention", width=8, n_heads=1, n_kv_heads=1, head_dim=8, qk_norm=False, eps=1e-6, position=None)
+    L = layer(part("pre_norm"), prefix="x.", names={"mixer": "attn."}, mixer=att, feed_forward=ffn, mixer_norm=norm,
+              feed_forward_norm=norm)
+    assert L.name_of("mixer") == "x.attn." and L.name_of("feed_forward") == "x.feed_forward."
+    assert L.part("feed_forward") == ffn and list(L.roles()) == ["mixer_norm", "mixer", "feed_forward_norm", "feed_forward"]
+    with pytest.raises(KeyError, match="needs a part in the role 'mixer_norm'"):
+        layer(part("pre_norm"), mixer=att, feed_forward=ffn, feed_forward_norm=norm)
+    with pytest.raises(KeyError, match="has no role 'gate'"):
+        layer(part("pre_norm"), mixer=att, feed_forward=ffn, mixer_norm=norm, feed_forward_norm=norm, gate=norm)
+    with pytest.raises(KeyError, match="has no part in the role 'gate'"):
+        L.part("gate")
+    with pytest.raises(KeyError, match="no arrangement named 'sandwich'"):
+        layer(part("sandwich"), mixer=att)

@@ -277,6 +277,101 @@ def test_qk_prepare_for_prompts(cfg, dtype):
         assert rel_err(vc[pg, :, p % 64], v_ref[t]) <= (0 if dtype == torch.float32 else tol)
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("cfg", [dict(nh=4, nkv=2, hd=128, rd=64, inter=False), dict(nh=3, nkv=1, hd=64, rd=64, inter=True),
+                                 dict(nh=5, nkv=5, hd=48, rd=20, inter=True), dict(nh=2, nkv=1, hd=256, rd=96, inter=False),
+                                 dict(nh=2, nkv=2, hd=16, rd=2, inter=False)])
+def test_qk_prepare_rotates_part_of_a_head_and_interleaved_pairs(cfg, dtype):
+    """The first ``rd`` columns of a head rotated in pairs (j, j + rd/2) or (2j, 2j + 1), the rest passing
+    through (normed all the same); and the dense route: keys and values to matrices of their own instead
+    of the cache, then ``kv_write`` into the pages, which must give the cache the direct route gives."""
+    ops = _ops()
+    nh, nkv, hd, rd, inter = cfg["nh"], cfg["nkv"], cfg["hd"], cfg["rd"], cfg["inter"]
+    eps, theta, rhalf = 1e-5, 1e4, cfg["rd"] // 2
+    toks = [(0, 0), (0, 1), (1, 63), (1, 64), (2, 150), (2, 151), (2, 152)]
+    T = len(toks)
+    g = torch.Generator().manual_seed(hd + rd)
+    qkv = torch.randn(T, (nh + 2 * nkv) * hd, generator=g).to(dtype)
+    qw, kw = 1 + 0.1 * torch.randn(hd, generator=g), 1 + 0.1 * torch.randn(hd, generator=g)
+    ang = torch.arange(200, dtype=torch.float64)[:, None] / theta ** (2.0 * torch.arange(rhalf, dtype=torch.float64) / rd)[None]
+    cos, sin = torch.cos(ang).float().to(DEV), torch.sin(ang).float().to(DEV)
+    table = torch.tensor([[5, 1, 6], [0, 7, 4], [3, 2, 8]], dtype=torch.int32, device=DEV)
+    pos = torch.tensor([p for _, p in toks], dtype=torch.int32, device=DEV)
+    seq = torch.tensor([s for s, _ in toks], dtype=torch.int32, device=DEV)
+
+    def prep(x, w, p):          # x [heads, hd] float64
+        x = x * w.double() / torch.sqrt((x * x).mean(-1, keepdim=True) + eps)
+        c, s_ = torch.cos(ang[p])[None], torch.sin(ang[p])[None]
+        y = x.clone()
+        if inter:
+            a, b = x[:, 0:rd:2], x[:, 1:rd:2]
+            y[:, 0:rd:2], y[:, 1:rd:2] = a * c - b * s_, a * s_ + b * c
+        else:
+            a, b = x[:, :rhalf], x[:, rhalf:rd]
+            y[:, :rhalf], y[:, rhalf:rd] = a * c - b * s_, a * s_ + b * c
+        return y
+    kc = torch.zeros(9, nkv, 64, hd, dtype=dtype, device=DEV)
+    vc = torch.zeros_like(kc)
+    q = torch.full((T, nh * hd), float("nan"), dtype=dtype, device=DEV)
+    ops.qk_prepare(qkv.to(DEV), qw.to(DEV), kw.to(DEV), cos, sin, pos, seq, kc, vc, table, 192, 64, nh, nkv, hd, eps,
+                   q_out=q, rotary_dim=rd, interleaved=inter)
+    tol = 1e-5 if dtype == torch.float32 else 2 ** -7
+    for t, (s_i, p) in enumerate(toks):
+        row = qkv[t].double()
+        assert rel_err(q[t].view(nh, hd), prep(row[:nh * hd].view(nh, hd), qw, p)) <= tol, (cfg, t)
+        pg = int(table[s_i, p // 64])
+        assert rel_err(kc[pg, :, p % 64], prep(row[nh * hd:(nh + nkv) * hd].view(nkv, hd), kw, p)) <= tol, (cfg, t)
+        assert rel_err(vc[pg, :, p % 64], row[(nh + nkv) * hd:].view(nkv, hd)) <= (0 if dtype == torch.float32 else tol)
+    # the dense route: norm here, rotation by a call of its own, then the write into the pages
+    kc2, vc2 = torch.zeros_like(kc), torch.zeros_like(vc)
+    q2 = torch.full((T, nh * hd), float("nan"), dtype=dtype, device=DEV)
+    kbuf = torch.full((2, T, nkv * hd), float("nan"), dtype=dtype, device=DEV)
+    ops.qk_prepare(qkv.to(DEV), qw.to(DEV), kw.to(DEV), None, None, pos, seq, kc2, vc2, table, 192, 64, nh, nkv, hd, eps,
+                   q_out=q2, kv_out=(kbuf[0], kbuf[1]))
+    assert float(kc2.abs().sum()) == 0 and float(vc2.abs().sum()) == 0           # nothing went into the cache yet
+    ops.rotate_pairs(q2.view(T, nh, hd), cos, sin, pos, rd, inter)
+    ops.rotate_pairs(kbuf[0].view(T, nkv, hd), cos, sin, pos, rd, inter)
+    ops.kv_write(kbuf[0], kbuf[1], pos, seq, kc2, vc2, table, 192, 64, nkv, hd)
+    two = 2e-6 if dtype == torch.float32 else 2 ** -6            # bfloat16: rounded once more between norm and rotation
+    assert rel_err(q2, q.double()) <= two and rel_err(kc2, kc.double()) <= two
+    assert torch.equal(vc2, vc)
+    with pytest.raises(ops.KernelError, match="rotary size"):
+        ops.qk_prepare(qkv.to(DEV), qw.to(DEV), kw.to(DEV), cos, sin, pos, seq, kc, vc, table, 192, 64, nh, nkv, hd, eps,
+                       q_out=q, rotary_dim=hd + 2)
+
+
+def test_fill_normal_is_the_host_generator_bit_for_bit():
+    """The fill kernel against the tests' own copy of the counter-based generator (tests/plain_random.py):
+    the same bits in float32, and the same after rounding to bfloat16."""
+    import plain_random as R
+    ops = _ops()
+    n = 300000
+    for key, shift, std in ((R.tensor_key(7, "model.embed_tokens.weight"), 0.0, 0.02), (12345, 1.0, 0.05), ((1 << 63) - 1, 0.0, 1.0)):
+        want = (np.float32(shift) + np.float32(std) * R.normal_array(key, n)).astype(np.float32)
+        got = torch.empty(n, device=DEV)
+        ops.fill_normal(got, key, shift, std)
+        assert np.array_equal(got.cpu().numpy().view(np.uint32), want.view(np.uint32)), key
+        got16 = torch.empty(n, dtype=torch.bfloat16, device=DEV)
+        ops.fill_normal(got16, key, shift, std)
+        assert np.array_equal(got16.view(torch.int16).cpu().numpy().view(np.uint16), R.to_bfloat16_bits(want)), key
+
+
+def test_models_drawn_on_the_device_and_on_the_host_are_the_same_model():
+    import ultima_b200 as u
+    from conftest import TINY
+    from ultima_b200.weights import random_tensors, random_tensors_on_device
+    cfg = u.config_from_dict(TINY["E"])
+    specs = u.model_spec_for(cfg).weight_specs()
+    for run_dtype in (torch.bfloat16, torch.float32):
+        dev = random_tensors_on_device(specs, 5, run_dtype, DEV)
+        host = random_tensors(specs, 5, run_dtype)
+        for s_ in specs:
+            d, h = dev[s_.name].cpu(), host[s_.name]
+            if s_.kind == "vector":                                # held in 32-bit on the device on both paths
+                h = random_tensors([s_], 5, torch.float32)[s_.name]
+            assert d.dtype == h.dtype and torch.equal(d, h), (s_.name, run_dtype)
+
+
 def test_silu_mul_convert_add_fill():
     ops = _ops()
     g = torch.Generator().manual_seed(9)
@@ -533,6 +628,45 @@ def test_attn_decode_tma(cfg, slices):
     assert err <= 2 ** -7, (cfg, slices, err)
 
 
+@pytest.mark.parametrize("hd", [64, 128])
+@pytest.mark.parametrize("kernel", ["mma", "tma", "tc"])
+@pytest.mark.parametrize("slices", [None, 1, 2])
+def test_decode_attention_on_a_wrapped_window_ring(kernel, hd, slices):
+    """A window of 100 kept in a ring of two pages (128 positions): position p lies at p mod 128, so once a
+    sequence is past 128 the page that takes the new position also holds the window's oldest keys, and the
+    first and the last key tile of a step are one physical page.  Only the window's mask and the zeroing of
+    values past the sequence's end keep old from new."""
+    for befores in ([127, 130, 200, 257], [128, 191, 192, 319], [63, 64, 100, 511]):
+        err = _attn_tc_case(8, 2, hd, 100, befores, [1] * 4, seed=hd + 31, slices=slices, ring_pages=2, kernel=kernel)
+        assert err <= 2 ** -7, (kernel, hd, slices, befores, err)
+
+
+@pytest.mark.parametrize("hd", [48, 64, 128])
+def test_decode_attention_mma_on_a_ring_of_one_page(hd):
+    for befores in ([40, 63, 64, 65], [127, 128, 200, 1000]):
+        err = _attn_tc_case(6, 3, hd, 33, befores, [1] * 4, seed=hd + 33, ring_pages=1, kernel="mma")
+        assert err <= 2 ** -7, (hd, befores, err)
+        if hd % 64 == 0:
+            err = _attn_tc_case(6, 3, hd, 33, befores, [1] * 4, seed=hd + 34, ring_pages=1, kernel="tma", slices=2)
+            assert err <= 2 ** -7, (hd, befores, err)
+
+
+@pytest.mark.parametrize("kernel,wide", [("mma", 0), (None, 0), (None, 2)])
+@pytest.mark.parametrize("hd", [64, 128])
+def test_prompt_attention_on_a_wrapped_window_ring(kernel, wide, hd):
+    """Continued prompts whose new tokens wrap around a ring of two pages: window 100, up to 29 new tokens
+    (window + new tokens - 1 = 128 positions must be held), for the mma.sync and both tcgen05 kernels."""
+    from ultima_b200.kernels import attn_tc
+    was = attn_tc.WIDE
+    attn_tc.set_wide(wide)
+    try:
+        for befores, news in (([127, 200, 257, 60], [20, 29, 5, 29]), ([100, 120, 128, 500], [29, 8, 29, 1])):
+            err = _attn_tc_case(4, 2, hd, 100, befores, news, seed=hd + 35, ring_pages=2, kernel=kernel)
+            assert err <= 2 ** -7, (kernel, wide, hd, befores, news, err)
+    finally:
+        attn_tc.set_wide(was)
+
+
 @pytest.mark.parametrize("cfg", [dict(nh=8, nkv=2, hd=128, window=0, norm=True, rot=True),
                                  dict(nh=8, nkv=1, hd=64, window=0, norm=True, rot=True),
                                  dict(nh=2, nkv=2, hd=256, window=0, norm=False, rot=True),
@@ -540,19 +674,24 @@ def test_attn_decode_tma(cfg, slices):
                                  dict(nh=32, nkv=2, hd=128, window=0, norm=True, rot=True)])
 @pytest.mark.parametrize("slices", [None, 1, 3])
 @pytest.mark.parametrize("owner", [True, False])
-def test_attn_decode_from_the_projection_slices(cfg, slices, owner):
+@pytest.mark.parametrize("wrapped", [False, True])
+def test_attn_decode_from_the_projection_slices(cfg, slices, owner, wrapped):
     """The decode kernel that sums the slices of the fused projection, prepares q and the new key and
     writes the cache itself gives, bit for bit, what qk_prepare followed by the decode kernel gives:
-    the output and the cache.  Without ownership of the cache it writes nothing and reads what is there."""
+    the output and the cache.  Without ownership of the cache it writes nothing and reads what is there.
+    ``wrapped``: a window of 100 in a ring of two pages, sequences past the ring's end, so that the page
+    of the new position is also the page of the window's oldest keys."""
     from ultima_b200.kernels import attn_tc
     from ultima_b200.engine import Runtime
     ops = _ops()
     rt = Runtime(DEV, torch.bfloat16)
     nh, nkv, hd, window = cfg["nh"], cfg["nkv"], cfg["hd"], cfg["window"]
     befores = [0, 63, 64, 300, 700]
+    ring_pages = 12
+    if wrapped:
+        window, ring_pages, befores = 100, 2, [127, 130, 200, 257, 64]
     n = len(befores)
     lens = [b + 1 for b in befores]
-    ring_pages = 12
     kc, vc, table, _ = _paged(n, lens, nkv, hd, torch.bfloat16, ring_pages, seed=hd + 21)
     g = torch.Generator().manual_seed(hd + 22)
     P, W = 3, (nh + 2 * nkv) * hd

@@ -133,6 +133,34 @@ def test_long_decoding(model_dirs, plain_models, name, dtype):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", ["C", "D"])
+def test_decoding_around_a_window_ring_of_one_page(model_dirs, plain_models, name, dtype):
+    """Passes of at most 16 tokens make the windowed layers' ring as small as it can be: one page of 64
+    positions for windows of 20 (C, head size 48) and 40 (D, head size 64).  A prompt of 50 tokens in four
+    passes, then token by token to 200 positions: the ring wraps three times, every page of it is used
+    again and again, and the page of the new position always holds the window's oldest keys too."""
+    from ultima_b200.cache import PAGE
+    V = TINY[name]["vocab_size"]
+    n = 200
+    ids = random_ids(77, n, V)
+    ref = _plain_logits(plain_models, name, ids)
+    eng = _engine(model_dirs, name, dtype, max_step_tokens=16)
+    rings = sorted(g.ring for g in eng.cache.kv_groups)
+    assert rings[0] == PAGE and rings[-1] > PAGE             # the windowed group wraps, the full one does not
+    s = eng.open(1)
+    rows = [eng.step(s, [ids[:50]], [list(range(50))]).cpu().numpy()]
+    for t in range(50, n):
+        rows.append(eng.step(s, [[ids[t]]], [[0]]).cpu().numpy())
+    eng.close(s)
+    eng.check_errors()
+    got = np.concatenate(rows, axis=0)
+    err, bound = close_enough(got, ref, dtype, TINY[name]["num_hidden_layers"])
+    if err > bound:
+        bad = int(np.argmax(np.abs(got - ref).max(axis=1) > bound))
+        pytest.fail(f"window ring [{name} {dtype}]: error {err:.3e} > {bound:.3e}, first bad position {bad}")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
 def test_first_tokens_and_want_subsets(model_dirs, plain_models, dtype):
     """Position 0 alone, a prompt of one token, and wanted places given out of order."""
     name = "B"

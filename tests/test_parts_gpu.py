@@ -220,7 +220,7 @@ def _register_toy():
 
 def test_toy_mixer_with_state_is_registered_built_and_stepped():
     from ultima_b200.engine import Engine
-    from ultima_b200.parts import LayerSpec, ModelSpec, Run, part
+    from ultima_b200.parts import ModelSpec, Run, layer, part
     from ultima_b200.weights import random_tensors
     _register_toy()
     width, vocab, decay = 40, 97, 0.75
@@ -228,11 +228,12 @@ def test_toy_mixer_with_state_is_registered_built_and_stepped():
     att = part("attention", width=width, n_heads=2, n_kv_heads=1, head_dim=16, qk_norm=False, eps=1e-5,
                position=None, window=None)
     layers = (
-        LayerSpec(part("pre_norm"), part("toy_running_mean", width=width, decay=decay),
-                  part("gated_silu", width=width, inner=56), norm, norm, prefix="l0."),
-        LayerSpec(part("pre_norm"), att, part("gated_silu", width=width, inner=72), norm, norm, prefix="l1."),
-        LayerSpec(part("pre_norm"), part("toy_running_mean", width=width, decay=0.5),
-                  part("gated_silu", width=width, inner=56), norm, norm, prefix="l2."),
+        layer(part("pre_norm"), prefix="l0.", mixer=part("toy_running_mean", width=width, decay=decay),
+              feed_forward=part("gated_silu", width=width, inner=56), mixer_norm=norm, feed_forward_norm=norm),
+        layer(part("pre_norm"), prefix="l1.", mixer=att, feed_forward=part("gated_silu", width=width, inner=72),
+              mixer_norm=norm, feed_forward_norm=norm),
+        layer(part("pre_norm"), prefix="l2.", mixer=part("toy_running_mean", width=width, decay=0.5),
+              feed_forward=part("gated_silu", width=width, inner=56), mixer_norm=norm, feed_forward_norm=norm),
     )
     spec = ModelSpec(width=width, vocab_size=vocab, max_positions=256,
                      embedding=part("token_table", vocab_size=vocab, width=width), embedding_name="emb.",
@@ -354,11 +355,12 @@ def _register_toy_routed_ffn():
 
 
 def _register_toy_position():
-    from ultima_b200.parts import Position, register_part
+    from ultima_b200.parts import Position, Rotation, register_part
 
     @register_part("position", "toy_slow_rotary", replace=True)
     class SlowRotary(Position):
-        """Half-split rotation with angle pos * scale / (j + 1): another table, the same kernel."""
+        """Half-split rotation with angle pos * scale / (j + 1): other tables, described to the
+        attention part as a rotation, so the library's kernels apply it."""
 
         def __init__(self, head_dim: int, scale: float, max_positions: int):
             self.head_dim, self.scale, self.max_positions = head_dim, scale, max_positions
@@ -369,12 +371,15 @@ def _register_toy_position():
             ang = torch.arange(self.max_positions, dtype=torch.float64)[:, None] * self.scale / \
                 (torch.arange(half, dtype=torch.float64)[None] + 1)
             self.cos, self.sin = torch.cos(ang).float().to(rt.device), torch.sin(ang).float().to(rt.device)
+
+        def rotation(self):
+            return Rotation(self.cos, self.sin, self.head_dim, False)
     return SlowRotary
 
 
 def test_toy_routed_feed_forward_and_another_position_encoding():
     from ultima_b200.engine import Engine
-    from ultima_b200.parts import LayerSpec, ModelSpec, Run, part
+    from ultima_b200.parts import ModelSpec, Run, layer, part
     from ultima_b200.weights import random_tensors
     _register_toy_routed_ffn()
     _register_toy_position()
@@ -382,8 +387,10 @@ def test_toy_routed_feed_forward_and_another_position_encoding():
     norm = part("rms", width=width, eps=1e-5)
     pos = part("toy_slow_rotary", head_dim=hd, scale=0.3, max_positions=128)
     att = part("attention", width=width, n_heads=3, n_kv_heads=3, head_dim=hd, qk_norm=True, eps=1e-5, position=pos)
-    layers = (LayerSpec(part("pre_norm"), att, part("toy_top1_experts", width=width, inner=40, n_experts=n_exp), norm, norm, prefix="a."),
-              LayerSpec(part("pre_norm"), att, part("gated_silu", width=width, inner=64), norm, norm, prefix="b."))
+    layers = (layer(part("pre_norm"), prefix="a.", mixer=att, mixer_norm=norm, feed_forward_norm=norm,
+                    feed_forward=part("toy_top1_experts", width=width, inner=40, n_experts=n_exp)),
+              layer(part("pre_norm"), prefix="b.", mixer=att, mixer_norm=norm, feed_forward_norm=norm,
+                    feed_forward=part("gated_silu", width=width, inner=64)))
     spec = ModelSpec(width=width, vocab_size=vocab, max_positions=128,
                      embedding=part("token_table", vocab_size=vocab, width=width), embedding_name="emb.",
                      layers=layers, runs=(Run(0), Run(1)), final_norm=norm, final_norm_name="fn.",

@@ -32,8 +32,11 @@ def test_random_traces(model_dirs, plain_models, name, seed, dtype):
     cfg, w = plain_models(name, "bfloat16")
     V, max_len = cfg["vocab_size"], min(cfg["max_position_embeddings"], 170)
     rng = np.random.default_rng(seed)
+    # seeds 3 and 5 (the configurations with windows) run in passes of 24 tokens, which makes their
+    # windowed rings one page long: prompts and decoding wrap around it
+    step_tokens = 24 if seed in (3, 5) else int(rng.choice([48, 4096]))
     eng = Engine.from_dir(model_dirs(name, "bfloat16"), dtype=dtype, max_tokens=5 * 192, max_seqs=5,
-                          max_step_tokens=int(rng.choice([48, 4096])), poison_cache=True)
+                          max_step_tokens=step_tokens, poison_cache=True)
     refs = {}
     for b, reqs in enumerate(_trace(rng, V, max_len)):
         slots = eng.open(len(reqs))

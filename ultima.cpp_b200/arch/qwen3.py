@@ -9,7 +9,7 @@ from __future__ import annotations
 
 from ..config.base import ArchitectureEntry, register_architecture
 from ..config.qwen3 import Qwen3Config
-from ..parts.base import LayerSpec, ModelSpec, Run, part
+from ..parts.base import ModelSpec, Run, layer, part
 
 _NAMES = (("mixer", "self_attn."), ("feed_forward", "mlp."), ("mixer_norm", "input_layernorm."),
           ("feed_forward_norm", "post_attention_layernorm."))
@@ -26,9 +26,8 @@ def build_spec(cfg: Qwen3Config, max_positions: int | None = None) -> ModelSpec:
                      n_kv_heads=cfg.num_key_value_heads, head_dim=cfg.head_dim, qk_norm=True,
                      eps=cfg.rms_norm_eps, position=position, window=cfg.window_of_layer(i))
         ffn = part("gated_silu", width=cfg.hidden_size, inner=cfg.intermediate_size)
-        layers.append(LayerSpec(arrangement=part("pre_norm"), mixer=mixer, feed_forward=ffn,
-                                mixer_norm=norm, feed_forward_norm=norm,
-                                prefix=f"model.layers.{i}.", names=_NAMES))
+        layers.append(layer(part("pre_norm"), prefix=f"model.layers.{i}.", names=_NAMES, mixer=mixer,
+                            feed_forward=ffn, mixer_norm=norm, feed_forward_norm=norm))
     return ModelSpec(
         width=cfg.hidden_size, vocab_size=cfg.vocab_size, max_positions=max_pos,
         embedding=part("token_table", vocab_size=cfg.vocab_size, width=cfg.hidden_size),

@@ -9,6 +9,8 @@ that is in use: running out is an error before anything is launched.
 """
 from __future__ import annotations
 
+PAGE = 64          # positions a page of the cache holds
+
 
 class CacheError(RuntimeError):
     """Out of slots or pages, or a slot used wrongly (freed twice, not held, over its length)."""

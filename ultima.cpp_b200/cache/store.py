@@ -23,9 +23,7 @@ import numpy as np
 import torch
 
 from ..parts.base import KVNeed, StateNeed
-from .book import CacheError, PageAllocator, SlotBook
-
-PAGE = 64
+from .book import PAGE, CacheError, PageAllocator, SlotBook
 
 
 def _ceil_div(a: int, b: int) -> int:

@@ -209,6 +209,10 @@ def cmd_run(argv) -> int:
     dec = (st.generated_tokens - len(prompts)) / st.decode_s if st.decode_s > 0 else 0.0
     print(f"[{st.prompt_tokens} prompt tok in {st.prefill_s * 1e3:.1f} ms ({pre:.1f} tok/s) | "
           f"{st.generated_tokens} gen tok in {st.decode_s * 1e3:.1f} ms ({dec:.1f} tok/s)]", file=sys.stderr)
+    if st.device_step_ms:
+        steps = sorted(st.device_step_ms)
+        print(f"[on the device: prompt step {st.device_prefill_ms:.2f} ms | {len(steps)} decode steps, "
+              f"median {steps[len(steps) // 2]:.3f} ms, longest {steps[-1]:.3f} ms]", file=sys.stderr)
     return 0
 
 

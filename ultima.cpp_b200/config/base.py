@@ -10,12 +10,35 @@ from __future__ import annotations
 
 import json
 import os
+import inspect
 from dataclasses import dataclass
-from typing import Callable, Optional
+from typing import Callable, Optional, Protocol, runtime_checkable
 
 
 class ConfigError(ValueError):
     """A configuration that is missing a key, holds a bad value or names no known model."""
+
+
+@runtime_checkable
+class ArchitectureConfig(Protocol):
+    """What the rest of the package asks of an architecture's typed configuration, whatever its own
+    keys are.  The engine, the loader of random models and the command line use these and nothing
+    else of a configuration; everything else is between the class and its own ``build_spec``.
+
+        architecture              the registry name the configuration was read under
+        max_position_embeddings   the longest context the model allows (caps the cache's reach)
+        torch_dtype               "bfloat16" | "float32" | "float16": the type a written folder stores
+        from_dict(d)              classmethod: config.json's object -> configuration; raises ConfigError
+        to_dict()                 the config.json that reads back as this configuration
+
+    and of the entry's ``build_spec(config, max_positions=None) -> ModelSpec``: the model as data,
+    with position tables sized for ``max_positions`` (default: the configuration's own limit).
+    """
+    architecture: str
+    max_position_embeddings: int
+    torch_dtype: str
+
+    def to_dict(self) -> dict: ...
 
 
 @dataclass(frozen=True)
@@ -24,14 +47,27 @@ class ArchitectureEntry:
     model_type: str                # "qwen3"
     supported: bool
     notes: str
-    config_cls: Optional[type] = None
-    build_spec: Optional[Callable] = None   # config -> ModelSpec
+    config_cls: Optional[type] = None       # a class that follows ArchitectureConfig
+    build_spec: Optional[Callable] = None   # (config, max_positions=None) -> ModelSpec
 
 
 _REGISTRY: dict[str, ArchitectureEntry] = {}
 
 
 def register_architecture(entry: ArchitectureEntry, replace: bool = False) -> ArchitectureEntry:
+    if entry.supported:
+        # the protocol above, checked where an architecture enters the table
+        cls = entry.config_cls
+        lacks = [a for a in ("from_dict", "to_dict") if not callable(getattr(cls, a, None))]
+        fields = getattr(cls, "__dataclass_fields__", None) or getattr(cls, "__annotations__", {})
+        lacks += [a for a in ("architecture", "max_position_embeddings", "torch_dtype")
+                  if a not in fields and not hasattr(cls, a)]
+        if cls is None or lacks:
+            raise ConfigError(f"architecture '{entry.name}': its configuration class lacks {', '.join(lacks) or 'everything'} "
+                              f"(see ArchitectureConfig)")
+        if not callable(entry.build_spec) or "max_positions" not in inspect.signature(entry.build_spec).parameters:
+            raise ConfigError(f"architecture '{entry.name}': build_spec must be callable as "
+                              f"build_spec(config, max_positions=None)")
     for key in (entry.name, entry.model_type):
         if key in _REGISTRY and _REGISTRY[key].name != entry.name and not replace:
             raise ConfigError(f"architecture key '{key}' is already registered")

@@ -110,8 +110,6 @@ __global__ void __launch_bounds__(NTHREADS)
 attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                const __grid_constant__ CUtensorMap map_v, TcAttnParams p) {
     extern __shared__ uint8_t smem_raw[];
-    pdl_trigger();
-    pdl_wait();
     // prompts: a one-dimensional grid numbered so that the blocks with the most keys to visit (the
     // last tiles of the rows, of every sequence and KV head) are handed out first
     const int per_tile = p.n_seqs * p.nkv;
@@ -122,7 +120,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
     const int TPB = BM / G;                                // tokens a tile: TPB * G of the 128 rows are in use
     const int tile = DECODE ? 0 : p.n_row_tiles - 1 - blockIdx.x / per_tile;
     const int tok_first = tile * TPB;
-    if (tok_first >= q_len) return;
+    if (tok_first >= q_len) return;                        // (a block that ends counts as one that has let its dependents go)
 
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint8_t* q_s = smem;
@@ -170,6 +168,11 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    // Dependents are let go only now that this block holds its tensor memory: a dependent product
+    // allocates its own before it waits for this grid's end and keeps it until then, so a block of
+    // this grid that still had to allocate beside it could wait for columns that never come free.
+    pdl_trigger();
+    pdl_wait();
 
     if (warp == 0) {
         // ---------------- TMA ----------------
@@ -442,8 +445,6 @@ attn_tc_wide_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
                     const __grid_constant__ CUtensorMap map_v, TcAttnParams p) {
     extern __shared__ uint8_t smem_raw[];
     constexpr int S = WIDE_STAGES;
-    pdl_trigger();
-    pdl_wait();
     const int per_tile = p.n_seqs * p.nkv;
     const int seq = (blockIdx.x % per_tile) / p.nkv;
     const int kvh = blockIdx.x % p.nkv;
@@ -504,6 +505,8 @@ attn_tc_wide_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    pdl_trigger();                                         // after the allocation, as in attn_tc_kernel
+    pdl_wait();
 
     if (warp == 0) {
         // ---------------- TMA ----------------

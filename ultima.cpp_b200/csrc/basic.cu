@@ -5,7 +5,7 @@
 //   embedding row read        src/model/qwen_model.cpp:145-157
 //   RMSNorm                   src/kernels/rmsnorm.cpp:10-17
 //   per-head norm of q and k  src/model/qwen_block.cpp:76-82, :713-718
-//   half-split rotation       src/kernels/rope.cpp:17-52
+//   rotation of pairs         src/kernels/rope.cpp:17-52 (half-split or interleaved pairs, the first rope_dim columns)
 //   cache write before read   src/model/qwen_block.cpp:725-727
 //   silu(gate) * up           src/kernels/elementwise.cpp:62-68
 // Sums of squares, the rotation and the gate are computed in 32-bit whatever the storage.
@@ -157,8 +157,15 @@ UB_API int ub_rmsnorm(const float* x, const int* rows, const float* w, void* out
 //   qkv   [parts][T, (nh + 2 nkv) * hd]   the row is the sum of ``n_parts`` partial results
 //                                         (slices of K of the projection), ``part_stride`` apart
 //   q_out [T, *] row stride q_out_stride  normed and rotated q heads (may be qkv itself)
-//   cos, sin  [max_pos, hd/2] float32 (null: no rotation)
+//   cos, sin  [max_pos, rd/2] float32 (null: no rotation); rd = ``rotary_dim`` <= hd: the head's
+//             first rd columns are rotated, the others pass through (the reference's rope_dim,
+//             src/kernels/rope.cpp:27,50); pairs are (j, j + rd/2), or (2j, 2j + 1) when
+//             ``interleaved`` (the pairing is per-architecture data in the reference,
+//             include/ultima/model/arch_registry.hpp:32-38)
 //   qw, kw    [hd] float32 (null: no norm)
+//   k_out, v_out  [T, nkv * hd] row stride kv_out_stride, element type of q_out (null: keys and
+//             values go into the paged cache): for a position encoding that is applied by code of
+//             its own between this kernel and the cache write (ub_kv_write)
 // ---------------------------------------------------------------------------------------
 template <typename TA, typename TQ, typename TC>
 __global__ void qk_prepare_kernel(const TA* qkv, int n_parts, long long part_stride,
@@ -167,7 +174,7 @@ __global__ void qk_prepare_kernel(const TA* qkv, int n_parts, long long part_str
                                   const float* __restrict__ sn, const int* __restrict__ tok_pos,
                                   const int* __restrict__ tok_seq, TC* __restrict__ kcache,
                                   TC* __restrict__ vcache, PagedKV c, int n_tokens, int nh, float eps,
-                                  int write_kv) {
+                                  int write_kv, int rd, int interleaved, TQ* k_out, TQ* v_out, long long kv_out_stride) {
     pdl_trigger();
     pdl_wait();
     const int lane = threadIdx.x & 31;
@@ -175,57 +182,134 @@ __global__ void qk_prepare_kernel(const TA* qkv, int n_parts, long long part_str
     const int heads_all = nh + 2 * c.n_kv_heads;
     if (wid >= (long long)n_tokens * heads_all) return;
     const int t = (int)(wid / heads_all), h = (int)(wid % heads_all);
-    const int hd = c.head_dim, half = hd >> 1;
+    const int hd = c.head_dim, n_pairs = hd >> 1, rhalf = rd >> 1;
     const TA* row = qkv + ((long long)t * heads_all + h) * hd;
     const int pos = tok_pos[t];
     const int seq = tok_seq[t];
-    if (h >= nh + c.n_kv_heads) {                       // a value head: copy into the cache
+    if (h >= nh + c.n_kv_heads) {                       // a value head: copy into the cache (or to v_out)
         if (!write_kv) return;
-        TC* dst = vcache + paged_offset(c, seq, pos, h - nh - c.n_kv_heads);
+        const int kvh = h - nh - c.n_kv_heads;
+        TC* dst = v_out ? nullptr : vcache + paged_offset(c, seq, pos, kvh);
+        TQ* dst2 = v_out ? v_out + (long long)t * kv_out_stride + (long long)kvh * hd : nullptr;
         for (int i = lane; i < hd; i += 32) {
             float v = 0.f;
             for (int p = 0; p < n_parts; ++p) v += to_f32<TA>(row[p * part_stride + i]);
-            dst[i] = from_f32<TC>(v);
+            if (dst2) dst2[i] = from_f32<TQ>(v); else dst[i] = from_f32<TC>(v);
         }
         return;
     }
     const bool is_k = h >= nh;
     if (is_k && !write_kv) return;
     const float* w = is_k ? kw : qw;
-    // a lane's pairs (j, j + half) for j = lane, lane + 32, ...: at most 4 (head sizes up to 256)
+    // a lane's pairs: pair x for x = lane, lane + 32, ...: at most 4 (head sizes up to 256).  The
+    // first rd/2 pairs are the rotated ones, the rest are neighbours that pass through.
     float va[4], vb[4];
+    int ia[4], ib[4];
     float ss = 0.f;
 #pragma unroll
     for (int u = 0; u < 4; ++u) {
-        const int j = lane + u * 32;
+        const int x = lane + u * 32;
         va[u] = vb[u] = 0.f;
-        if (j < half) {
+        ia[u] = ib[u] = 0;
+        if (x < n_pairs) {
+            if (x < rhalf) { ia[u] = interleaved ? 2 * x : x; ib[u] = interleaved ? 2 * x + 1 : x + rhalf; }
+            else { ia[u] = rd + 2 * (x - rhalf); ib[u] = ia[u] + 1; }
             for (int p = 0; p < n_parts; ++p) {
-                va[u] += to_f32<TA>(row[p * part_stride + j]);
-                vb[u] += to_f32<TA>(row[p * part_stride + j + half]);
+                va[u] += to_f32<TA>(row[p * part_stride + ia[u]]);
+                vb[u] += to_f32<TA>(row[p * part_stride + ib[u]]);
             }
             ss += va[u] * va[u] + vb[u] * vb[u];
         }
     }
     ss = warp_sum(ss);
     const float inv = w ? inv_rms(ss, (float)hd, eps) : 1.0f;
-    TC* dst = is_k ? kcache + paged_offset(c, seq, pos, h - nh) : nullptr;
-    TQ* qdst = q_out + (long long)t * q_out_stride + (long long)h * hd;
+    TC* dst = (is_k && !k_out) ? kcache + paged_offset(c, seq, pos, h - nh) : nullptr;
+    TQ* qdst = is_k ? (k_out ? k_out + (long long)t * kv_out_stride + (long long)(h - nh) * hd : nullptr)
+                    : q_out + (long long)t * q_out_stride + (long long)h * hd;
 #pragma unroll
     for (int u = 0; u < 4; ++u) {
-        const int j = lane + u * 32;
-        if (j >= half) continue;
+        const int x = lane + u * 32;
+        if (x >= n_pairs) continue;
         float a = va[u], b = vb[u];
-        if (w) { a = a * w[j] * inv; b = b * w[j + half] * inv; }
+        if (w) { a = a * w[ia[u]] * inv; b = b * w[ib[u]] * inv; }
         float ra = a, rb = b;
-        if (cs) {
-            const float co = cs[(long long)pos * half + j], si = sn[(long long)pos * half + j];
+        if (cs && x < rhalf) {
+            const float co = cs[(long long)pos * rhalf + x], si = sn[(long long)pos * rhalf + x];
             ra = a * co - b * si;
             rb = a * si + b * co;
         }
-        if (is_k) { dst[j] = from_f32<TC>(ra); dst[j + half] = from_f32<TC>(rb); }
-        else { qdst[j] = from_f32<TQ>(ra); qdst[j + half] = from_f32<TQ>(rb); }
+        if (dst) { dst[ia[u]] = from_f32<TC>(ra); dst[ib[u]] = from_f32<TC>(rb); }
+        else { qdst[ia[u]] = from_f32<TQ>(ra); qdst[ib[u]] = from_f32<TQ>(rb); }
     }
+}
+
+// Rotation alone, in place: x [T, n_heads, hd] (token stride x_stride elements, heads side by side),
+// the tables and the pairing as above.  One warp a (token, head).
+template <typename TX>
+__global__ void rotate_pairs_kernel(TX* x, long long x_stride, int n_tokens, int n_heads, int hd, const float* __restrict__ cs,
+                                    const float* __restrict__ sn, const int* __restrict__ tok_pos, int rd, int interleaved) {
+    const int lane = threadIdx.x & 31;
+    const long long wid = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (wid >= (long long)n_tokens * n_heads) return;
+    const int t = (int)(wid / n_heads), h = (int)(wid % n_heads);
+    const int rhalf = rd >> 1;
+    TX* row = x + (long long)t * x_stride + (long long)h * hd;
+    const int pos = tok_pos[t];
+    for (int j = lane; j < rhalf; j += 32) {
+        const int ia = interleaved ? 2 * j : j, ib = interleaved ? 2 * j + 1 : j + rhalf;
+        const float a = to_f32<TX>(row[ia]), b = to_f32<TX>(row[ib]);
+        const float co = cs[(long long)pos * rhalf + j], si = sn[(long long)pos * rhalf + j];
+        row[ia] = from_f32<TX>(a * co - b * si);
+        row[ib] = from_f32<TX>(a * si + b * co);
+    }
+}
+UB_API int ub_rotate_pairs(void* x, int dtype, long long x_stride, int n_tokens, int n_heads, int hd, const float* cs,
+                           const float* sn, const int* tok_pos, int rotary_dim, int interleaved, cudaStream_t st) {
+    if (n_tokens <= 0 || n_heads <= 0) return 0;
+    if (rotary_dim < 2 || rotary_dim % 2 != 0 || rotary_dim > hd || !cs || !sn) return UB_ERR_ARG;
+    const long long warps = (long long)n_tokens * n_heads;
+    const unsigned grid = (unsigned)((warps + 7) / 8);
+    if (dtype == UB_F32) rotate_pairs_kernel<float><<<grid, 256, 0, st>>>((float*)x, x_stride, n_tokens, n_heads, hd, cs, sn, tok_pos, rotary_dim, interleaved);
+    else if (dtype == UB_BF16) rotate_pairs_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>((__nv_bfloat16*)x, x_stride, n_tokens, n_heads, hd, cs, sn, tok_pos, rotary_dim, interleaved);
+    else return UB_ERR_UNSUPPORTED;
+    UB_LAUNCH_CHECK();
+    return 0;
+}
+
+// Keys and values of the step's tokens, k and v [T, nkv * hd] (row stride kv_stride), into the paged
+// cache.  One warp a (token, kv head).
+template <typename TX, typename TC>
+__global__ void kv_write_kernel(const TX* __restrict__ k, const TX* __restrict__ v, long long kv_stride, const int* __restrict__ tok_pos,
+                                const int* __restrict__ tok_seq, TC* __restrict__ kcache, TC* __restrict__ vcache, PagedKV c,
+                                int n_tokens) {
+    const int lane = threadIdx.x & 31;
+    const long long wid = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (wid >= (long long)n_tokens * c.n_kv_heads) return;
+    const int t = (int)(wid / c.n_kv_heads), h = (int)(wid % c.n_kv_heads);
+    const long long at = paged_offset(c, tok_seq[t], tok_pos[t], h);
+    const TX* kr = k + (long long)t * kv_stride + (long long)h * c.head_dim;
+    const TX* vr = v + (long long)t * kv_stride + (long long)h * c.head_dim;
+    for (int i = lane; i < c.head_dim; i += 32) {
+        kcache[at + i] = from_f32<TC>(to_f32<TX>(kr[i]));
+        vcache[at + i] = from_f32<TC>(to_f32<TX>(vr[i]));
+    }
+}
+UB_API int ub_kv_write(const void* k, const void* v, int dtype, long long kv_stride, const int* tok_pos, const int* tok_seq,
+                       void* kcache, void* vcache, int cache_dtype, const int* table, int pages_per_seq, int ring, int page,
+                       int n_tokens, int nkv, int hd, cudaStream_t st) {
+    if (n_tokens <= 0) return 0;
+    if (ring % page != 0 || nkv < 1 || hd < 1) return UB_ERR_ARG;
+    PagedKV c{table, pages_per_seq, ring, page, nkv, hd};
+    const unsigned grid = (unsigned)(((long long)n_tokens * nkv + 7) / 8);
+    if (dtype == UB_F32 && cache_dtype == UB_F32)
+        kv_write_kernel<float, float><<<grid, 256, 0, st>>>((const float*)k, (const float*)v, kv_stride, tok_pos, tok_seq, (float*)kcache, (float*)vcache, c, n_tokens);
+    else if (dtype == UB_BF16 && cache_dtype == UB_BF16)
+        kv_write_kernel<__nv_bfloat16, __nv_bfloat16><<<grid, 256, 0, st>>>((const __nv_bfloat16*)k, (const __nv_bfloat16*)v, kv_stride, tok_pos, tok_seq, (__nv_bfloat16*)kcache, (__nv_bfloat16*)vcache, c, n_tokens);
+    else if (dtype == UB_F32 && cache_dtype == UB_BF16)
+        kv_write_kernel<float, __nv_bfloat16><<<grid, 256, 0, st>>>((const float*)k, (const float*)v, kv_stride, tok_pos, tok_seq, (__nv_bfloat16*)kcache, (__nv_bfloat16*)vcache, c, n_tokens);
+    else return UB_ERR_UNSUPPORTED;
+    UB_LAUNCH_CHECK();
+    return 0;
 }
 
 // The same for head sizes of 64, 128 and 256: a lane holds E = hd / 32 neighbouring elements, the
@@ -325,9 +409,13 @@ UB_API int ub_qk_prepare(const void* qkv, int in_dtype, int n_parts, long long p
                          const float* sn, const int* tok_pos, const int* tok_seq, void* kcache,
                          void* vcache, int cache_dtype, const int* table, int pages_per_seq, int ring,
                          int page, int n_tokens, int nh, int nkv, int hd, float eps, int write_kv,
+                         int rotary_dim, int interleaved, void* k_out, void* v_out, long long kv_out_stride,
                          cudaStream_t st) {
     if (n_tokens <= 0) return 0;
     if (hd % 2 != 0 || hd > 256 || ring % page != 0 || n_parts < 1) return UB_ERR_ARG;
+    if (cs && (rotary_dim < 2 || rotary_dim % 2 != 0 || rotary_dim > hd)) return UB_ERR_ARG;
+    if ((!k_out) != (!v_out)) return UB_ERR_ARG;
+    if (!cs) { rotary_dim = 0; interleaved = 0; }
     PagedKV c{table, pages_per_seq, ring, page, nkv, hd};
     const long long warps = (long long)n_tokens * (nh + 2 * nkv);
     const int wpb = 8;
@@ -336,9 +424,10 @@ UB_API int ub_qk_prepare(const void* qkv, int in_dtype, int n_parts, long long p
     const bool aligned = (((uintptr_t)qkv | (uintptr_t)q_out | (uintptr_t)kcache | (uintptr_t)vcache | (uintptr_t)qw |
                            (uintptr_t)kw | (uintptr_t)cs | (uintptr_t)sn) & 15) == 0 &&
                          part_stride % 8 == 0 && q_out_stride % 8 == 0;
-    const bool vec = aligned && (hd == 64 || hd == 128 || hd == 256);
-    // the vector kernel: blocks of 8 warps; with many tokens one block a token (its warps loop over
-    // the heads), with few tokens a warp a head
+    // the vector kernel: whole heads rotated in halves, keys and values straight into the cache
+    const bool vec = aligned && (hd == 64 || hd == 128 || hd == 256) && !k_out && (!cs || (rotary_dim == hd && !interleaved));
+    // blocks of 8 warps; with many tokens one block a token (its warps loop over the heads), with few
+    // tokens a warp a head
     const int heads_all = nh + 2 * nkv;
     const dim3 vgrid(n_tokens, n_tokens >= 256 ? 1 : (heads_all + 7) / 8);
 #define LAUNCH_V(TA, TQ, TC, E) e = ub_launch_dependent(qk_prepare_vec_kernel<TA, TQ, TC, E>, vgrid, dim3(256), 0, st, \
@@ -349,7 +438,8 @@ UB_API int ub_qk_prepare(const void* qkv, int in_dtype, int n_parts, long long p
         else if (vec && hd == 256) LAUNCH_V(TA, TQ, TC, 8); \
         else e = ub_launch_dependent(qk_prepare_kernel<TA, TQ, TC>, dim3(grid), dim3(wpb * 32), 0, st, \
         (const TA*)qkv, n_parts, part_stride, (TQ*)q_out, q_out_stride, qw, kw, cs, sn, tok_pos, tok_seq, \
-        (TC*)kcache, (TC*)vcache, c, n_tokens, nh, eps, write_kv); } while (0)
+        (TC*)kcache, (TC*)vcache, c, n_tokens, nh, eps, write_kv, rotary_dim, interleaved, (TQ*)k_out, (TQ*)v_out, \
+        kv_out_stride); } while (0)
     if (in_dtype == UB_F32 && q_dtype == UB_F32 && cache_dtype == UB_F32) LAUNCH(float, float, float);
     else if (in_dtype == UB_BF16 && q_dtype == UB_BF16 && cache_dtype == UB_BF16) LAUNCH(__nv_bfloat16, __nv_bfloat16, __nv_bfloat16);
     else if (in_dtype == UB_F32 && q_dtype == UB_BF16 && cache_dtype == UB_BF16) LAUNCH(float, __nv_bfloat16, __nv_bfloat16);
@@ -433,7 +523,21 @@ UB_API int ub_add_into(float* acc, const void* in, int in_dtype, long long n, cu
 }
 
 // ---------------------------------------------------------------------------------------
-// random fill: out[i] = shift + std * N(0,1), from a counter hash of (seed, i)
+// random fill: out[i] = shift + std * z(key, i), z standard normal.
+//
+// One counter-based generator, written three times with the same bits: here, in numpy in
+// weights/random_init.py and, as the tests' own copy, in tests/plain_random.py.  A draw depends on
+// the tensor's key and the element's index only.  Every step is an integer operation or ONE
+// correctly rounded float32 operation (add, multiply, divide, square root; never a fused
+// multiply-add, never a library logarithm or cosine), so the three give the same bits:
+//   r  = mix64(key ^ mix64(i))                        SplitMix64's finaliser
+//   u1 = ((r >> 41) + 0.5) * 2^-23                    in (0, 1), exact
+//   t  = (r >> 16) & 0xFFFFFF                          24 bits: the angle 2 pi t / 2^24
+//   ln u1   exponent * ln 2 + 2 s (1 + s^2/3 + ... + s^10/11), s = (m - 1) / (m + 1), m the
+//           mantissa brought into [sqrt(1/2), sqrt(2))
+//   cos     quadrant from the top two bits of t, the rest folded into [0, pi/4], Taylor sums of
+//           sine and cosine there (to x^9 and x^10), Horner's rule
+//   z  = sqrt(-2 ln u1) * cos(2 pi t / 2^24)          Box-Muller
 // ---------------------------------------------------------------------------------------
 __device__ __forceinline__ unsigned long long mix64(unsigned long long z) {
     z += 0x9E3779B97F4A7C15ull;
@@ -441,15 +545,54 @@ __device__ __forceinline__ unsigned long long mix64(unsigned long long z) {
     z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
     return z ^ (z >> 31);
 }
+__device__ __forceinline__ float fbits(unsigned u) { return __uint_as_float(u); }
+__device__ __forceinline__ float counter_normal(unsigned long long key, unsigned long long i) {
+    const unsigned long long r = mix64(key ^ mix64(i));
+    // ---- ln(u1)
+    const float u1 = __fmul_rn(__fadd_rn(__uint2float_rn((unsigned)(r >> 41)), 0.5f), fbits(0x34000000u));   // * 2^-23
+    const unsigned ub = __float_as_uint(u1);
+    int e = (int)(ub >> 23) - 127;
+    float m = fbits((ub & 0x7FFFFFu) | 0x3F800000u);                  // [1, 2)
+    if (m > fbits(0x3FB504F3u)) { m = __fmul_rn(m, 0.5f); e += 1; }    // [sqrt(1/2), sqrt(2))
+    const float s = __fdiv_rn(__fsub_rn(m, 1.0f), __fadd_rn(m, 1.0f));
+    const float s2 = __fmul_rn(s, s);
+    float p = fbits(0x3DBA2E8Cu);                                      // 1/11
+    p = __fadd_rn(__fmul_rn(p, s2), fbits(0x3DE38E39u));               // 1/9
+    p = __fadd_rn(__fmul_rn(p, s2), fbits(0x3E124925u));               // 1/7
+    p = __fadd_rn(__fmul_rn(p, s2), fbits(0x3E4CCCCDu));               // 1/5
+    p = __fadd_rn(__fmul_rn(p, s2), fbits(0x3EAAAAABu));               // 1/3
+    p = __fadd_rn(__fmul_rn(p, s2), 1.0f);
+    const float ln_m = __fmul_rn(__fmul_rn(2.0f, s), p);
+    const float ln_u = __fadd_rn(__fmul_rn(__int2float_rn(e), fbits(0x3F317218u)), ln_m);    // e ln 2 + ln m
+    const float rad = __fsqrt_rn(__fmul_rn(-2.0f, ln_u));
+    // ---- cos(2 pi t / 2^24)
+    const unsigned t = (unsigned)(r >> 16) & 0xFFFFFFu;
+    const unsigned quad = t >> 22, rest = t & 0x3FFFFFu;              // angle = (quad + rest / 2^22) pi/2
+    const bool fold = rest > 0x200000u;                                // past the middle of the quadrant
+    const unsigned fr = fold ? 0x400000u - rest : rest;               // [0, 2^21]
+    const float x = __fmul_rn(__fmul_rn(__uint2float_rn(fr), fbits(0x34800000u)), fbits(0x3FC90FDBu));   // * 2^-22 * pi/2
+    const float x2 = __fmul_rn(x, x);
+    float sn = fbits(0x3638EF1Du);                                     // 1/9!
+    sn = __fsub_rn(fbits(0x39500D01u), __fmul_rn(sn, x2));             // 1/7! - ...
+    sn = __fsub_rn(fbits(0x3C088889u), __fmul_rn(sn, x2));             // 1/5! - ...
+    sn = __fsub_rn(fbits(0x3E2AAAABu), __fmul_rn(sn, x2));             // 1/3! - ...
+    sn = __fsub_rn(1.0f, __fmul_rn(sn, x2));
+    sn = __fmul_rn(sn, x);
+    float cs = fbits(0x3493F27Eu);                                     // 1/10!
+    cs = __fsub_rn(fbits(0x37D00D01u), __fmul_rn(cs, x2));             // 1/8! - ...
+    cs = __fsub_rn(fbits(0x3AB60B61u), __fmul_rn(cs, x2));             // 1/6! - ...
+    cs = __fsub_rn(fbits(0x3D2AAAABu), __fmul_rn(cs, x2));             // 1/4! - ...
+    cs = __fsub_rn(0.5f, __fmul_rn(cs, x2));
+    cs = __fsub_rn(1.0f, __fmul_rn(cs, x2));
+    const float sin_q = fold ? cs : sn, cos_q = fold ? sn : cs;        // sine and cosine of the angle within the quadrant
+    const float c = quad == 0 ? cos_q : quad == 1 ? -sin_q : quad == 2 ? -cos_q : sin_q;
+    return __fmul_rn(rad, c);
+}
 template <typename TO>
-__global__ void fill_normal_kernel(TO* __restrict__ out, long long n, unsigned long long seed, float shift, float stdv) {
+__global__ void fill_normal_kernel(TO* __restrict__ out, long long n, unsigned long long key, float shift, float stdv) {
     const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= n) return;
-    const unsigned long long r = mix64(seed ^ mix64((unsigned long long)i));
-    const float u1 = ((float)(unsigned)(r >> 40) + 0.5f) * (1.0f / 16777216.0f);
-    const float u2 = ((float)(unsigned)((r >> 8) & 0xFFFFFFu) + 0.5f) * (1.0f / 16777216.0f);
-    const float z = sqrtf(-2.0f * logf(u1)) * cospif(2.0f * u2);
-    out[i] = from_f32<TO>(shift + stdv * z);
+    out[i] = from_f32<TO>(__fadd_rn(shift, __fmul_rn(stdv, counter_normal(key, (unsigned long long)i))));
 }
 UB_API int ub_fill_normal(void* out, int dtype, long long n, unsigned long long seed, float shift, float stdv,
                           cudaStream_t st) {

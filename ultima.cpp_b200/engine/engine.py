@@ -82,16 +82,14 @@ class Engine:
         # decode steps (one token a sequence, every logit wanted) are captured as CUDA graphs,
         # one for each (number of sequences, slices of the key range); parts must allow it
         from .model import TRACE as _tracing
-        self.use_graphs = bool(use_graphs) and not _tracing and all(
-            getattr(L.mixer, "graph_safe", False) and getattr(L.feed_forward, "graph_safe", False)
-            for L in self.model.layers)
+        self.use_graphs = bool(use_graphs) and not _tracing and all(L.graph_safe for L in self.model.layers)
         self._graphs: dict = {}
 
     # ---- construction ------------------------------------------------------------------
     @classmethod
     def from_dir(cls, model_dir: str, dtype="bfloat16", **kw) -> "Engine":
         """Model class by config.json, weights by name from model.safetensors."""
-        cfg = config_from_dir(model_dir)
+        cfg = config_from_dir(model_dir)              # an ArchitectureConfig (config/base.py)
         entry = find_architecture(cfg.architecture)
         max_ctx = kw.get("max_context")
         # positions beyond what the cache can hold are never reached: size tables to that
@@ -144,6 +142,19 @@ class Engine:
         """Keep the first ``length`` positions of a slot (to continue from a shared prefix)."""
         self.cache.truncate(slot, length)
 
+    def mark(self):
+        """A point on the device's timeline (a CUDA event on the current stream); two of them give the
+        device time of what was queued between them (``elapsed_ms``).  The generation loop marks every
+        step this way."""
+        e = torch.cuda.Event(enable_timing=True)
+        e.record()
+        return e
+
+    @staticmethod
+    def elapsed_ms(a, b) -> float:
+        b.synchronize()
+        return a.elapsed_time(b)
+
     def memory_report(self) -> dict:
         """Bytes held on the device: weights, cache, scratch."""
         seen, weights = set(), 0
@@ -152,8 +163,7 @@ class Engine:
             if isinstance(t, torch.Tensor) and t.is_cuda and t.data_ptr() not in seen:
                 seen.add(t.data_ptr())
                 weights += t.numel() * t.element_size()
-        for part in [self.model.embedding, self.model.final_norm, self.model.head] + \
-                [p for L in self.model.layers for p in (L.mixer, L.feed_forward, L.mixer_norm, L.feed_forward_norm)]:
+        for part in self.model.all_parts():
             for v in vars(part).values():
                 add(v)
         return {"weights": weights, "cache": self.cache.nbytes(), "scratch": self.rt.arena._buf.numel(),
@@ -181,7 +191,7 @@ class Engine:
         V = self.spec.vocab_size
         lens_after = {}
         for s, t, w in zip(slots, tokens, want):
-            self.cache.slots.check(s)
+            self._check_slot(s)
             if len(t) == 0:
                 if len(w):
                     raise StepError("step: logits wanted of a sequence that brings no token")
@@ -248,6 +258,12 @@ class Engine:
         out[torch.tensor(order, dtype=torch.long, device=self.device)] = torch.cat(pieces, dim=0)
         return out
 
+    def _check_slot(self, s) -> None:
+        try:
+            self.cache.slots.check(s)
+        except CacheError as e:
+            raise StepError(f"step: {e}") from e
+
     def _step_one_token_each(self, slots, tokens) -> torch.Tensor:
         """The common decode step, checked with less work: one token a sequence, every logit wanted."""
         B = len(slots)
@@ -260,12 +276,12 @@ class Engine:
             raise StepError(f"step: token id {bad} is outside the vocabulary [0, {V})")
         before, after = [], {}
         for s in slots:
-            self.cache.slots.check(s)
+            self._check_slot(s)
             n = self.cache.slots.length[s]
             if n + 1 > self.max_context:
                 raise StepError(f"step: slot {s} would reach {n + 1} positions; the limit is {self.max_context}")
             before.append(n)
-            if n % 64 == 0:                      # only a sequence at a page's edge needs a new page
+            if n % PAGE == 0:                    # only a sequence at a page's edge needs a new page
                 after[s] = n + 1
         if after:
             try:
@@ -294,12 +310,12 @@ class Engine:
             raise StepError("step_fed: token ids must be int32 on the engine's device, one a slot")
         before, after = [], {}
         for s in slots:
-            self.cache.slots.check(s)
+            self._check_slot(s)
             n = self.cache.slots.length[s]
             if n + 1 > self.max_context:
                 raise StepError(f"step: slot {s} would reach {n + 1} positions; the limit is {self.max_context}")
             before.append(n)
-            if n % 64 == 0:
+            if n % PAGE == 0:
                 after[s] = n + 1
         if after:
             try:
@@ -345,17 +361,22 @@ class Engine:
         ids = [t[0] for t in new_tokens]
         entry = self._graphs.get(key)
         if entry is None:
+            # The first step of this shape runs the ordinary way (which also loads libraries, makes
+            # tensor maps and sizes the scratch) and its logits are the step's result; the capture
+            # that follows records the same launches without running them, so the step has been
+            # executed once: a part that keeps state of its own advances it once, not twice.
             record = DecodeRecord(B, [t.shape[1] for t in tables], self.device, self._ring)
             batch = record.update(slots, ids, before, tables, ids_dev)
-            self.model.forward(batch, self.cache)              # warm: libraries, tensor maps, scratch
+            self.last_h2d_bytes = record.total * 4
+            first = self.model.forward(batch, self.cache)
             torch.cuda.synchronize(self.device)
             graph = torch.cuda.CUDAGraph()
             l0 = self.rt.launches
             with torch.cuda.graph(graph):
                 logits = self.model.forward(batch, self.cache)
-            entry = (graph, record, logits, self.rt.launches - l0)
+            self._graphs[key] = (graph, record, logits, self.rt.launches - l0)
             self.rt.launches = l0
-            self._graphs[key] = entry
+            return first
         graph, record, logits, n_launch = entry
         record.update(slots, ids, before, tables, ids_dev)
         self.last_h2d_bytes = record.total * 4

@@ -14,6 +14,7 @@ from __future__ import annotations
 import time
 from dataclasses import dataclass, field
 
+from ..cache.book import PAGE
 from ..sampling.params import SamplingParams
 from ..sampling.sampler import stream_seed
 
@@ -27,14 +28,20 @@ class Generation:
 
 @dataclass
 class LoopStats:
+    """What a run of the loop cost.  ``prefill_s`` and ``decode_s`` are the host's clock, as the
+    reference reports them (apps/ultima-cli/main.cpp:689-698); ``device_prefill_ms`` and
+    ``device_step_ms`` are the device's own time of the prompt step and of every decode step
+    (between marks the engine leaves on the stream), where the engine can give marks."""
     prompt_tokens: int = 0
     generated_tokens: int = 0
     prefill_s: float = 0.0
     decode_s: float = 0.0
     steps: int = 0
+    device_prefill_ms: float = 0.0
+    device_step_ms: list = field(default_factory=list)
 
 
-def plan_batches(prompt_lens: list, max_batch: int, max_tokens: int, n_predict: list, page: int = 64):
+def plan_batches(prompt_lens: list, max_batch: int, max_tokens: int, n_predict: list, page: int = PAGE):
     """Requests in order, cut into batches of at most ``max_batch`` whose tokens (prompt plus
     what may be generated, each rounded up to a page) fit ``max_tokens``."""
     def cost(i):
@@ -92,7 +99,11 @@ def run_batch(engine, sample, prompts: list, params: list, n_predict: list, stop
         owner = getattr(sample, "__self__", None)
         begin = getattr(sample, "begin", None) or getattr(owner, "begin", None)
         ahead = begin is not None and getattr(engine, "feeds_from_device", False)
+        mark = getattr(engine, "mark", None) if stats is not None else None
+        marks = [mark()] if mark else []
         logits = engine.step([slots[i] for i in live], [prompts[i] for i in live], None)
+        if mark:
+            marks.append(mark())
         if stats:
             stats.prompt_tokens += sum(len(prompts[i]) for i in live)
 
@@ -113,6 +124,8 @@ def run_batch(engine, sample, prompts: list, params: list, n_predict: list, stop
                 ids_dev = getattr(getattr(pending, "__self__", None), "ids_dev", None)
                 if ids_dev is not None:
                     next_logits = engine.step_fed([slots[i] for i in live], ids_dev)
+                    if mark:
+                        marks.append(mark())
             ids = pending()
             now = time.perf_counter()
             if stats:
@@ -150,11 +163,19 @@ def run_batch(engine, sample, prompts: list, params: list, n_predict: list, stop
                 pending = draw(next_logits if same else next_logits[rows], live, continuing=same)
             else:
                 logits = engine.step([slots[i] for i in live], feed, None, **borrow)
+                if mark:
+                    marks.append(mark())
                 pending = draw(logits, live)
         return out
     finally:
         if stats:
             stats.generated_tokens += sum(len(g.tokens) for g in out)
+            if len(marks) >= 2:
+                # a mark after every step: the prompt step, then one decode step (and the sampling
+                # of the step before it) between each two
+                ms = [engine.elapsed_ms(a, b) for a, b in zip(marks[:-1], marks[1:])]
+                stats.device_prefill_ms += ms[0]
+                stats.device_step_ms.extend(ms[1:])
         if held:
             engine.close([slots[i] for i in sorted(held)])
 
@@ -200,9 +221,8 @@ class LLM:
         from .engine import Engine
         from ..sampling.sampler import Sampler
         self.max_batch = int(max_batch)
-        page = 64
         if max_tokens is None:
-            max_tokens = self.max_batch * (-(-int(n_ctx) // page) * page)
+            max_tokens = self.max_batch * (-(-int(n_ctx) // PAGE) * PAGE)
         self.engine = Engine.from_dir(model_dir, dtype=dtype, max_tokens=max_tokens, max_context=n_ctx,
                                       max_seqs=self.max_batch, device=device, **engine_kw)
         self.sampler = Sampler(self.engine.device, self.engine.spec.vocab_size, self.engine.rt)

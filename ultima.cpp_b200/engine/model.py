@@ -20,13 +20,26 @@ def _trace(name: str, index: int, x: torch.Tensor) -> None:
 from ..parts.base import ModelSpec, build_part
 
 
-@dataclass
 class BuiltLayer:
-    arrangement: object
-    mixer: object
-    feed_forward: object
-    mixer_norm: object
-    feed_forward_norm: object
+    """A layer's arrangement and its parts, built and bound; a part is reached by its role
+    (``layer.mixer``, ``layer.parts["mixer"]``)."""
+
+    def __init__(self, arrangement, parts: dict):
+        self.arrangement, self.parts = arrangement, dict(parts)
+        for role, p in parts.items():
+            setattr(self, role, p)
+        holders = [p for p in parts.values() if getattr(p, "cache_need", None) is not None and p.cache_need() is not None]
+        if len(holders) > 1:
+            raise ValueError("a layer may hold one part that keeps a cache; this one has "
+                             + ", ".join(f"{p.family} '{p.kind}'" for p in holders))
+        self.cache_holder = holders[0] if holders else None
+
+    def cache_need(self):
+        return self.cache_holder.cache_need() if self.cache_holder is not None else None
+
+    @property
+    def graph_safe(self) -> bool:
+        return all(getattr(p, "graph_safe", False) for p in self.parts.values())
 
 
 class Model:
@@ -37,34 +50,31 @@ class Model:
 
         def bound(family, ps, prefix):
             p = build_part(family, ps)
-            rel = {s.name: tensors[prefix + s.name] for s in p.weight_specs()}
-            return p, rel
+            p.bind({s.name: tensors[prefix + s.name] for s in p.weight_specs()}, rt)
+            return p
 
-        self.embedding, rel = bound("embedding", spec.embedding, spec.embedding_name)
-        self.embedding.bind(rel, rt)
+        self.embedding = bound("embedding", spec.embedding, spec.embedding_name)
         self.layers = []
         for L in spec.layers:
-            parts = {}
-            for role, family, ps in (("mixer_norm", "norm", L.mixer_norm), ("mixer", "mixer", L.mixer),
-                                     ("feed_forward_norm", "norm", L.feed_forward_norm),
-                                     ("feed_forward", "feed_forward", L.feed_forward)):
-                p, rel = bound(family, ps, L.name_of(role))
-                p.bind(rel, rt)
-                parts[role] = p
-            self.layers.append(BuiltLayer(arrangement=build_part("arrangement", L.arrangement), **parts))
-        self.final_norm, rel = bound("norm", spec.final_norm, spec.final_norm_name)
-        self.final_norm.bind(rel, rt)
-        self.head, rel = bound("head", spec.head, spec.head_name)
+            arrangement = build_part("arrangement", L.arrangement)
+            parts = {role: bound(family, L.part(role), L.name_of(role)) for role, family in L.roles().items()}
+            self.layers.append(BuiltLayer(arrangement, parts))
+        self.final_norm = bound("norm", spec.final_norm, spec.final_norm_name)
+        self.head = build_part("head", spec.head)
         if spec.head.get("tied"):
-            rel = {"weight": self.embedding.table}
-        self.head.bind(rel, rt)
+            self.head.bind({"weight": self.embedding.table}, rt)
+        else:
+            self.head.bind({s.name: tensors[spec.head_name + s.name] for s in self.head.weight_specs()}, rt)
         for r in spec.runs:
             if not (0 <= r.layer < len(self.layers)):
                 raise ValueError(f"run list names layer {r.layer}; the model has {len(self.layers)}")
 
+    def all_parts(self) -> list:
+        return [self.embedding, self.final_norm, self.head] + [p for L in self.layers for p in L.parts.values()]
+
     def cache_needs(self):
-        """For each run of the run list, what its mixer asks of the cache."""
-        return [self.layers[r.layer].mixer.cache_need() for r in self.spec.runs]
+        """For each run of the run list, what its layer asks of the cache."""
+        return [self.layers[r.layer].cache_need() for r in self.spec.runs]
 
     def cache_sources(self):
         return [r.cache_from for r in self.spec.runs]

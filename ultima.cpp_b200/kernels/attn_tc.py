@@ -7,10 +7,9 @@ from ctypes import c_float, c_int, c_longlong, c_void_p
 import torch
 
 from . import build
-from .ops import KernelError, _check, _ptr, _stream
+from .ops import KernelError, _check, _ptr, _stream, sm_count
 
 SOURCE = "attn_mma.cu"
-N_SMS = 148
 import os as _os
 SLICE_FACTOR = int(_os.environ.get("ULTIMA_SLICE_FACTOR", "2"))
 SLICE_CAP = int(_os.environ.get("ULTIMA_SLICE_CAP", "16"))
@@ -139,13 +138,14 @@ def accepts(q, kv, head_dim, n_heads, n_kv_heads) -> bool:
             and q.data_ptr() % 16 == 0)
 
 
-def decode_slices(n_seqs: int, n_kv_heads: int, longest: int, window, per_sm: int = SLICE_FACTOR) -> int:
+def decode_slices(n_seqs: int, n_kv_heads: int, longest: int, window, per_sm: int = SLICE_FACTOR,
+                  n_sms: int | None = None) -> int:
     """Slices of the key range, so that a decode step with few sequences still fills the GPU
-    (``per_sm`` CTAs an SM)."""
+    (``per_sm`` CTAs an SM; ``n_sms``: the device's multiprocessors, asked of it when not given)."""
     span = longest if not window else min(longest, window + 64)
     tiles = max(1, -(-span // 64))
     ctas = n_seqs * n_kv_heads
-    want = -(-per_sm * N_SMS // ctas)
+    want = -(-per_sm * (n_sms or sm_count()) // ctas)
     n = max(1, min(want, tiles, SLICE_CAP))
     return 1 << (n.bit_length() - 1)            # a power of two: few distinct captured graphs
 

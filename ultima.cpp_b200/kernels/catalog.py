@@ -17,22 +17,18 @@ def all_targets() -> list:
 
 
 def targets_for_model(spec, dtype, sampler: bool = True) -> list:
-    """What one model needs: on the float32 path the CUDA-core product and the float32 attention; on
-    the bfloat16 path the tcgen05 product (the CUDA-core one stands in for shapes it refuses) and the
-    attention library of each head size the model's mixers use.  ``sampler``: the sampling kernel
-    too (a replay of given tokens samples nothing)."""
+    """What one model needs: the row-wise kernels and the CUDA-core product always (the latter stands
+    in for shapes the tensor-core product refuses), the tcgen05 product on the bfloat16 path, and
+    whatever the model's parts ask for themselves (``Part.kernel_needs``: the attention part names
+    the attention library of its head size).  ``sampler``: the sampling kernel too (a replay of
+    given tokens samples nothing)."""
     import torch
     out = [("basic.cu", ()), ("gemm_simt.cu", ())]
-    dims = sorted({L.mixer.get("head_dim") for L in spec.layers if L.mixer.get("head_dim")})
     if dtype == torch.bfloat16:
         out.append(("gemm_tcgen05.cu", ()))
-        fits = [hd for hd in dims if hd % 16 == 0 and 16 <= hd <= 256]
-        out += [("attn_mma.cu", (f"HEAD_DIM={hd}",)) for hd in fits]
-        out += [("attn_tcgen05.cu", (f"HEAD_DIM={hd}",)) for hd in fits if hd in TC_HEAD_DIMS]
-        if len(fits) != len(dims):
-            out.append(("attn_simple.cu", ()))
-    else:
-        out.append(("attn_simple.cu", ()))
+    for t in spec.kernel_needs(dtype):
+        if t not in out:
+            out.append(t)
     if sampler:
         out.append(("sampling.cu", ()))
     return out

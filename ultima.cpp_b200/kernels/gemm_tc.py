@@ -10,10 +10,9 @@ from ctypes import c_int, c_longlong, c_void_p
 import torch
 
 from . import build
-from .ops import EPI_ADD, EPI_STORE, EPI_SWIGLU, EPI_SWIGLU_IL, BF16, F32, KernelError, _check, _ptr, _stream
+from .ops import EPI_ADD, EPI_STORE, EPI_SWIGLU, EPI_SWIGLU_IL, BF16, F32, KernelError, _check, _ptr, _stream, sm_count
 
 SOURCE = "gemm_tcgen05.cu"
-N_SMS = 148
 _lib = None
 _maps: dict = {}
 
@@ -93,13 +92,15 @@ def token_tile(T: int, epilogue: int) -> int:
     return 256 if T > 192 else 128
 
 
-def cta_slots(bn: int, epilogue: int) -> int:
+def cta_slots(bn: int, epilogue: int, n_sms: int | None = None) -> int:
     """CTAs of this kernel that the GPU holds at once: two an SM for token tiles of up to 64 (their
-    shared-memory ring is kept to half an SM's), one otherwise."""
-    return 2 * N_SMS if (bn <= 64 and epilogue != EPI_SWIGLU) else N_SMS
+    shared-memory ring is kept to half an SM's), one otherwise.  ``n_sms``: the device's
+    multiprocessors (asked of the current device when not given)."""
+    n_sms = n_sms or sm_count()
+    return 2 * n_sms if (bn <= 64 and epilogue != EPI_SWIGLU) else n_sms
 
 
-def k_splits(T: int, N: int, K: int, bn: int, epilogue: int) -> int:
+def k_splits(T: int, N: int, K: int, bn: int, epilogue: int, n_sms: int | None = None) -> int:
     """Slices of K, so that a product with few tiles still fills the GPU, and never more CTAs than
     the GPU holds at once (a second wave would start only when the first has ended).  Only the
     add-into epilogue is split here (its slices meet in the float32 residual stream)."""
@@ -107,7 +108,7 @@ def k_splits(T: int, N: int, K: int, bn: int, epilogue: int) -> int:
         return 1
     tiles = -(-N // 128) * -(-T // bn)
     nkb = -(-K // 64)
-    slots = cta_slots(bn, epilogue)
+    slots = cta_slots(bn, epilogue, n_sms)
     if tiles * 2 > slots or nkb < 8:
         return 1
     s = max(1, min(slots // tiles, nkb // 4))
@@ -118,12 +119,12 @@ def k_splits(T: int, N: int, K: int, bn: int, epilogue: int) -> int:
 USE_PAIRS = os.environ.get("ULTIMA_GEMM_PAIRS", "1") != "0"
 
 
-def pairs(T: int, N: int, splits: int, epilogue: int) -> bool:
+def pairs(T: int, N: int, splits: int, epilogue: int, n_sms: int | None = None) -> bool:
     """Whether the product runs on pairs of CTAs (tiles of 256 weight rows by 256 tokens): many
     tokens, K whole, and at least one tile for every pair of SMs."""
     if not USE_PAIRS or splits != 1 or epilogue == EPI_SWIGLU or T <= 128:
         return False
-    return -(-N // 256) * -(-T // 256) >= N_SMS // 2
+    return -(-N // 256) * -(-T // 256) >= (n_sms or sm_count()) // 2
 
 
 def gemm(a, w, out, epilogue, w2, rt, splits: int | None = None, bn: int | None = None):
@@ -157,13 +158,13 @@ def gemm(a, w, out, epilogue, w2, rt, splits: int | None = None, bn: int | None 
     _check(rc, "gemm_tc")
 
 
-def store_splits(T: int, N: int, K: int) -> int:
+def store_splits(T: int, N: int, K: int, n_sms: int | None = None) -> int:
     """Slices of K for a product whose result is stored (not added): worth it only with few
     tokens, where the float32 partial results are small beside the weights."""
     bn = token_tile(T, EPI_STORE)
     tiles = -(-N // 128) * -(-T // bn)
     nkb = -(-K // 64)
-    slots = cta_slots(bn, EPI_STORE)
+    slots = cta_slots(bn, EPI_STORE, n_sms)
     if T > 64 or tiles * 2 > slots or nkb < 8:
         return 1
     # the float32 partial results (written, then read) stay below a quarter of the weight bytes

@@ -14,10 +14,26 @@ from . import build
 
 F32, BF16 = 0, 1
 EPI_STORE, EPI_ADD, EPI_SWIGLU, EPI_SWIGLU_IL = 0, 1, 2, 3
+MAX_HEAD_DIM = 256          # the largest head size the attention and q/k preparation kernels take
 
 
 class KernelError(RuntimeError):
     pass
+
+
+_sm_counts: dict = {}
+
+
+def sm_count(device=None) -> int:
+    """Streaming multiprocessors of the device (the current one by default), asked of the device once.
+    Slice counts, K splits and the choice between kernels follow it."""
+    if not torch.cuda.is_available():
+        raise KernelError("no CUDA device: the number of multiprocessors cannot be asked")
+    idx = torch.cuda.current_device() if device is None else torch.device(device).index or 0
+    n = _sm_counts.get(idx)
+    if n is None:
+        n = _sm_counts[idx] = int(torch.cuda.get_device_properties(idx).multi_processor_count)
+    return n
 
 
 def _code(t: torch.Tensor) -> int:
@@ -70,7 +86,9 @@ def _declare(lib, source: str) -> None:
         "basic.cu": {
             "ub_embed": [P, I, P, P, I, I, I, P, P],
             "ub_rmsnorm": [P, P, P, P, I, I, I, F, P],
-            "ub_qk_prepare": [P, I, I, L, P, I, L, P, P, P, P, P, P, P, P, I, P, I, I, I, I, I, I, I, F, I, P],
+            "ub_qk_prepare": [P, I, I, L, P, I, L, P, P, P, P, P, P, P, P, I, P, I, I, I, I, I, I, I, F, I, I, I, P, P, L, P],
+            "ub_rotate_pairs": [P, I, L, I, I, I, P, P, P, I, I, P],
+            "ub_kv_write": [P, P, I, L, P, P, P, P, I, P, I, I, I, I, I, I, P],
             "ub_silu_mul": [P, I, I, L, P, I, I, I, P],
             "ub_convert": [P, I, P, I, L, P],
             "ub_add_into": [P, P, I, L, P],
@@ -111,12 +129,17 @@ def rmsnorm(x, weight, out, eps, rows=None):
 
 
 def qk_prepare(qkv, q_weight, k_weight, cos, sin, tok_pos, tok_seq, k_cache, v_cache, table,
-               ring, page, n_heads, n_kv_heads, head_dim, eps, write_kv=True, q_out=None):
+               ring, page, n_heads, n_kv_heads, head_dim, eps, write_kv=True, q_out=None,
+               rotary_dim=None, interleaved=False, kv_out=None):
     """Per-head norm and rotation of q and k, and the write of k, v into the cache.
 
     qkv: [T, (heads + 2 kv heads) * head size], or [parts, T, ...] whose sum over parts it is
     (slices of K of the projection).  q goes to ``q_out`` ([T, heads * head size], any row stride),
-    or back into qkv's q columns when q_out is None (one part only)."""
+    or back into qkv's q columns when q_out is None (one part only).  cos, sin: [positions,
+    rotary_dim / 2]; the first ``rotary_dim`` columns of a head (default: all) are rotated, in pairs
+    (j, j + rotary_dim / 2) or, ``interleaved``, (2j, 2j + 1).  ``kv_out`` = (k, v), each
+    [T, kv heads * head size] with q_out's element type and one row stride: keys and values go
+    there instead of into the cache (see ``kv_write``)."""
     _need_cuda(qkv, k_cache, v_cache, table)
     width = (n_heads + 2 * n_kv_heads) * head_dim
     if qkv.dim() == 3:
@@ -133,14 +156,49 @@ def qk_prepare(qkv, q_weight, k_weight, cos, sin, tok_pos, tok_seq, k_cache, v_c
     assert table.dtype == torch.int32 and table.dim() == 2 and table.is_contiguous()
     for v in (q_weight, k_weight, cos, sin):
         assert v is None or (v.dtype == torch.float32 and v.is_contiguous())
+    rd = int(rotary_dim) if rotary_dim is not None else head_dim
     if cos is not None:
-        assert cos.shape[1] == head_dim // 2
+        if rd % 2 or not (2 <= rd <= head_dim):
+            raise KernelError(f"qk_prepare: rotary size {rd} must be even and at most the head size {head_dim}")
+        assert cos.shape[1] == rd // 2 and sin.shape == cos.shape
+    k_out = v_out = None
+    kv_stride = 0
+    if kv_out is not None:
+        k_out, v_out = kv_out
+        assert k_out.dtype == q_out.dtype == v_out.dtype and k_out.stride(1) == 1 and v_out.stride(1) == 1
+        assert k_out.stride(0) == v_out.stride(0) and k_out.shape == v_out.shape == (T, n_kv_heads * head_dim)
+        kv_stride = k_out.stride(0)
     _check(_lib("basic.cu").ub_qk_prepare(
         _ptr(qkv), _code(qkv), n_parts, part_stride, _ptr(q_out), _code(q_out), q_out.stride(0),
         _ptr(q_weight), _ptr(k_weight), _ptr(cos), _ptr(sin), _ptr(tok_pos),
         _ptr(tok_seq), _ptr(k_cache), _ptr(v_cache), _code(k_cache), _ptr(table), table.shape[1],
-        ring, page, T, n_heads, n_kv_heads, head_dim, float(eps), 1 if write_kv else 0, _stream()),
+        ring, page, T, n_heads, n_kv_heads, head_dim, float(eps), 1 if write_kv else 0,
+        rd, 1 if interleaved else 0, _ptr(k_out), _ptr(v_out), kv_stride, _stream()),
         "qk_prepare")
+
+
+def rotate_pairs(x, cos, sin, tok_pos, rotary_dim=None, interleaved=False):
+    """Rotate, in place, pairs of the first ``rotary_dim`` columns of every head of x [T, heads,
+    head size] (heads side by side in a row, any row stride) by the angles of each token's position."""
+    _need_cuda(x, cos, sin, tok_pos)
+    T, n_heads, hd = x.shape
+    assert x.stride(2) == 1 and x.stride(1) == hd and cos.dtype == torch.float32 and cos.is_contiguous()
+    rd = int(rotary_dim) if rotary_dim is not None else hd
+    assert cos.shape[1] == rd // 2 and sin.shape == cos.shape and tok_pos.dtype == torch.int32
+    _check(_lib("basic.cu").ub_rotate_pairs(_ptr(x), _code(x), x.stride(0), T, n_heads, hd, _ptr(cos), _ptr(sin),
+                                            _ptr(tok_pos), rd, 1 if interleaved else 0, _stream()), "rotate_pairs")
+
+
+def kv_write(k, v, tok_pos, tok_seq, k_cache, v_cache, table, ring, page, n_kv_heads, head_dim):
+    """k, v [T, kv heads * head size] (one row stride) into the paged cache at each token's position."""
+    _need_cuda(k, v, k_cache, v_cache, table)
+    T = k.shape[0]
+    assert k.shape == v.shape == (T, n_kv_heads * head_dim) and k.stride(1) == 1 and v.stride(1) == 1
+    assert k.stride(0) == v.stride(0) and k.dtype == v.dtype
+    assert table.dtype == torch.int32 and table.dim() == 2 and table.is_contiguous()
+    _check(_lib("basic.cu").ub_kv_write(_ptr(k), _ptr(v), _code(k), k.stride(0), _ptr(tok_pos), _ptr(tok_seq), _ptr(k_cache),
+                                        _ptr(v_cache), _code(k_cache), _ptr(table), table.shape[1], ring, page, T,
+                                        n_kv_heads, head_dim, _stream()), "kv_write")
 
 
 def silu_mul(gate_up, out):

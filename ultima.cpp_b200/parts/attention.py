@@ -1,5 +1,6 @@
 """The attention mixer: grouped-query attention over the cache, with optional per-head norm
-of queries and keys, an optional position encoding and an optional window."""
+of queries and keys, an optional position encoding (any part of the "position" family) and an
+optional window."""
 from __future__ import annotations
 
 import math
@@ -23,8 +24,11 @@ class Attention(Mixer):
     The three projections are held as one matrix [q | k | v] and run as one product.
     """
 
-    graph_safe = True        # launches kernels only; no host work that depends on the data
-
+    @property
+    def graph_safe(self) -> bool:
+        """Launches kernels only, no host work that depends on the data; a position encoding it holds
+        has to say the same of itself."""
+        return self.position is None or bool(getattr(self.position, "graph_safe", False))
 
     def __init__(self, width: int, n_heads: int, n_kv_heads: int, head_dim: int, qk_norm: bool,
                  eps: float, position: PartSpec | None, window: int | None = None,
@@ -51,7 +55,21 @@ class Attention(Mixer):
     def cache_need(self):
         return KVNeed(self.nkv, self.hd, self.window)
 
+    def kernel_needs(self, run_dtype):
+        from ..kernels import attn_tc, catalog
+        if run_dtype != torch.bfloat16:
+            return [("attn_simple.cu", ())]
+        if self.hd % 16 == 0 and 16 <= self.hd <= 256:
+            out = [attn_tc.target(self.hd)]
+            if self.hd in catalog.TC_HEAD_DIMS:
+                out.append(attn_tc.tc_target(self.hd))
+            return out
+        return [("attn_simple.cu", ())]
+
     def bind(self, tensors, rt):
+        if self.hd % 2 or self.hd > ops.MAX_HEAD_DIM:
+            raise ValueError(f"attention: head size {self.hd} is not one the kernels take (even, at most "
+                             f"{ops.MAX_HEAD_DIM})")
         ws = [tensors["q_proj.weight"], tensors["k_proj.weight"], tensors["v_proj.weight"]]
         if len({w.dtype for w in ws}) != 1:
             raise ValueError("q, k and v projections must share one element type")
@@ -66,15 +84,18 @@ class Attention(Mixer):
     def forward(self, h, residual, batch, cache, rt):
         T = h.shape[0]
         kv = cache.kv
-        cos = sin = None
-        if self.position is not None:
-            cos, sin = self.position.cos, self.position.sin
+        # A position encoding that describes itself as a rotation of pairs is applied by the kernels
+        # that norm and write the cache; any other is called between the norm and the cache write.
+        rot = self.position.rotation() if self.position is not None else None
+        apart = self.position is not None and rot is None
+        cos, sin = (rot.cos, rot.sin) if rot is not None else (None, None)
+        whole = rot is None or (rot.dim == self.hd and not rot.interleaved)
         o = rt.arena.alloc((T, self.q_width), rt.dtype)
         parts = rt.matmul_parts(h, self.wqkv)        # few tokens: K in slices, summed by the next kernel
         if parts is not None:
             # one token a sequence: the attention kernel can take the slices as they are
-            if rt.attention_from_qkv(parts, self.q_norm, self.k_norm, cos, sin, self.eps, kv, o, batch,
-                                     self.nh, self.nkv, self.hd, self.scale):
+            if not apart and whole and rt.attention_from_qkv(parts, self.q_norm, self.k_norm, cos, sin, self.eps, kv,
+                                                             o, batch, self.nh, self.nkv, self.hd, self.scale):
                 rt.matmul(o, self.wo, residual, ops.EPI_ADD)
                 return
             qkv = parts
@@ -84,8 +105,20 @@ class Attention(Mixer):
             rt.matmul(h, self.wqkv, qkv)
             q = qkv[:, :self.q_width]
         rt.launches += 1
-        ops.qk_prepare(qkv, self.q_norm, self.k_norm, cos, sin, batch.tok_pos, batch.tok_seq,
-                       kv.k, kv.v, kv.table, kv.ring, kv.page, self.nh, self.nkv, self.hd, self.eps,
-                       write_kv=kv.owner, q_out=q)
+        if apart:
+            kbuf = rt.arena.alloc((2, T, self.kv_width), q.dtype)
+            ops.qk_prepare(qkv, self.q_norm, self.k_norm, None, None, batch.tok_pos, batch.tok_seq,
+                           kv.k, kv.v, kv.table, kv.ring, kv.page, self.nh, self.nkv, self.hd, self.eps,
+                           write_kv=kv.owner, q_out=q, kv_out=(kbuf[0], kbuf[1]))
+            self.position.forward(q.view(T, self.nh, self.hd), kbuf[0].view(T, self.nkv, self.hd), batch.tok_pos, rt)
+            if kv.owner:
+                rt.launches += 1
+                ops.kv_write(kbuf[0], kbuf[1], batch.tok_pos, batch.tok_seq, kv.k, kv.v, kv.table, kv.ring, kv.page,
+                             self.nkv, self.hd)
+        else:
+            ops.qk_prepare(qkv, self.q_norm, self.k_norm, cos, sin, batch.tok_pos, batch.tok_seq,
+                           kv.k, kv.v, kv.table, kv.ring, kv.page, self.nh, self.nkv, self.hd, self.eps,
+                           write_kv=kv.owner, q_out=q, rotary_dim=rot.dim if rot is not None else None,
+                           interleaved=bool(rot.interleaved) if rot is not None else False)
         rt.attention(q, kv, o, batch, self.nh, self.nkv, self.hd, self.scale)
         rt.matmul(o, self.wo, residual, ops.EPI_ADD)
