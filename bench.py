@@ -625,10 +625,115 @@ def run_other(args):
     return 0
 
 
+REF_MODEL_SRCS = ["dtype", "tensor_info", "metadata_store", "loaded_model", "arch_registry", "qwen_config",
+                  "qwen_tensor_slots", "weight_dispatch", "qwen_block", "qwen_model", "hadamard"]
+REF_LAYERS = 2            # of the 36: what the reference's CPU code gets through in about a minute
+REF_PROMPT, REF_PREFILL_TOKENS = 64, 256
+
+
+def build_reference(say) -> str:
+    """The reference's own sources, copied unchanged into baseline/_ref/src and compiled there with g++
+    for the CPU (its CMake build fetches packages from the network and its file loader is for Windows
+    only, so the translation units of the model path are compiled directly), linked with
+    baseline/ref_bench.cpp.  Returns the program's path, or raises with the reason."""
+    import glob
+    import shutil
+    ref_root = os.path.join(ROOT, "baseline", "_ref")
+    exe = os.path.join(ref_root, "ref_bench")
+    harness = os.path.join(ROOT, "baseline", "ref_bench.cpp")
+    if os.path.isfile(exe) and os.path.getmtime(exe) >= os.path.getmtime(harness):
+        return exe
+    src = os.environ.get("ULTIMA_REFERENCE_DIR") or os.path.join(os.path.dirname(ROOT), "reference")
+    if not os.path.isfile(os.path.join(src, "src", "model", "qwen_model.cpp")):
+        raise RuntimeError("the reference's sources are not on this machine and no program was built before "
+                           "(set ULTIMA_REFERENCE_DIR to a checkout of tattooinmtl/Ultima.cpp)")
+    if not shutil.which("g++"):
+        raise RuntimeError("no g++ to compile the reference's sources with")
+    tree = os.path.join(ref_root, "src_tree")
+    for sub in ("include", "src"):
+        dst = os.path.join(tree, sub)
+        if not os.path.isdir(dst):
+            shutil.copytree(os.path.join(src, sub), dst)
+    inc = os.path.join(ref_root, "inc")
+    os.makedirs(os.path.join(inc, "nonstd"), exist_ok=True)
+    os.makedirs(os.path.join(ref_root, "obj"), exist_ok=True)
+    import torch
+    if not os.path.exists(os.path.join(inc, "fmt")):        # the header-only fmt inside the torch wheel, as a formatting library
+        shutil.copytree(os.path.join(os.path.dirname(torch.__file__), "include", "fmt"), os.path.join(inc, "fmt"))
+    with open(os.path.join(inc, "nonstd", "expected.hpp"), "w") as f:
+        f.write("#pragma once\n#include <expected>\nnamespace nonstd { using std::expected; using std::unexpected; }\n")
+    srcs = ["src/core/error.cpp", "src/runtime/thread_pool.cpp", "src/kv_cache/kv_cache.cpp",
+            "src/kv_cache/recurrent_state.cpp", "src/sampler/sampler.cpp"]
+    srcs += sorted(os.path.relpath(q, tree) for q in glob.glob(os.path.join(tree, "src/kernels/*.cpp")))
+    srcs += [f"src/model/{m}.cpp" for m in REF_MODEL_SRCS]
+    flags = ["-std=c++23", "-O2", "-mavx2", "-mfma", "-DFMT_HEADER_ONLY", "-include", "immintrin.h",
+             "-I", os.path.join(tree, "include"), "-I", os.path.join(tree, "src/model"), "-isystem", inc]
+    say(f"compiling {len(srcs)} files of the reference with g++ ...")
+    procs = []
+    for q in srcs:
+        obj = os.path.join(ref_root, "obj", q.replace("/", "_") + ".o")
+        if not os.path.exists(obj):
+            procs.append(subprocess.Popen(["g++"] + flags + ["-c", os.path.join(tree, q), "-o", obj]))
+        if len(procs) >= 8:
+            if any(pr.wait() != 0 for pr in procs):
+                raise RuntimeError("g++ failed on the reference's sources")
+            procs = []
+    if any(pr.wait() != 0 for pr in procs):
+        raise RuntimeError("g++ failed on the reference's sources")
+    objs = sorted(glob.glob(os.path.join(ref_root, "obj", "*.o")))
+    if subprocess.call(["g++"] + flags + [harness] + objs + ["-lpthread", "-o", exe]) != 0:
+        raise RuntimeError("g++ failed on baseline/ref_bench.cpp")
+    return exe
+
+
 def run_reference(args):
-    why = ("the reference is a CPU-only C++/CMake program with no Python package, no CUDA code and a "
-           "Windows-only model loader; the offline pip install of it fails (no setup.py or pyproject.toml)")
-    print(json.dumps({"impl": "reference", "unavailable": why}), flush=True)
+    """The reference arm: the reference's unmodified model code through its own public interface, on the
+    CPU it is written for (it has no GPU code), same metric and unit.  It has no batch, so the eight
+    sequences of a step run one after another; it runs REF_LAYERS of the 36 layers, from prompts of
+    REF_PROMPT tokens, and both are named in ``config``.  When neither a program built before nor the
+    sources and a compiler are there, the line says ``unavailable`` with the reason."""
+    def say(msg):
+        print(f"[bench] {msg}", file=sys.stderr, flush=True)
+    try:
+        exe = build_reference(say)
+    except Exception as e:
+        print(json.dumps({"impl": "reference", "unavailable": str(e)}), flush=True)
+        return 0
+    c = QWEN3_8B
+    steps = args.steps if args.steps is not None else 16
+    warmup = max(1, min(args.warmup, 3))
+    threads = os.cpu_count() or 1
+    cmd = [exe] + [str(x) for x in (REF_LAYERS, c["hidden_size"], c["intermediate_size"], c["num_attention_heads"],
+                                    c["num_key_value_heads"], c["head_dim"], c["vocab_size"], BATCH, REF_PROMPT, steps,
+                                    warmup, REF_PREFILL_TOKENS, threads)]
+    say("running " + " ".join(cmd[1:]))
+    try:
+        res = subprocess.run(cmd, capture_output=True, text=True, timeout=1400)
+    except subprocess.TimeoutExpired:
+        print(json.dumps({"impl": "reference", "unavailable": "the reference's program did not end within its time limit"}), flush=True)
+        return 0
+    if res.returncode != 0 or not res.stdout.strip():
+        print(json.dumps({"impl": "reference", "unavailable": f"the reference's program ended with code {res.returncode}: "
+                          + res.stderr.strip()[-200:]}), flush=True)
+        return 0
+    dec, pre, ms_step, pre_ms = (float(x) for x in res.stdout.split())
+    out = {
+        "metric": "decode tokens/s, Qwen3-8B sizes, bf16, batch 8, 2048-token prompts",
+        "value": round(dec, 3), "unit": "tokens/s", "n_gpus": 1, "steps": steps, "warmup": warmup,
+        "ms_per_step": round(ms_step, 3), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16 weights, fp32 arithmetic (the reference's only arithmetic)",
+        "data": "synthetic: random weights from a hash, token ids from a hash",
+        "config": {"model": "Qwen3-8B sizes", "layers": REF_LAYERS, "layers_full": c["num_hidden_layers"],
+                   "hidden": c["hidden_size"], "heads": c["num_attention_heads"], "kv_heads": c["num_key_value_heads"],
+                   "head_dim": c["head_dim"], "intermediate": c["intermediate_size"], "vocab": c["vocab_size"],
+                   "global_batch": BATCH, "batching": "none: the sequences of a step one after another",
+                   "prompt_len": REF_PROMPT, "device": "cpu", "threads": threads, "parallelism": "the host's cores"},
+        # the reference's interface is the host's: token ids in, logits out, its own argmax; nothing is copied
+        "e2e": {"value": round(dec, 3), "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0, "prefill": {"value": round(pre, 2), "tokens": REF_PREFILL_TOKENS, "ms": round(pre_ms, 2)},
+        "impl": "reference",
+    }
+    print(json.dumps(out), flush=True)
     return 0
 
 
