@@ -10,10 +10,18 @@ CONFIGS = {
     "B": dict(architectures=["Qwen3ForCausalLM"], vocab_size=1000, hidden_size=96, intermediate_size=320,
               num_hidden_layers=3, num_attention_heads=8, num_key_value_heads=1, head_dim=32,
               rms_norm_eps=1e-5, rope_theta=1000000.0, max_position_embeddings=256, tie_word_embeddings=False),
+    # a window of 4 positions on the first and the last of three layers (the reference's keys
+    # attention.sliding_window and attention.sliding_window_pattern, src/model/qwen_config.cpp:229-253)
+    "C": dict(architectures=["Qwen3ForCausalLM"], vocab_size=300, hidden_size=48, intermediate_size=80,
+              num_hidden_layers=3, num_attention_heads=3, num_key_value_heads=1, head_dim=16,
+              rms_norm_eps=1e-6, rope_theta=10000.0, max_position_embeddings=64, tie_word_embeddings=False,
+              use_sliding_window=True, sliding_window=4,
+              layer_types=["sliding_attention", "full_attention", "sliding_attention"]),
 }
 PROMPTS = {"A": [(37 * i * i + 11 * i + 5) % 512 for i in range(11)],
-           "B": [(91 * i * i + 7 * i + 3) % 1000 for i in range(40)]}
-KEPT = {"A": list(range(11)), "B": [0, 1, 31, 32, 39]}       # positions whose logits are stored
+           "B": [(91 * i * i + 7 * i + 3) % 1000 for i in range(40)],
+           "C": [(53 * i * i + 17 * i + 2) % 300 for i in range(16)]}
+KEPT = {"A": list(range(11)), "B": [0, 1, 31, 32, 39], "C": list(range(16))}       # positions whose logits are stored
 
 
 def _uniform(n: int, salt: int) -> np.ndarray:

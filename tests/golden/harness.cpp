@@ -3,9 +3,10 @@
 // Windows only, so the model reaches it through its abstract LoadedModel interface, as its own
 // configuration tests do (tests/unit/test_qwen_config.cpp:18-38).
 //
-// input file: int32 {layers, hidden, ffn, heads, kv_heads, head_dim, vocab, ctx, tied, n_tokens},
-//             float32 {eps, theta}, int32 tokens[n_tokens], then every tensor as float32 in the
-//             order of golden_weights.tensor_list.
+// input file: int32 {layers, hidden, ffn, heads, kv_heads, head_dim, vocab, ctx, tied, n_tokens, window},
+//             int32 pattern[layers] (1: the layer attends to the last ``window`` positions only; all 0
+//             and window 0 for a model without a window), float32 {eps, theta}, int32 tokens[n_tokens],
+//             then every tensor as float32 in the order of golden_weights.tensor_list.
 // output file: float32 logits [n_tokens, vocab] from token-by-token decode, then float32
 //              logits [vocab] of a whole-prompt prefill (its last position).
 #include "ultima/kv_cache/kv_cache.hpp"
@@ -27,6 +28,7 @@ struct Mem : LoadedModel {
     MetadataStore md;
     std::vector<TensorInfo> infos;
     std::map<std::string, std::vector<float>, std::less<>> data;
+    std::vector<std::uint8_t> blob;        // what stands in for the file: the per-layer window pattern
 
     void add(const std::string& name, std::vector<std::uint64_t> dims_inner_first, std::vector<float> v) {
         TensorInfo ti;
@@ -43,10 +45,10 @@ struct Mem : LoadedModel {
             if (ti.name == name) return TensorView{ti, data.find(name)->second.data()};
         return std::nullopt;
     }
-    std::uint64_t file_size_bytes() const override { return 0; }
+    std::uint64_t file_size_bytes() const override { return blob.size(); }
     std::uint64_t alignment() const override { return 32; }
     std::uint32_t gguf_version() const override { return 3; }
-    const std::uint8_t* file_data() const override { return nullptr; }
+    const std::uint8_t* file_data() const override { return blob.empty() ? nullptr : blob.data(); }
 };
 
 static std::vector<float> rd(FILE* f, std::size_t n) {
@@ -59,11 +61,14 @@ int main(int argc, char** argv) {
     if (argc != 3) { std::fprintf(stderr, "usage: harness IN OUT\n"); return 2; }
     FILE* f = std::fopen(argv[1], "rb");
     if (!f) return 2;
-    std::int32_t h[10];
-    if (std::fread(h, 4, 10, f) != 10) return 3;
+    std::int32_t h[11];
+    if (std::fread(h, 4, 11, f) != 11) return 3;
     const std::uint64_t L = h[0], H = h[1], F = h[2], nh = h[3], nkv = h[4], hd = h[5], V = h[6], ctx = h[7];
     const bool tied = h[8] != 0;
     const int n_tok = h[9];
+    const std::uint64_t window = h[10];
+    std::vector<std::int32_t> pattern(L);
+    if (std::fread(pattern.data(), 4, L, f) != L) return 3;
     float fl[2];
     if (std::fread(fl, 4, 2, f) != 2) return 3;
     std::vector<std::int32_t> toks(n_tok);
@@ -81,6 +86,13 @@ int main(int argc, char** argv) {
     m.md.insert("qwen3.attention.layer_norm_rms_epsilon", MetadataValue{fl[0]});
     m.md.insert("qwen3.rope.freq_base", MetadataValue{fl[1]});
     m.md.insert("tokenizer.ggml.tokens", MetadataValue{std::vector<std::string>(V, "x")});
+    if (window > 0) {
+        // the window engages only with both keys (src/model/qwen_config.cpp:229-253); the pattern is an
+        // array that the reference reads from the file's bytes (src/model/loaded_model.cpp:50-61)
+        for (auto v : pattern) m.blob.push_back(v ? 1 : 0);
+        m.md.insert("qwen3.attention.sliding_window", MetadataValue{std::uint64_t{window}});
+        m.md.insert("qwen3.attention.sliding_window_pattern", MetadataValue{MetadataArrayView{0, L, 0}});
+    }
 
     m.add("token_embd.weight", {H, V}, rd(f, V * H));
     for (std::uint64_t i = 0; i < L; ++i) {

@@ -1,6 +1,7 @@
 #!/usr/bin/env python3
-"""Makes tests/golden/tiny_{A,B}.npz: the logits of the reference's own model code
-(tattooinmtl/Ultima.cpp, compiled unchanged for the CPU) on two tiny Qwen3 models.
+"""Makes tests/golden/tiny_{A,B,C}.npz: the logits of the reference's own model code
+(tattooinmtl/Ultima.cpp, compiled unchanged for the CPU) on three tiny Qwen3 models (C has a
+sliding window on two of its three layers).
 
     python tests/golden/make_golden.py /path/to/Ultima.cpp [build_dir]
 
@@ -68,10 +69,12 @@ def run(exe: str, name: str, bdir: str):
     w = G.weights(cfg)
     inp, out = os.path.join(bdir, f"{name}.in"), os.path.join(bdir, f"{name}.out")
     with open(inp, "wb") as f:
-        f.write(struct.pack("<10i", cfg["num_hidden_layers"], cfg["hidden_size"], cfg["intermediate_size"],
+        f.write(struct.pack("<11i", cfg["num_hidden_layers"], cfg["hidden_size"], cfg["intermediate_size"],
                             cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["head_dim"],
                             cfg["vocab_size"], cfg["max_position_embeddings"], int(cfg["tie_word_embeddings"]),
-                            len(toks)))
+                            len(toks), int(cfg.get("sliding_window") or 0)))
+        types = cfg.get("layer_types") or ["full_attention"] * cfg["num_hidden_layers"]
+        f.write(struct.pack(f"<{len(types)}i", *[int(t == "sliding_attention") for t in types]))
         f.write(struct.pack("<2f", cfg["rms_norm_eps"], cfg["rope_theta"]))
         f.write(np.asarray(toks, dtype="<i4").tobytes())
         for n, _, _ in G.tensor_list(cfg):
@@ -93,5 +96,5 @@ if __name__ == "__main__":
     ref = sys.argv[1]
     bdir = sys.argv[2] if len(sys.argv) > 2 else os.path.join(tempfile.gettempdir(), "ultima_golden_build")
     exe = build(ref, bdir)
-    for name in ("A", "B"):
+    for name in ("A", "B", "C"):
         run(exe, name, bdir)

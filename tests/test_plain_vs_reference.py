@@ -1,8 +1,10 @@
 """The plain implementation against the reference's own model code (no GPU).
 
-tests/golden/tiny_{A,B}.npz hold the logits that tattooinmtl/Ultima.cpp's model code, compiled
-unchanged for the CPU by tests/golden/make_golden.py, gives on two tiny Qwen3 models whose
-weights come from integer arithmetic (tests/golden/golden_weights.py).  The reference computes
+tests/golden/tiny_{A,B,C}.npz hold the logits that tattooinmtl/Ultima.cpp's model code, compiled
+unchanged for the CPU by tests/golden/make_golden.py, gives on three tiny Qwen3 models whose
+weights come from integer arithmetic (tests/golden/golden_weights.py); the third has a sliding
+window of 4 positions on two of its three layers, which pins the window's edge (p - window, p] and
+its per-layer pattern to the reference's own code.  The reference computes
 in float32, the plain implementation in float64; they agree to float32 rounding.  The reference's
 whole-prompt logits equal its token-by-token logits exactly, which the files record too."""
 import os
@@ -17,7 +19,7 @@ import golden_weights as G  # noqa: E402
 import plain_qwen3 as P  # noqa: E402
 
 
-@pytest.mark.parametrize("name", ["A", "B"])
+@pytest.mark.parametrize("name", ["A", "B", "C"])
 def test_plain_matches_the_reference(name):
     gold = np.load(os.path.join(HERE, "golden", f"tiny_{name}.npz"))
     cfg = G.CONFIGS[name]
