@@ -4,6 +4,7 @@ shorter requests end earlier, one batch after another so that slots are used aga
 decoding; the first tokens of a sequence."""
 import numpy as np
 import pytest
+import torch
 
 from conftest import TINY, random_ids, close_enough
 
@@ -238,3 +239,56 @@ def test_sizes_that_fit_no_tensor_core_kernel(model_dirs, plain_models, dtype):
     _check(np.concatenate(rows), ref, dtype, "F", "70 tokens, then one by one beside a second sequence")
     eng.check_errors()
     assert eng.cache.pages_held() == 0
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", ["B", "E"])
+def test_logits_with_range(tmp_path, name, dtype):
+    """The same comparisons on a model whose matrices are five times as large as a random model's, so
+    that its logits reach well beyond 1: the bound, which is relative to the largest logit, is then
+    small beside the logits' spread and a key weighted wrongly would show, not only a key lost."""
+    import json
+    import os
+    import plain_qwen3 as P
+    import ultima_b200 as u
+    from ultima_b200.engine import Engine
+    from ultima_b200.weights import random_tensors, write_safetensors
+    cfg = u.config_from_dict(TINY[name])
+    spec = u.model_spec_for(cfg)
+    tensors = random_tensors(spec.weight_specs(), 13, torch.bfloat16)
+    for s_ in spec.weight_specs():
+        if s_.kind == "matrix":
+            tensors[s_.name] = (tensors[s_.name].float() * 5.0).to(torch.bfloat16)
+    d = str(tmp_path / "wide")
+    os.makedirs(d)
+    with open(os.path.join(d, "config.json"), "w") as f:
+        json.dump(cfg.to_dict(), f)
+    write_safetensors(os.path.join(d, "model.safetensors"), tensors)
+    pc, pw = P.read_folder(d)
+    V, L = cfg.vocab_size, cfg.num_hidden_layers
+    eng = Engine.from_dir(d, dtype=dtype, max_tokens=1024, max_seqs=3, poison_cache=True)
+    seqs = [random_ids(200 + i, n, V) for i, n in enumerate((100, 37, 66))]
+    refs = [P.forward(pc, pw, s_) for s_ in seqs]
+    assert min(float(np.abs(r).max()) for r in refs) > 3.0 and min(float(r.std()) for r in refs) > 0.5
+    # whole; then prompts together and the last 32 tokens one by one, the shorter ones leaving first
+    sl = eng.open(1)
+    got = eng.step(sl, [seqs[0]], [list(range(100))]).cpu().numpy()
+    eng.close(sl)
+    err, bound = close_enough(got, refs[0], dtype, L)
+    assert err <= bound, f"whole [{name} {dtype}]: {err:.3e} > {bound:.3e} (spread {refs[0].std():.2f})"
+    cut = [len(s_) - 32 for s_ in seqs]
+    sl = eng.open(3)
+    out = eng.step(sl, [s_[:c] for s_, c in zip(seqs, cut)], [list(range(c)) for c in cut]).cpu().numpy()
+    rows, o = [], 0
+    for c in cut:
+        rows.append([out[o:o + c]])
+        o += c
+    for t in range(32):
+        out = eng.step(sl, [[s_[c + t]] for s_, c in zip(seqs, cut)]).cpu().numpy()
+        for i in range(3):
+            rows[i].append(out[i:i + 1])
+    eng.close(sl)
+    for i in range(3):
+        g = np.concatenate(rows[i])
+        err, bound = close_enough(g, refs[i], dtype, L)
+        assert err <= bound, f"request {i} [{name} {dtype}]: {err:.3e} > {bound:.3e} (spread {refs[i].std():.2f})"

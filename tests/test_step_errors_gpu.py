@@ -152,3 +152,15 @@ def test_truncate_is_refused_where_a_window_has_let_go_of_the_past(model_dirs):
     eng.truncate(s[0], 0)                                          # to the start it can
     assert eng.length(s[0]) == 0
     eng.close(s)
+
+
+def test_a_head_size_no_kernel_takes_is_refused_when_the_engine_is_built():
+    import ultima_b200 as u
+    from ultima_b200.engine import Engine
+    from ultima_b200.weights import random_tensors
+    cfg = u.config_from_dict(dict(TINY["A"], head_dim=272, num_attention_heads=2, num_key_value_heads=1))
+    spec = u.model_spec_for(cfg)
+    tensors = {k: v.to("cuda:0") for k, v in random_tensors(spec.weight_specs(), 1).items()}
+    for dtype in ("float32", "bfloat16"):
+        with pytest.raises(ValueError, match="head size 272 is not one the kernels take"):
+            Engine(spec, tensors, dtype=dtype, max_tokens=256)

@@ -62,8 +62,8 @@ class Engine:
         torch.cuda.set_device(self.device)
         self.rt = runtime or Runtime(self.device, self.dtype)
         from ..kernels import build as _build, catalog as _catalog
+        self.model = Model(spec, tensors, self.rt)        # parts refuse sizes no kernel takes here, before anything is compiled
         _build.prebuild(_catalog.targets_for_model(spec, self.dtype, sampler=with_sampler))     # nvcc runs side by side
-        self.model = Model(spec, tensors, self.rt)
         self.max_tokens = int(max_tokens)
         self.max_context = int(min(max_context or spec.max_positions, spec.max_positions))
         self.max_step_tokens = int(max_step_tokens)
