@@ -124,8 +124,9 @@ def fill_cache(engine, slots, n_tokens):
 def measured_peaks():
     """What this GPU gives a plain device-to-device copy (bytes read + bytes written a second, 4 GiB a
     buffer) and the library's bfloat16 product (8192^3, a burst of 20 and a loop of about two seconds):
-    the same kind of figures as the denominators in MEASURED_PEAKS.json, for the box a run was taken on.
-    Nothing of the library under test runs here."""
+    the same kind of figures as the denominators in MEASURED_PEAKS.json, for the box a run was taken on;
+    and the library's product on the four shapes of a prompt layer.  Nothing of the library under test
+    runs here."""
     import torch
     dev = torch.device("cuda:0")
     torch.cuda.set_device(dev)
@@ -160,9 +161,28 @@ def measured_peaks():
     clocks.start()
     loop_ms = timed(lambda: torch.matmul(x, y, out=out), reps)
     clk = clocks.stop()
+    # the library's product on the four shapes of a 2,048-token prompt's layer (weights rotated so that they
+    # come from memory as in a model): what these shapes allow, against the 8192^3 figure the fractions use
+    shapes = {}
+    c = QWEN3_8B
+    q, kv, h, f = c["num_attention_heads"] * c["head_dim"], c["num_key_value_heads"] * c["head_dim"], c["hidden_size"], c["intermediate_size"]
+    for name, n, k in (("qkv", q + 2 * kv, h), ("output", h, q), ("gate_up", 2 * f, h), ("down", h, f)):
+        a = torch.randn(PREFILL_TOKENS, k, device=dev, dtype=torch.bfloat16)
+        ws = [torch.randn(n, k, device=dev, dtype=torch.bfloat16) for _ in range(4)]
+        o = torch.empty(PREFILL_TOKENS, n, device=dev, dtype=torch.bfloat16)
+        turn = [0]
+
+        def one():
+            torch.matmul(a, ws[turn[0] % 4].t(), out=o)
+            turn[0] += 1
+        for _ in range(5):
+            one()
+        us = timed(one, 30) * 1e3
+        shapes[name] = {"us": round(us, 1), "tflops": round(2.0 * PREFILL_TOKENS * n * k / us / 1e6, 1)}
+        del a, ws, o
     print(json.dumps({"only": "peaks", "copy_gbs": round(copy_gbs, 1), "bf16_tflops_burst": round(flop / burst_ms / 1e9, 1),
                       "bf16_tflops_loop": round(flop / loop_ms / 1e9, 1), "loop_reps": reps, "clocks": clk,
-                      "in_use": peaks()}))
+                      "library_on_prompt_shapes": shapes, "in_use": peaks()}))
     return 0
 
 
