@@ -68,6 +68,7 @@ class Model:
         for r in spec.runs:
             if not (0 <= r.layer < len(self.layers)):
                 raise ValueError(f"run list names layer {r.layer}; the model has {len(self.layers)}")
+        self._stack = None            # see _stack_plan
 
     def all_parts(self) -> list:
         return [self.embedding, self.final_norm, self.head] + [p for L in self.layers for p in L.parts.values()]
@@ -79,6 +80,15 @@ class Model:
     def cache_sources(self):
         return [r.cache_from for r in self.spec.runs]
 
+    def _stack_plan(self, cache):
+        """The plan that runs all layers of a decode step as one resident kernel, if this model's layers
+        are of the kinds that kernel takes (kernels/decode_stack.py); None otherwise."""
+        if self._stack is None:
+            from ..kernels import decode_stack
+            self._stack = decode_stack.StackPlan(self, self.rt, cache) if not TRACE and \
+                decode_stack.StackPlan.fits(self, self.rt, cache) else False
+        return self._stack or None
+
     def forward(self, batch, cache) -> torch.Tensor:
         """Logits (float32 [wanted rows, vocabulary]) of one step; the cache is read and
         extended in place."""
@@ -87,11 +97,15 @@ class Model:
         x = self.embedding.forward(batch.tok_ids, rt)
         if TRACE:
             _trace("embd", 0, x)
-        for i, r in enumerate(self.spec.runs):
-            layer = self.layers[r.layer]
-            layer.arrangement.run(layer, x, batch, cache.run_cache(i, batch.tables), rt)
-            if TRACE:
-                _trace("l_out", i, x)
+        plan = self._stack_plan(cache) if (batch.max_new == 1 and batch.n_tokens <= 64) else None
+        if plan is not None:
+            plan.run(x, batch)                    # one token a sequence: the whole stack in one kernel
+        else:
+            for i, r in enumerate(self.spec.runs):
+                layer = self.layers[r.layer]
+                layer.arrangement.run(layer, x, batch, cache.run_cache(i, batch.tables), rt)
+                if TRACE:
+                    _trace("l_out", i, x)
         if batch.want_rows.numel() == 0:
             return torch.empty((0, self.spec.vocab_size), dtype=torch.float32, device=rt.device)
         h = self.final_norm.forward(x, rt, rows=batch.want_rows)

@@ -13,7 +13,8 @@ TC_HEAD_DIMS = (64, 128)          # head sizes the tcgen05 prefill attention is 
 
 def all_targets() -> list:
     return (list(PLAIN) + [("attn_mma.cu", (f"HEAD_DIM={hd}",)) for hd in HEAD_DIMS]
-            + [("attn_tcgen05.cu", (f"HEAD_DIM={hd}",)) for hd in TC_HEAD_DIMS])
+            + [("attn_tcgen05.cu", (f"HEAD_DIM={hd}",)) for hd in TC_HEAD_DIMS]
+            + [("decode_stack.cu", (f"HEAD_DIM={hd}",)) for hd in TC_HEAD_DIMS])
 
 
 def targets_for_model(spec, dtype, sampler: bool = True) -> list:
