@@ -196,7 +196,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
                 bool moved = false;
                 if (armed_k < n_tiles) {
                     const int j = armed_k, s = j % KV_STAGES;
-                    if (mbar_try_wait(&k_empty[s], (uint32_t)(((j / KV_STAGES) & 1) ^ 1))) {
+                    if (mbar_test_wait(&k_empty[s], (uint32_t)(((j / KV_STAGES) & 1) ^ 1))) {
                         const int row = row_of(j);
                         mbar_expect_tx(&k_full[s], KV_BYTES);
                         for (int nb = 0; nb < NB; ++nb) tma_load_2d(k_s + s * KV_BYTES + nb * BN * 128, &map_k, &k_full[s], nb * 64, row);
@@ -206,7 +206,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
                 }
                 if (armed_v < armed_k) {
                     const int j = armed_v, s = j % KV_STAGES;
-                    if (mbar_try_wait(&v_empty[s], (uint32_t)(((j / KV_STAGES) & 1) ^ 1))) {
+                    if (mbar_test_wait(&v_empty[s], (uint32_t)(((j / KV_STAGES) & 1) ^ 1))) {
                         const int row = row_of(j);
                         mbar_expect_tx(&v_full[s], KV_BYTES);
                         for (int nb = 0; nb < NB; ++nb) tma_load_2d(v_s + s * KV_BYTES + nb * BN * 128, &map_v, &v_full[s], nb * 64, row);
@@ -530,7 +530,7 @@ attn_tc_wide_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
                 bool moved = false;
                 if (armed_k < n_union) {
                     const int j = armed_k, s = j % S;
-                    if (mbar_try_wait(&k_empty[s], (uint32_t)(((j / S) & 1) ^ 1))) {
+                    if (mbar_test_wait(&k_empty[s], (uint32_t)(((j / S) & 1) ^ 1))) {
                         const int row = row_of(j);
                         mbar_expect_tx(&k_full[s], KV_BYTES);
                         for (int nb = 0; nb < NB; ++nb) tma_load_2d(k_s + s * KV_BYTES + nb * BN * 128, &map_k, &k_full[s], nb * 64, row);
@@ -540,7 +540,7 @@ attn_tc_wide_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
                 }
                 if (armed_v < armed_k) {
                     const int j = armed_v, s = j % S;
-                    if (mbar_try_wait(&v_empty[s], (uint32_t)(((j / S) & 1) ^ 1))) {
+                    if (mbar_test_wait(&v_empty[s], (uint32_t)(((j / S) & 1) ^ 1))) {
                         const int row = row_of(j);
                         mbar_expect_tx(&v_full[s], KV_BYTES);
                         for (int nb = 0; nb < NB; ++nb) tma_load_2d(v_s + s * KV_BYTES + nb * BN * 128, &map_v, &v_full[s], nb * 64, row);
