@@ -312,11 +312,13 @@ UB_API int ub_kv_write(const void* k, const void* v, int dtype, long long kv_str
     return 0;
 }
 
-// The same for head sizes of 64, 128 and 256: a lane holds E = hd / 32 neighbouring elements, the
-// lower 16 lanes the first half of the head and the upper 16 the second, so the partner of a
-// rotation pair sits 16 lanes away and every access is one aligned vector.
+// The same for head sizes of 64, 128 and 256.  Sixteen lanes take a head: a lane holds E = hd / 32
+// neighbouring elements of the head's first half and the E elements of the second half that pair with
+// them in the rotation, so the rotation needs no exchange between lanes, the sum of squares four, and
+// every access is one aligned vector.  Two heads a warp and instruction mean half as many instructions a
+// byte as a head a warp, which is what this kernel is short of (its loads are small and many).
 template <typename TA, typename TQ, typename TC, int E>
-__global__ void __launch_bounds__(256, E <= 4 ? 4 : 2) qk_prepare_vec_kernel(const TA* qkv, int n_parts, long long part_stride,
+__global__ void __launch_bounds__(256, 3) qk_prepare_vec_kernel(const TA* qkv, int n_parts, long long part_stride,
                                       TQ* q_out, long long q_out_stride, const float* __restrict__ qw,
                                       const float* __restrict__ kw, const float* __restrict__ cs,
                                       const float* __restrict__ sn, const int* __restrict__ tok_pos,
@@ -324,82 +326,106 @@ __global__ void __launch_bounds__(256, E <= 4 ? 4 : 2) qk_prepare_vec_kernel(con
                                       TC* __restrict__ vcache, PagedKV c, int n_tokens, int nh, float eps,
                                       int write_kv) {
     pdl_trigger();
-    // blockIdx.x is the token; the warps of its blocks take the token's heads in turn, so what belongs
-    // to the token (its position, the cosines and sines of that position, the norm weights) is fetched
-    // once a warp, and before the kernel that writes qkv has ended: none of it is written by a kernel
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, n_warps = blockDim.x >> 5;
+    // blockIdx.x is the token; the half-warps of its blocks take the token's heads in turn, so what
+    // belongs to the token (its position, the cosines and sines of that position, the norm weights) is
+    // fetched once a lane, and before the kernel that writes qkv has ended: none of it is written by a kernel
+    const int hl = threadIdx.x & 15, hw = threadIdx.x >> 4, n_hw = blockDim.x >> 4;
     const int heads_all = nh + 2 * c.n_kv_heads;
     const int t = blockIdx.x;
     constexpr int hd = 32 * E, half = hd / 2;
     const int pos = tok_pos[t];
     const int seq = tok_seq[t];
-    float co[E], si[E], gq[E], gk[E];
-    if (qw) load_vec<float, E>(qw + lane * E, gq);
-    if (kw) load_vec<float, E>(kw + lane * E, gk);
-    const bool upper = lane >= 16;
+    float co[E], si[E], gq[2][E], gk[2][E];
+    if (qw) { load_vec<float, E>(qw + hl * E, gq[0]); load_vec<float, E>(qw + half + hl * E, gq[1]); }
+    if (kw) { load_vec<float, E>(kw + hl * E, gk[0]); load_vec<float, E>(kw + half + hl * E, gk[1]); }
     // where the token's keys and values go: the page is looked up once, a head is then a stride away
     const int li = pos % c.ring;
     const long long kv_at = write_kv ? (((long long)c.table[(long long)seq * c.pages_per_seq + li / c.page] * c.n_kv_heads) * c.page
-                                        + (li % c.page)) * hd + lane * E : 0;
+                                        + (li % c.page)) * hd + hl * E : 0;
     const long long kv_head_stride = (long long)c.page * hd;
-    const TA* trow = qkv + (long long)t * heads_all * hd + lane * E;
-    TQ* qrow = q_out + (long long)t * q_out_stride + lane * E;
+    const TA* trow = qkv + (long long)t * heads_all * hd + hl * E;
+    TQ* qrow = q_out + (long long)t * q_out_stride + hl * E;
     pdl_wait();
-    // four of the warp's heads at a time: the loads of all four are in flight before the first is used
-    const int h_step = n_warps * gridDim.y;
-    const int h_first = blockIdx.y * n_warps + warp;
-    for (int h0 = h_first; h0 < heads_all; h0 += 4 * h_step) {
-        float v4[4][E];
+    // three of the half-warp's heads at a time (all of them where a token has up to 48 heads and its block
+    // sixteen half-warps): their loads are in flight before the first is used
+    constexpr int UH = 3;
+    const int h_step = n_hw * gridDim.y;
+    // (the loop's count is the same for both halves of a warp: they meet in the shuffles below)
+    const int h_first = blockIdx.y * n_hw + (hw & ~1);
+    for (int hb = h_first; hb < heads_all; hb += UH * h_step) {
+        const int h0 = hb + (hw & 1);
+        float v3[UH][2][E];
 #pragma unroll
-        for (int u = 0; u < 4; ++u) {
+        for (int u = 0; u < UH; ++u) {
             const int h = h0 + u * h_step;
             const bool is_kv = h >= nh;
-            if (h < heads_all && !(is_kv && !write_kv))
-                load_vec<TA, E>(trow + h * hd, v4[u]);
+            if (h < heads_all && !(is_kv && !write_kv)) {
+                load_vec<TA, E>(trow + h * hd, v3[u][0]);
+                load_vec<TA, E>(trow + h * hd + half, v3[u][1]);
+            }
         }
-        if (cs && h0 == h_first) {
+        if (cs && hb == h_first) {
             // after the first heads' loads, which do not have to wait for the position as these do
-            const int j0 = (lane & 15) * E;                      // index of the pair within the half
-            load_vec<float, E>(cs + (long long)pos * half + j0, co);
-            load_vec<float, E>(sn + (long long)pos * half + j0, si);
+            load_vec<float, E>(cs + (long long)pos * half + hl * E, co);
+            load_vec<float, E>(sn + (long long)pos * half + hl * E, si);
         }
 #pragma unroll
-        for (int u = 0; u < 4; ++u) {
+        for (int u = 0; u < UH; ++u) {
             const int h = h0 + u * h_step;
-            if (h >= heads_all) break;
+            // (a half-warp whose head is past the last one still takes part in the shuffles below)
+            const bool live = h < heads_all;
             const bool is_v = h >= nh + c.n_kv_heads, is_k = !is_v && h >= nh;
-            if ((is_v || is_k) && !write_kv) continue;
-            float* v = v4[u];
-            const TA* row = trow + h * hd;
-            for (int p = 1; p < n_parts; ++p) {
-                float more[E];
-                load_vec<TA, E>(row + p * part_stride, more);
+            const bool skip = !live || ((is_v || is_k) && !write_kv);
+            float (*v)[E] = v3[u];
+            if (!skip) {
+                const TA* row = trow + h * hd;
+                for (int p = 1; p < n_parts; ++p) {
+                    float more[2][E];
+                    load_vec<TA, E>(row + p * part_stride, more[0]);
+                    load_vec<TA, E>(row + p * part_stride + half, more[1]);
 #pragma unroll
-                for (int i = 0; i < E; ++i) v[i] += more[i];
+                    for (int i = 0; i < E; ++i) { v[0][i] += more[0][i]; v[1][i] += more[1][i]; }
+                }
             }
-            if (is_v) {
-                store_vec<TC, E>(vcache + kv_at + (h - nh - c.n_kv_heads) * kv_head_stride, v);
-                continue;
+            if (!skip && is_v) {
+                TC* dst = vcache + kv_at + (h - nh - c.n_kv_heads) * kv_head_stride;
+                store_vec<TC, E>(dst, v[0]);
+                store_vec<TC, E>(dst + half, v[1]);
             }
-            if (is_k ? kw != nullptr : qw != nullptr) {
-                float ss = 0.f;
+            const bool normed = is_k ? kw != nullptr : qw != nullptr;
+            float ss = 0.f;
+            if (!skip && !is_v && normed) {
 #pragma unroll
-                for (int i = 0; i < E; ++i) ss += v[i] * v[i];
-                ss = warp_sum(ss);
+                for (int i = 0; i < E; ++i) ss += v[0][i] * v[0][i] + v[1][i] * v[1][i];
+            }
+            // the sum over the sixteen lanes of the head (all lanes of the warp take part)
+#pragma unroll
+            for (int o = 8; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+            if (skip || is_v) continue;
+            if (normed) {
                 const float inv = inv_rms(ss, (float)hd, eps);
 #pragma unroll
-                for (int i = 0; i < E; ++i) v[i] = v[i] * (is_k ? gk[i] : gq[i]) * inv;
+                for (int i = 0; i < E; ++i) {
+                    v[0][i] = v[0][i] * (is_k ? gk[0][i] : gq[0][i]) * inv;
+                    v[1][i] = v[1][i] * (is_k ? gk[1][i] : gq[1][i]) * inv;
+                }
             }
             if (cs) {
 #pragma unroll
                 for (int i = 0; i < E; ++i) {
-                    const float other = __shfl_xor_sync(0xffffffffu, v[i], 16);
-                    // lower lanes hold a (partner b): a c - b s; upper lanes hold b (partner a): a s + b c
-                    v[i] = upper ? other * si[i] + v[i] * co[i] : v[i] * co[i] - other * si[i];
+                    const float a = v[0][i], b = v[1][i];
+                    v[0][i] = a * co[i] - b * si[i];
+                    v[1][i] = a * si[i] + b * co[i];
                 }
             }
-            if (is_k) store_vec<TC, E>(kcache + kv_at + (h - nh) * kv_head_stride, v);
-            else store_vec<TQ, E>(qrow + h * hd, v);
+            if (is_k) {
+                TC* dst = kcache + kv_at + (h - nh) * kv_head_stride;
+                store_vec<TC, E>(dst, v[0]);
+                store_vec<TC, E>(dst + half, v[1]);
+            } else {
+                store_vec<TQ, E>(qrow + h * hd, v[0]);
+                store_vec<TQ, E>(qrow + h * hd + half, v[1]);
+            }
         }
     }
 }
@@ -426,10 +452,10 @@ UB_API int ub_qk_prepare(const void* qkv, int in_dtype, int n_parts, long long p
                          part_stride % 8 == 0 && q_out_stride % 8 == 0;
     // the vector kernel: whole heads rotated in halves, keys and values straight into the cache
     const bool vec = aligned && (hd == 64 || hd == 128 || hd == 256) && !k_out && (!cs || (rotary_dim == hd && !interleaved));
-    // blocks of 8 warps; with many tokens one block a token (its warps loop over the heads), with few
-    // tokens a warp a head
+    // blocks of 16 half-warps; with many tokens one block a token (its half-warps loop over the heads), with
+    // few tokens a half-warp a head
     const int heads_all = nh + 2 * nkv;
-    const dim3 vgrid(n_tokens, n_tokens >= 256 ? 1 : (heads_all + 7) / 8);
+    const dim3 vgrid(n_tokens, n_tokens >= 256 ? 1 : (heads_all + 15) / 16);
 #define LAUNCH_V(TA, TQ, TC, E) e = ub_launch_dependent(qk_prepare_vec_kernel<TA, TQ, TC, E>, vgrid, dim3(256), 0, st, \
         (const TA*)qkv, n_parts, part_stride, (TQ*)q_out, q_out_stride, qw, kw, cs, sn, tok_pos, tok_seq, \
         (TC*)kcache, (TC*)vcache, c, n_tokens, nh, eps, write_kv)
