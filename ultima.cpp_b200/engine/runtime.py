@@ -11,6 +11,10 @@ import torch
 from ..kernels import ops
 
 
+_ELEMENT_SIZE = {torch.float32: 4, torch.bfloat16: 2, torch.float16: 2, torch.int32: 4, torch.int64: 8,
+                 torch.uint8: 1, torch.int8: 1, torch.float64: 8, torch.int16: 2, torch.bool: 1}
+
+
 class Arena:
     """Scratch memory for one step: a bump allocator over one buffer, reset layer by layer.
     A request that does not fit gets a fresh, larger buffer (earlier tensors stay valid
@@ -42,7 +46,7 @@ class Arena:
         n = 1
         for s in shape:
             n *= int(s)
-        nbytes = n * torch.empty((), dtype=dtype).element_size()
+        nbytes = n * _ELEMENT_SIZE[dtype]
         start = -(-self._off // self.ALIGN) * self.ALIGN
         if start + nbytes > self._buf.numel():
             size = max(2 * self._buf.numel(), start + nbytes + (1 << 20))

@@ -27,12 +27,18 @@ _sm_counts: dict = {}
 def sm_count(device=None) -> int:
     """Streaming multiprocessors of the device (the current one by default), asked of the device once.
     Slice counts, K splits and the choice between kernels follow it."""
+    if device is None:
+        n = _sm_counts.get(None)
+        if n is not None:
+            return n
     if not torch.cuda.is_available():
         raise KernelError("no CUDA device: the number of multiprocessors cannot be asked")
     idx = torch.cuda.current_device() if device is None else torch.device(device).index or 0
     n = _sm_counts.get(idx)
     if n is None:
         n = _sm_counts[idx] = int(torch.cuda.get_device_properties(idx).multi_processor_count)
+    if device is None:
+        _sm_counts[None] = n            # (one process drives one GPU: the current device does not change)
     return n
 
 
@@ -48,8 +54,19 @@ def _ptr(t):
     return 0 if t is None else t.data_ptr()
 
 
+# The current stream's handle is asked for at every launch: through the raw accessor that torch's own
+# extensions use (a few hundred nanoseconds) where it exists, not through the Stream object (microseconds).
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+_device_index = None
+
+
 def _stream() -> int:
-    return torch.cuda.current_stream().cuda_stream
+    global _device_index
+    if _raw_stream is None:
+        return torch.cuda.current_stream().cuda_stream
+    if _device_index is None:
+        _device_index = torch.cuda.current_device()
+    return _raw_stream(_device_index)
 
 
 def _check(rc: int, what: str) -> None:
