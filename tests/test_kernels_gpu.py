@@ -423,6 +423,38 @@ def test_gemm_tc_store(shape):
         assert rel_err(out, ref) <= (2 ** -8 if dt == torch.bfloat16 else max(2e-6, K * 2.0 ** -25)), (shape, dt)
 
 
+def test_product_plans_follow_shapes_and_contents():
+    """The runtime launches a product again from a remembered plan when operands and result lie where they
+    lay before.  Other shapes at the same addresses get a plan of their own, other contents at the same
+    addresses go through the old plan and give the new result, and a second runtime reports to its own
+    status word."""
+    gemm_tc, rt = _tc()
+    rt2 = _tc()[1]
+    ops = _ops()
+    g = torch.Generator().manual_seed(77)
+    abuf = torch.empty(1 << 20, dtype=torch.bfloat16, device=DEV)
+    wbuf = torch.empty(1 << 20, dtype=torch.bfloat16, device=DEV)
+    obuf = torch.empty(1 << 20, dtype=torch.float32, device=DEV)
+    seen = set()
+    for rep, (T, K, N) in enumerate([(8, 512, 256), (8, 512, 256), (16, 256, 256), (8, 256, 512), (8, 512, 256)]):
+        a = abuf[:T * K].view(T, K)
+        w = wbuf[:N * K].view(N, K)
+        out = obuf[:T * N].view(T, N)
+        a.copy_(torch.randn(T, K, generator=g).to(torch.bfloat16))
+        w.copy_((torch.randn(N, K, generator=g) * 0.05).to(torch.bfloat16))
+        out.fill_(float("nan"))
+        for r in (rt, rt2):
+            key = gemm_tc.launch_key(a, w, out, ops.EPI_STORE, None, r._status_ptr)
+            known = key in gemm_tc._plans
+            r.matmul(a, w, out, ops.EPI_STORE)
+            torch.cuda.synchronize()
+            gemm_tc.check_error(r)
+            assert key in gemm_tc._plans
+            assert rel_err(out, a.double() @ w.double().T) <= max(2e-6, K * 2.0 ** -25), (rep, T, K, N, known)
+            seen.add(key)
+    assert len(seen) == 6          # three shapes, two runtimes: the repeats found their plans
+
+
 @pytest.mark.parametrize("shape", [(3, 4096, 512, None), (8, 12288, 256, None), (64, 2048, 128, 4), (200, 1024, 300, 2),
                                    (7, 960, 130, 3)])
 def test_gemm_tc_add_with_and_without_k_split(shape):

@@ -28,12 +28,14 @@ class Arena:
         self._off = 0
         self.high_water = 0
         self._retired = []          # earlier buffers stay alive: captured graphs may point into them
+        self._views = {}            # (offset, dtype, shape) -> the tensor over that place of the current buffer
 
     def reserve(self, nbytes: int) -> None:
         if nbytes > self._buf.numel():
             if self._off != 0:
                 raise RuntimeError("arena can grow only when empty")
             self._retired.append(self._buf)
+            self._views.clear()
             self._buf = torch.empty(nbytes, dtype=torch.uint8, device=self.device)
 
     def mark(self) -> int:
@@ -51,11 +53,21 @@ class Arena:
         if start + nbytes > self._buf.numel():
             size = max(2 * self._buf.numel(), start + nbytes + (1 << 20))
             self._retired.append(self._buf)
+            self._views.clear()
             self._buf = torch.empty(size, dtype=torch.uint8, device=self.device)
             start = 0
         self._off = start + nbytes
-        self.high_water = max(self.high_water, self._off)
-        return self._buf[start:start + nbytes].view(dtype).view(*shape)
+        if self._off > self.high_water:
+            self.high_water = self._off
+        # layers reset the arena to the same mark, so the same (place, type, shape) comes again and again:
+        # the tensor object made for it the first time is handed out again (making one costs microseconds)
+        key = (start, dtype, tuple(shape))
+        t = self._views.get(key)
+        if t is None:
+            if len(self._views) > 4096:
+                self._views.clear()
+            t = self._views[key] = self._buf[start:start + nbytes].view(dtype).view(*shape)
+        return t
 
 
 class Runtime:
@@ -77,6 +89,7 @@ class Runtime:
         # (they are the head of a buffer whose tail takes the sampled token ids: one copy brings both)
         self.status_and_ids = torch.zeros(4 + 4096, dtype=torch.int32, device=self.device)
         self.status = self.status_and_ids[:4]
+        self._status_ptr = self.status[1:2].data_ptr()
 
     def shared(self, key, make):
         """One object for all parts that ask with the same key (rotation tables and the like)."""
@@ -99,8 +112,11 @@ class Runtime:
         self.launches += 1
         if self.use_tensor_cores and a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16:
             from ..kernels import gemm_tc
+            key = gemm_tc.launch_key(a, w, out, epilogue, w2, self._status_ptr)
+            if gemm_tc.relaunch(key):
+                return None
             if gemm_tc.accepts(a, w, out, epilogue, w2):
-                return gemm_tc.gemm(a, w, out, epilogue, w2, self)
+                return gemm_tc.gemm(a, w, out, epilogue, w2, self, key=key)
         if epilogue == ops.EPI_SWIGLU_IL:
             raise ops.KernelError("the interleaved gate/up layout is for the tensor-core product only; "
                                   "this call does not fit it (operand alignment)")

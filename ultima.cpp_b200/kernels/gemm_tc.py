@@ -46,12 +46,13 @@ def lib():
     return _lib
 
 
-def _tmap(t: torch.Tensor, box_rows: int) -> int:
-    """Address of a 64-byte aligned CUtensorMap on the host for the 2-D bfloat16 matrix ``t``."""
+def _tmap_entry(t: torch.Tensor, box_rows: int):
+    """(the buffer that holds it, address) of a 64-byte aligned CUtensorMap on the host for the 2-D bfloat16
+    matrix ``t``."""
     key = (t.data_ptr(), t.shape[0], t.shape[1], t.stride(0), box_rows)
     hit = _maps.get(key)
     if hit is not None:
-        return hit[1]
+        return hit
     raw = ctypes.create_string_buffer(128 + 64)
     addr = (ctypes.addressof(raw) + 63) & ~63
     rc = lib().ub_tmap_bf16_2d(addr, t.data_ptr(), t.shape[0], t.shape[1], t.stride(0), box_rows)
@@ -61,7 +62,11 @@ def _tmap(t: torch.Tensor, box_rows: int) -> int:
     if len(_maps) > 4096:
         _maps.clear()
     _maps[key] = (raw, addr)
-    return addr
+    return _maps[key]
+
+
+def _tmap(t: torch.Tensor, box_rows: int) -> int:
+    return _tmap_entry(t, box_rows)[1]
 
 
 def _ok_operand(t: torch.Tensor) -> bool:
@@ -127,7 +132,7 @@ def pairs(T: int, N: int, splits: int, epilogue: int, n_sms: int | None = None) 
     return -(-N // 256) * -(-T // 256) >= (n_sms or sm_count()) // 2
 
 
-def gemm(a, w, out, epilogue, w2, rt, splits: int | None = None, bn: int | None = None):
+def gemm(a, w, out, epilogue, w2, rt, splits: int | None = None, bn: int | None = None, key=None):
     """out: [T, N]; for EPI_SWIGLU_IL [T, N / 2]; for EPI_STORE with ``splits`` > 1 a float32
     [splits, T, N] whose sum over the first axis is the product."""
     T, K = a.shape
@@ -146,16 +151,45 @@ def gemm(a, w, out, epilogue, w2, rt, splits: int | None = None, bn: int | None 
         ldo = out.stride(0)
     L = lib()
     if not tile_given and out.dim() == 2 and pairs(T, N, s, epilogue):
-        rc = L.ub_gemm_tc_pair(_tmap(w, 128), _tmap(a, 128), _ptr(out), BF16 if out.dtype == torch.bfloat16 else F32,
-                               out.stride(0), T, N, K, epilogue, _ptr(rt.status[1:2]), _stream())
-        return _check(rc, "gemm_tc_pair")
-    mw = _tmap(w, 128)
-    mw2 = _tmap(w2, 128) if w2 is not None else 0
-    ma = _tmap(a, bn)
-    err = rt.status[1:2]
-    rc = L.ub_gemm_tc(mw, mw2, ma, _ptr(out), BF16 if out.dtype == torch.bfloat16 else F32, ldo,
-                      split_stride, T, N, K, bn, epilogue, s, _ptr(err), _stream())
-    _check(rc, "gemm_tc")
+        fn, what = L.ub_gemm_tc_pair, "gemm_tc_pair"
+        maps = (_tmap_entry(w, 128), _tmap_entry(a, 128))
+        args = (maps[0][1], maps[1][1], _ptr(out), BF16 if out.dtype == torch.bfloat16 else F32,
+                out.stride(0), T, N, K, epilogue, _ptr(rt.status[1:2]))
+    else:
+        fn, what = L.ub_gemm_tc, "gemm_tc"
+        maps = (_tmap_entry(w, 128), _tmap_entry(w2, 128) if w2 is not None else (None, 0), _tmap_entry(a, bn))
+        args = (maps[0][1], maps[1][1], maps[2][1], _ptr(out),
+                BF16 if out.dtype == torch.bfloat16 else F32, ldo, split_stride, T, N, K, bn, epilogue, s,
+                _ptr(rt.status[1:2]))
+    if key is not None:
+        if len(_plans) > 8192:
+            _plans.clear()
+        _plans[key] = (fn, args, what, maps)     # (the maps' host memory lives as long as the plan)
+    _check(fn(*args, _stream()), what)
+
+
+# A product that came before with the same operands at the same places (the weights always are, the
+# activations and the result because a step's scratch is handed out in the same order every time) is
+# launched again from its plan: the function, its arguments and the tensor maps they point to.
+_plans: dict = {}
+
+
+def launch_key(a, w, out, epilogue, w2, status_ptr: int):
+    """Everything a plan depends on: places, shapes and strides of the operands and of the result, the
+    epilogue, and the status word the kernel reports to (another engine's tensors may come to lie at the
+    same addresses with other shapes)."""
+    return (a.data_ptr(), a.shape[0], a.shape[1], a.stride(0), w.data_ptr(), w.shape[0], w.stride(0), out.data_ptr(),
+            out.dim(), out.shape[-1], out.stride(-2) if out.dim() > 1 else 0, out.dtype, epilogue,
+            0 if w2 is None else w2.data_ptr(), status_ptr)
+
+
+def relaunch(key) -> bool:
+    """Launch the product of this key from its plan; False when there is none yet."""
+    plan = _plans.get(key)
+    if plan is None:
+        return False
+    _check(plan[0](*plan[1], _stream()), plan[2])
+    return True
 
 
 def store_splits(T: int, N: int, K: int, n_sms: int | None = None) -> int:
