@@ -180,7 +180,7 @@ def launch_key(a, w, out, epilogue, w2, status_ptr: int):
     same addresses with other shapes)."""
     return (a.data_ptr(), a.shape[0], a.shape[1], a.stride(0), w.data_ptr(), w.shape[0], w.stride(0), out.data_ptr(),
             out.dim(), out.shape[-1], out.stride(-2) if out.dim() > 1 else 0, out.dtype, epilogue,
-            0 if w2 is None else w2.data_ptr(), status_ptr)
+            0 if w2 is None else w2.data_ptr(), status_ptr, USE_PAIRS)
 
 
 def relaunch(key) -> bool:
