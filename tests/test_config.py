@@ -1,7 +1,5 @@
 """Configuration and registry (no GPU)."""
-import copy
 import json
-import os
 
 import pytest
 

@@ -1,8 +1,7 @@
 """Generation through the entry point against the plain implementation."""
-import numpy as np
 import pytest
 
-from conftest import TINY, random_ids
+from conftest import random_ids
 
 pytestmark = pytest.mark.gpu
 

@@ -2,7 +2,7 @@
 stop tokens, sequences that end earlier, slots given back, nothing fed after the end."""
 import pytest
 
-from ultima_b200.engine.generate import generate, plan_batches, run_batch
+from ultima_b200.engine.generate import generate, plan_batches
 from ultima_b200.sampling import SamplingParams
 
 

@@ -5,7 +5,7 @@ import math
 import numpy as np
 
 import plain_qwen3 as P
-from conftest import TINY, random_ids
+from conftest import random_ids
 
 
 def test_rmsnorm_closed_form():

@@ -4,7 +4,7 @@ against the plain implementation.  Seeds are fixed; a failure names the request 
 import numpy as np
 import pytest
 
-from conftest import TINY, close_enough
+from conftest import close_enough
 
 pytestmark = pytest.mark.gpu
 

@@ -9,7 +9,6 @@ way and is not compared (a few of the 64)."""
 import numpy as np
 import pytest
 
-from conftest import TINY
 
 pytestmark = pytest.mark.gpu
 

@@ -7,7 +7,7 @@ import sys
 import numpy as np
 import pytest
 
-from conftest import ROOT, TINY, random_ids, close_enough
+from conftest import ROOT, random_ids, close_enough
 
 pytestmark = pytest.mark.gpu
 

@@ -3,7 +3,6 @@ import json
 import os
 import struct
 
-import numpy as np
 import pytest
 import torch
 

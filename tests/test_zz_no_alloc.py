@@ -9,7 +9,6 @@ checks both against the entry point whose scratch the caller supplies.  It is co
 so that a run that stops at the first failure has already run every other test, and it must
 pass alone in a fresh process as well as after the others.
 """
-import ctypes
 import math
 from ctypes import c_float, c_int, c_longlong, c_void_p
 

@@ -21,7 +21,6 @@ from __future__ import annotations
 
 import json
 import sys
-import time
 
 USAGE = __doc__
 

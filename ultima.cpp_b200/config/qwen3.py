@@ -10,7 +10,7 @@ biases, half-split rotary pairing.
 """
 from __future__ import annotations
 
-from dataclasses import dataclass, field, asdict
+from dataclasses import dataclass
 from typing import Optional
 
 from .base import ConfigError

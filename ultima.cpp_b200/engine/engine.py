@@ -15,7 +15,7 @@ from __future__ import annotations
 import numpy as np
 import torch
 
-from ..arch import model_spec_for
+from .. import arch as _arch  # noqa: F401  (the architectures enter the registry when this is imported)
 from ..cache import Cache, CacheError, PAGE
 from ..config.base import config_from_dir, find_architecture
 from ..parts.base import KVNeed, ModelSpec

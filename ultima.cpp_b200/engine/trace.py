@@ -17,8 +17,6 @@ import json
 import os
 import sys
 
-import numpy as np
-
 
 def replay(engine, lines, out_dir: str, say=None) -> int:
     """Feed ``lines`` (an iterable of JSON strings) through ``engine``; returns the number of

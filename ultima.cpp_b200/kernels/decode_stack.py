@@ -12,7 +12,7 @@ from __future__ import annotations
 
 import ctypes
 import os
-from ctypes import c_float, c_int, c_longlong, c_void_p
+from ctypes import c_int, c_longlong, c_void_p
 
 import numpy as np
 import torch

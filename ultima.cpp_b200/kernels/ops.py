@@ -4,7 +4,6 @@ implementation behind them: on a machine without the GPU or the compiler they ra
 """
 from __future__ import annotations
 
-import ctypes
 from ctypes import c_float, c_int, c_longlong, c_ulonglong, c_void_p
 
 import numpy as np

@@ -12,7 +12,7 @@ activation, QKV kind and rotary style per architecture, include/ultima/model/arc
 """
 from __future__ import annotations
 
-from dataclasses import dataclass, field
+from dataclasses import dataclass
 from typing import Optional
 
 from ..weights.spec import WeightSpec

@@ -6,7 +6,6 @@ import numpy as np
 import torch
 
 from ..kernels import ops
-from .params import SamplingParams
 
 _MASK = (1 << 64) - 1
 
