@@ -335,6 +335,21 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const __gri
 
     if (warp == 0) {
         if (lane == 0) {
+            // the weights of the first stages depend on no kernel before this one: asked for before the wait
+            long long pre = 0;
+            {
+                Pieces first(n_tiles, nkb, p.share_tail, blockIdx.x, gridDim.x);
+                int tile, kb0, kb1;
+                while (pre < S::STAGES && first.next(tile, kb0, kb1)) {
+                    const int n0 = (tile / tiles_t) * BM;
+                    for (int kb = kb0; kb < kb1 && pre < S::STAGES; ++kb, ++pre) {
+                        uint8_t* st = smem + (int)pre * S::STAGE_BYTES;
+                        mbar_expect_tx(&full[pre], S::STAGE_BYTES);
+                        tma_load_2d(st, &map_w, &full[pre], kb * BK, n0);
+                        if (EPI == EPI_SWIGLU) tma_load_2d(st + S::A_BYTES, &map_w2, &full[pre], kb * BK, n0);
+                    }
+                }
+            }
             pdl_wait();
             long long it = 0;                            // stages filled so far, over all tiles
             bool ok = true;
@@ -345,12 +360,14 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const __gri
                 for (int kb = kb0; kb < kb1; ++kb, ++it) {
                     const int s = (int)(it % S::STAGES);
                     const uint32_t ph = (uint32_t)((it / S::STAGES) & 1);
-                    ok = mbar_wait(&empty[s], ph ^ 1, err);
-                    if (!ok) break;
                     uint8_t* st = smem + s * S::STAGE_BYTES;
-                    mbar_expect_tx(&full[s], S::STAGE_BYTES);
-                    tma_load_2d(st, &map_w, &full[s], kb * BK, n0);
-                    if (EPI == EPI_SWIGLU) tma_load_2d(st + S::A_BYTES, &map_w2, &full[s], kb * BK, n0);
+                    if (it >= pre) {
+                        ok = mbar_wait(&empty[s], ph ^ 1, err);
+                        if (!ok) break;
+                        mbar_expect_tx(&full[s], S::STAGE_BYTES);
+                        tma_load_2d(st, &map_w, &full[s], kb * BK, n0);
+                        if (EPI == EPI_SWIGLU) tma_load_2d(st + S::A_BYTES, &map_w2, &full[s], kb * BK, n0);
+                    }
                     tma_load_2d(st + S::A_BYTES * (EPI == EPI_SWIGLU ? 2 : 1), &map_a, &full[s], kb * BK, t0);
                 }
             }
