@@ -5,9 +5,11 @@
 
 One JSON line on standard output.  A step is one decode step of a batch of 8 sequences whose
 prompts (2,048 random token ids each) are already in the cache; ``value`` is decoded tokens
-a second, timed on the device with CUDA events around exactly K steps.  ``e2e`` is the same
-through the Python entry point (``LLM.generate``): token ids from the host in, sampled ids
-back on the host every step.  ``prefill`` times one 2,048-token prompt; ``points`` gives
+a second, timed on the device with CUDA events around exactly K steps after W warm-up steps.
+``e2e`` is the same through the Python entry point (``LLM.generate``): token ids from the host in,
+sampled ids back on the host every step; on the host's clock, again exactly K steps after W
+warm-up steps (the prompts and the steps right after them, which the device runs more slowly,
+are outside the timed region, as they are for ``value``).  ``prefill`` times one 2,048-token prompt; ``points`` gives
 decode at batch 1 and 64; ``roofline`` compares the bytes a decode step has to read (every
 weight once, the cache of the live sequences) with the measured copy bandwidth.
 Weights are random from a seed (there is no checkpoint offline); the step reads 15 GB of
@@ -543,11 +545,15 @@ def run_ours(args):
     # end to end through the generation loop: host token ids in, sampled ids out, every step
     prompts = [rng.integers(0, cfg.vocab_size, size=PROMPT).tolist() for _ in range(BATCH)]
     stats = LoopStats()
-    n_new = args.warmup + args.steps
+    n_new = args.warmup + args.steps + 1         # the prompts' own token, then warm-up steps, then the timed steps
     generate(engine, sampler.sample, prompts, SamplingParams(), n_new, (), max_batch=BATCH, stats=stats)
     stats = LoopStats()
     generate(engine, sampler.sample, prompts, SamplingParams(), n_new, (), max_batch=BATCH, stats=stats)
-    e2e_val = BATCH * (n_new - 1) / stats.decode_s
+    # the same rule as for ``value``: the first ``warmup`` steps after the prompts are not timed, then exactly
+    # ``steps`` steps are, on the host's clock from the arrival of one step's ids to the arrival of the last's
+    done = stats.step_done_s
+    assert len(done) == n_new and args.steps < len(done)
+    e2e_val = BATCH * args.steps / (done[-1] - done[-1 - args.steps])
     h2d = engine.last_h2d_bytes                   # the step's record (ids, positions, page tables); the
     # sampler's records stay on the device while a batch samples with the same parameters
     dev_ms = sorted(stats.device_step_ms)

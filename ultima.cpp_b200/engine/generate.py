@@ -39,6 +39,7 @@ class LoopStats:
     steps: int = 0
     device_prefill_ms: float = 0.0
     device_step_ms: list = field(default_factory=list)
+    step_done_s: list = field(default_factory=list)       # the host's clock when each step's ids had arrived
 
 
 def plan_batches(prompt_lens: list, max_batch: int, max_tokens: int, n_predict: list, page: int = PAGE):
@@ -134,6 +135,7 @@ def run_batch(engine, sample, prompts: list, params: list, n_predict: list, stop
                 else:
                     stats.decode_s += now - t0
                 stats.steps += 1
+                stats.step_done_s.append(now)
             first = False
             t0 = now
             going, feed, rows = [], [], []
