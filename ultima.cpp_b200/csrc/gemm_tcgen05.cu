@@ -54,11 +54,13 @@ struct Smem {
     static constexpr int B_BYTES = BN * BK * 2;
     static constexpr int STAGE_BYTES = A_BYTES * (EPI == EPI_SWIGLU ? 2 : 1) + B_BYTES;
     // token tiles of up to 64 leave room for two CTAs on an SM (this kernel's and the next one's)
-    static constexpr int BUDGET = (BN <= 64 && EPI != EPI_SWIGLU ? (EPI == EPI_SWIGLU_IL ? 106 : 110) : 196) * 1024;
+    static constexpr int BUDGET = (BN <= 64 && EPI != EPI_SWIGLU ? 110 : 196) * 1024;
     static constexpr int STAGES_RAW = BUDGET / STAGE_BYTES;
     static constexpr int STAGES = STAGES_RAW > 10 ? 10 : STAGES_RAW;
-    static constexpr int XCH_BYTES = EPI == EPI_SWIGLU_IL ? 64 * 16 * 4 : 0;
-    static constexpr int TOTAL = STAGES * STAGE_BYTES + 1024 /*alignment*/ + 256 /*barriers*/ + XCH_BYTES;
+    // (the interleaved gate product's exchange buffer, 4 KB, lies over the first stage: the epilogue runs when
+    // every stage has been used for the last time)
+    static constexpr int TOTAL = STAGES * STAGE_BYTES + 1024 /*alignment*/ + 256 /*barriers*/;
+    static_assert(STAGE_BYTES >= 64 * 16 * 4, "the exchange buffer must fit a stage");
     static constexpr int ACC_COLS = BN * (EPI == EPI_SWIGLU ? 2 : 1);
     static constexpr int TMEM_COLS = ACC_COLS <= 32 ? 32 : ACC_COLS <= 64 ? 64 : ACC_COLS <= 128 ? 128 : ACC_COLS <= 256 ? 256 : 512;
 };
@@ -132,7 +134,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     uint64_t* acc_full = empty + S::STAGES;
     uint32_t* tmem_slot = (uint32_t*)(acc_full + 1);
     volatile int* err = (volatile int*)(tmem_slot + 1);
-    float* xch = (float*)(smem + S::STAGES * S::STAGE_BYTES + 256);       // EPI_SWIGLU_IL only
+    float* xch = (float*)smem;                   // EPI_SWIGLU_IL only: over the first stage, which is free by then
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int n0 = blockIdx.x * BM;                 // first weight row = first output column
