@@ -207,3 +207,49 @@ def test_the_toy_architecture_is_listed_and_refuses_a_bad_configuration():
     assert "blocks.1.ffn.down_proj.weight" in names and "out.weight" not in names      # tied: no output matrix
     assert [r.layer for r in spec.runs] == [0, 1, 0]
     assert os.path.basename(__file__).startswith("test_")
+
+
+def test_the_command_line_programs_take_an_architecture_from_outside_the_package(tmp_path):
+    """``bin/trace_run`` and ``bin/ultima`` are processes of their own: a module named in ULTIMA_ARCH_MODULES
+    enters its architecture into their registry.  The module here imports this test file's definitions."""
+    import json
+    import subprocess
+    import sys
+    import plain_qwen3 as P
+    import ultima_b200 as u
+    from conftest import ROOT
+    _register()
+    cfg = u.config_from_dict(CONFIGS["tc"])
+    model_dir = str(tmp_path / "tc")
+    u.write_random_model(model_dir, cfg, seed=12, dtype="bfloat16")
+    plug = tmp_path / "plug"
+    plug.mkdir()
+    (plug / "toy_twin_arch.py").write_text("import test_toy_architecture_gpu as t\nt._register()\n")
+    env = dict(os.environ)
+    env["ULTIMA_ARCH_MODULES"] = "toy_twin_arch"
+    env["PYTHONPATH"] = os.pathsep.join([str(plug), os.path.dirname(os.path.abspath(__file__)), env.get("PYTHONPATH", "")])
+    listed = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "ultima"), "archs"], env=env, capture_output=True,
+                            text=True, timeout=300)
+    assert listed.returncode == 0 and "ToyTwinForCausalLM" in listed.stdout, listed.stderr[-1500:]
+    pcfg, w = P.read_folder(model_dir)
+    rng = np.random.default_rng(8)
+    a, b = rng.integers(0, pcfg["vocab"], size=70).tolist(), rng.integers(0, pcfg["vocab"], size=9).tolist()
+    steps = [{"step": 0, "entries": [{"id": "a", "tokens": a[:66], "want": [0, 65]}, {"id": "b", "tokens": b[:5], "want": [4]}], "end": []}]
+    for t in range(4):
+        steps.append({"step": t + 1, "entries": [{"id": "a", "tokens": [a[66 + t]], "want": [0]},
+                                                 {"id": "b", "tokens": [b[5 + t]], "want": [0]}],
+                      "end": ["a", "b"] if t == 3 else []})
+    out_dir = str(tmp_path / "out")
+    p = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "trace_run"), "--model", model_dir, "--dtype", "float32",
+                        "--out", out_dir, "--max-tokens", "192"], input="".join(json.dumps(s) + "\n" for s in steps),
+                       env=env, capture_output=True, text=True, timeout=600)
+    assert p.returncode == 0, p.stderr[-2000:]
+    ra, rb = _plain_forward(pcfg, w, a), _plain_forward(pcfg, w, b)
+    first = np.fromfile(os.path.join(out_dir, "0.f32"), dtype="<f4").reshape(3, pcfg["vocab"])
+    want = [ra[0], ra[65], rb[4]]
+    for t in range(4):
+        rows = np.fromfile(os.path.join(out_dir, f"{t + 1}.f32"), dtype="<f4").reshape(2, pcfg["vocab"])
+        first = np.concatenate([first, rows])
+        want += [ra[66 + t], rb[5 + t]]
+    err, bound = close_enough(first, np.stack(want), "float32", pcfg["depth"] + 1)
+    assert err <= bound, (err, bound)
