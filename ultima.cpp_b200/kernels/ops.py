@@ -56,16 +56,13 @@ def _ptr(t):
 # The current stream's handle is asked for at every launch: through the raw accessor that torch's own
 # extensions use (a few hundred nanoseconds) where it exists, not through the Stream object (microseconds).
 _raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
-_device_index = None
+_raw_device = getattr(torch._C, "_cuda_getDevice", None)
 
 
 def _stream() -> int:
-    global _device_index
-    if _raw_stream is None:
+    if _raw_stream is None or _raw_device is None:
         return torch.cuda.current_stream().cuda_stream
-    if _device_index is None:
-        _device_index = torch.cuda.current_device()
-    return _raw_stream(_device_index)
+    return _raw_stream(_raw_device())
 
 
 def _check(rc: int, what: str) -> None:
